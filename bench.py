@@ -1,0 +1,414 @@
+#!/usr/bin/env python
+"""Benchmark of the Q4_0 mat-mul hot path (decode skinny-GEMM at LLaMA-7B FFN shapes).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
+
+Workload (BASELINE config 2): gate / up 11008x4096 and down 4096x11008 Q4_0 weights,
+seeded N(0, 0.02) synthetic values, f32 N(0, 1) activations at batch B (default 1).
+A *step* is one pass over a pool of `--sets` distinct FFN weight sets (3 mat-muls per
+set); the pool is larger than the 126 MB L2 several times over, so every weight byte
+comes from HBM.  Metric: algorithmic bytes (weights once + f32 activations once + f32
+outputs once) per second, in GB/s.
+
+One JSON line is printed by rank 0 (see the keys at the end of run_ours / run_reference).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, FFN = 4096, 11008
+METRIC = "q4_0_mul_mat_hbm_gbs"
+UNIT = "GB/s"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def algorithmic_bytes(n: int, k: int, b: int) -> int:
+    """Weights once + f32 activations once + f32 outputs once."""
+    return n * (k // 32) * 18 + b * k * 4 + b * n * 4
+
+
+def ffn_shapes():
+    """(name, N, K) of the three FFN mat-muls."""
+    return [("gate", FFN, HIDDEN), ("up", FFN, HIDDEN), ("down", HIDDEN, FFN)]
+
+
+# ----------------------------------------------------------------------------- synthetic data
+def make_q4_0(n: int, k: int, seed: int, device):
+    """Seeded N(0, 0.02) weights quantised to Q4_0 blocks ({f16 d; 16 bytes of nibbles}; element
+    j in the low nibble of byte j, element j+16 in the high nibble; value (q - 8) * d) with torch
+    ops.  Data generation only — not part of the measured path.  Returns uint8 [n * k/32 * 18]."""
+    import torch
+
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    w = torch.randn(n, k // 32, 32, generator=g, device=device, dtype=torch.float32) * 0.02
+    idx = w.abs().argmax(dim=-1, keepdim=True)
+    mx = torch.gather(w, -1, idx)
+    d = mx / -8.0
+    idv = torch.where(d != 0, 1.0 / d, torch.zeros_like(d))
+    q = torch.clamp(torch.trunc(w * idv + 8.5), 0, 15).to(torch.uint8)
+    packed = q[..., :16] | (q[..., 16:] << 4)
+    dh = d.to(torch.float16).view(torch.uint8).reshape(n, k // 32, 2)
+    return torch.cat([dh, packed], dim=-1).reshape(-1).contiguous()
+
+
+class ClockSampler:
+    """Polls SM clock, power and throttle reasons of one GPU through NVML while a region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self.nv is not None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_pass(O, sets_host, xs, nth: int):
+    """One pass of the reference's CPU mat-mul (oracle restatement) over host weight sets."""
+    for ws in sets_host:
+        for (name, n, k), w in zip(ffn_shapes(), ws):
+            O.mul_mat_q4_0(w, xs[k], nth=nth, avx=True)
+
+
+def make_host_sets(nsets: int, batch: int):
+    """Host copies of `nsets` FFN weight sets + activations, generated with torch on the CPU."""
+    import numpy as np
+    import torch
+
+    sets = []
+    for s in range(nsets):
+        ws = []
+        for mi, (name, n, k) in enumerate(ffn_shapes()):
+            ws.append(make_q4_0(n, k, 20261125 + 1000 * s + mi, torch.device("cpu")).numpy().reshape(n, -1))
+        sets.append(ws)
+    g = torch.Generator()
+    g.manual_seed(77)
+    xs = {k: torch.randn(batch, k, generator=g).numpy().astype(np.float32) for k in (HIDDEN, FFN)}
+    return sets, xs
+
+
+def time_cpu(O, sets_host, xs, nth: int, min_seconds: float, min_passes: int = 2):
+    cpu_pass(O, sets_host, xs, nth)  # warm-up
+    t0 = time.perf_counter()
+    passes = 0
+    while passes < min_passes or time.perf_counter() - t0 < min_seconds:
+        cpu_pass(O, sets_host, xs, nth)
+        passes += 1
+    return (time.perf_counter() - t0) / passes, passes
+
+
+def run_reference(args):
+    """The reference's own CPU implementation of the path, timed on the host cores: the C++
+    restatement of MatMul::f_q_f32_f32 + vec_dot_q8_0 (AVX2) with the reference's fixed
+    4-task split, because the Rust crate cannot be built in this image."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle as O
+
+    O.build()
+    nsets = 4  # 304 MB of weights: larger than any host L3
+    sets_host, xs = make_host_sets(nsets, args.batch)
+    bytes_pass = nsets * sum(algorithmic_bytes(n, k, args.batch) for _, n, k in ffn_shapes())
+    nth = 4
+    for _ in range(args.warmup):
+        cpu_pass(O, sets_host, xs, nth)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_pass(O, sets_host, xs, nth)
+    dt = (time.perf_counter() - t0) / max(1, args.steps)
+    val = bytes_pass / dt / 1e9
+    sample = f"{nsets} FFN weight sets ({nsets * 3} mat-muls, {bytes_pass / 1e6:.0f} MB) per step at batch {args.batch}"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak",
+        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": "config2: LLaMA-7B FFN decode skinny-GEMM, gate/up 11008x4096 + down 4096x11008, Q4_0 x Q8_0",
+                   "batch": args.batch, "sets_per_step": nsets},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": nth, "kind": "port", "sample": sample,
+                         "host_cpus": os.cpu_count()},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import galois_b200 as gb
+    from galois_b200 import lib
+    from galois_b200.shard import shard_rows
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if args.gpus > 1 and world == 1:
+        raise SystemExit("launch multi-GPU runs with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    stream = torch.cuda.Stream(device)
+    torch.cuda.set_stream(stream)
+    dev = gb.CudaDevice(local_rank, stream)
+    ctx = dev.ctx
+    B, nsets = args.batch, args.sets
+
+    # ---- resident weights: `nsets` FFN sets, row-sharded when world > 1
+    shapes = ffn_shapes()
+    bands = {name: shard_rows(n, world, rank) for name, n, k in shapes}
+    weights = []  # [set][matrix] -> (torch uint8 buffer, galois_dim of the local band)
+    for s in range(nsets):
+        ws = []
+        for mi, (name, n, k) in enumerate(shapes):
+            r0, nr = bands[name]
+            buf = make_q4_0(nr, k, 20261125 + 1000 * s + mi + 100000 * rank, device)
+            ws.append((buf, gb.Dim.ggml((k, nr), gb.GGmlType.Q4_0).c_struct()))
+        weights.append(ws)
+    g = torch.Generator(device=device)
+    g.manual_seed(77)
+    xs = {k: torch.randn(B, k, generator=g, device=device, dtype=torch.float32) for k in (HIDDEN, FFN)}
+    xdims = {k: gb.Dim.ggml((k, B), gb.GGmlType.F32).c_struct() for k in (HIDDEN, FFN)}
+    outs, odims, fulls = {}, {}, {}
+    for name, n, k in shapes:
+        nr = bands[name][1]
+        outs[name] = torch.zeros(B, nr, device=device, dtype=torch.float32)
+        odims[name] = gb.Dim.ggml((nr, B), gb.GGmlType.F32).c_struct()
+        if world > 1:
+            fulls[name] = torch.zeros(world, B, nr, device=device, dtype=torch.float32)
+    weight_bytes = sum(w[0].numel() for ws in weights for w in ws)
+    bytes_step = nsets * sum(algorithmic_bytes(n, k, B) for _, n, k in shapes)  # whole job, all ranks
+    calls_step = nsets * len(shapes)
+
+    def mul_mat(wbuf, wdim, k, name):
+        rc = lib.galois_b200_mul_mat_q4_0_f32(ctx, C.c_void_p(wbuf.data_ptr()), C.byref(wdim), C.c_void_p(xs[k].data_ptr()),
+                                              C.byref(xdims[k]), C.c_void_p(outs[name].data_ptr()), C.byref(odims[name]))
+        if rc != 0:
+            raise RuntimeError(f"mul_mat_q4_0 failed: {lib.galois_b200_last_error(ctx)} ({rc})")
+
+    def step():
+        for ws in weights:
+            for (name, n, k), (wbuf, wdim) in zip(shapes, ws):
+                mul_mat(wbuf, wdim, k, name)
+                if world > 1:  # the exchange step: all-gather of the f32 output bands
+                    dist.all_gather_into_tensor(fulls[name], outs[name])
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    for _ in range(max(3, args.warmup)):
+        step()
+    sync_all()
+
+    # ---- `value`: whole-job throughput, inputs resident in HBM; one CUDA graph per step at N = 1
+    use_graph = world == 1 and not args.no_graph
+    launches0 = dev.launch_count()
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        launches_step = dev.launch_count() - launches0
+        run_step = graph.replay
+    else:
+        step()
+        launches_step = dev.launch_count() - launches0
+        run_step = step
+    for _ in range(max(3, args.warmup)):
+        run_step()
+    sync_all()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        run_step()
+    e1.record(stream)
+    sync_all()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / args.steps
+    value = bytes_step / (ms_step * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel: events around every mat-mul kernel launch (stream launches)
+    lib.galois_b200_profile_enable(ctx, 1)
+    prof_steps = max(1, min(args.steps, 4096 // calls_step))
+    for _ in range(prof_steps):
+        step()
+    tot, cnt = C.c_double(), C.c_int64()
+    lib.galois_b200_profile_read(ctx, C.byref(tot), C.byref(cnt))
+    lib.galois_b200_profile_enable(ctx, 0)
+    kernel_ms = tot.value / max(1, cnt.value)
+    local_bytes_call = sum(algorithmic_bytes(bands[name][1], k, B) for name, n, k in shapes) / len(shapes)
+    peak, peak_kind = measured_peak_gbs()
+    achieved = local_bytes_call / (kernel_ms * 1e-3) / 1e9 if kernel_ms > 0 else 0.0
+
+    # ---- e2e: the host-buffer entry point; activations from pinned host memory, results read back
+    e2e = None
+    if world == 1:
+        xh = {k: torch.randn(B, k, dtype=torch.float32).pin_memory() for k in (HIDDEN, FFN)}
+        oh = {name: torch.zeros(B, n, dtype=torch.float32).pin_memory() for name, n, k in shapes}
+
+        def e2e_step():
+            for ws in weights:
+                for (name, n, k), (wbuf, wdim) in zip(shapes, ws):
+                    rc = lib.galois_b200_mul_mat_q4_0_f32_host(ctx, C.c_void_p(wbuf.data_ptr()), C.byref(wdim),
+                                                               C.c_void_p(xh[k].data_ptr()), C.byref(xdims[k]),
+                                                               C.c_void_p(oh[name].data_ptr()), C.byref(odims[name]))
+                    if rc != 0:
+                        raise RuntimeError(f"mul_mat_q4_0_host failed: {lib.galois_b200_last_error(ctx)} ({rc})")
+
+        for _ in range(3):
+            e2e_step()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        e2e_ms = e0.elapsed_time(e1) / args.steps
+        e2e = {"value": bytes_step / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": nsets * sum(B * k * 4 for _, n, k in shapes),
+               "d2h_bytes_per_step": nsets * sum(B * n * 4 for _, n, k in shapes), "ms_per_step": e2e_ms}
+    sampler.stop()
+
+    # ---- CPU baseline (rank 0, N = 1): the oracle's restatement of the reference CPU path, 4 tasks
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        import oracle as O
+
+        O.build()
+        csets = 2
+        sets_host = [[w[0].cpu().numpy().reshape(shapes[i][1], -1) for i, w in enumerate(ws)] for ws in weights[:csets]]
+        xs_host = {k: v.cpu().numpy() for k, v in xs.items()}
+        dt, passes = time_cpu(O, sets_host, xs_host, 4, args.cpu_seconds)
+        cbytes = csets * sum(algorithmic_bytes(n, k, B) for _, n, k in shapes)
+        cpu = {"value": cbytes / dt / 1e9, "unit": UNIT, "cores": 4, "kind": "port",
+               "sample": f"{csets} of the {nsets} FFN weight sets ({csets * 3} mat-muls, {cbytes / 1e6:.0f} MB) x {passes} passes, "
+                         f"AVX2 vec_dot, the reference's fixed 4-task split", "host_cpus": os.cpu_count()}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "u8", "data": "synthetic",
+            "config": {"workload": "config2: LLaMA-7B FFN decode skinny-GEMM, gate/up 11008x4096 + down 4096x11008, Q4_0 x Q8_0",
+                       "batch": B, "sets_per_step": nsets, "mat_muls_per_step": calls_step,
+                       "weight_bytes_resident_per_gpu": weight_bytes,
+                       "l2": f"inputs larger than L2: {weight_bytes / L2_BYTES:.1f}x the 126 MB L2 streamed between reuses",
+                       "launch": "cuda_graph" if use_graph else "stream",
+                       "parallelism": f"rows/{world} + nccl all_gather" if world > 1 else "single gpu"},
+            "roofline": {"bound": "hbm", "kernel": "mmv_q4_0_bulk", "achieved": achieved, "peak": peak, "unit": UNIT,
+                         "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                         "kernel_us": kernel_ms * 1e3, "algorithmic_bytes_per_launch": local_bytes_call,
+                         "timed_launches": cnt.value, "frac_of_8000_nominal": achieved / 8000.0},
+            "gpu_launches": launches_step * args.steps,
+            "clocks": sampler.summary(),
+        }
+        if e2e is not None:
+            line["e2e"] = e2e
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    dev.close()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--sets", type=int, default=16, help="distinct FFN weight sets per step (16 -> 1.2 GB of Q4_0)")
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-graph", action="store_true", help="plain stream launches instead of one CUDA graph per step")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,72 @@
+"""ctypes binding of ``libgalois_b200.so`` (declared in ``include/galois_b200.h``).
+
+There is no fallback of any kind: if the shared library is missing or a symbol
+is absent, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libgalois_b200.so")
+
+
+class GaloisDim(C.Structure):
+    """``galois_dim``: copy of galois ``Dim`` (src/shape.rs:29-34)."""
+
+    _fields_ = [("n_dims", C.c_int32), ("ne", C.c_int64 * 4), ("nb", C.c_int64 * 4)]
+
+
+_P, _F, _I, _I64, _SZ = C.c_void_p, C.c_float, C.c_int, C.c_int64, C.c_size_t
+_DP = C.POINTER(GaloisDim)
+
+# name -> (argtypes, restype); must list every function include/galois_b200.h declares
+SIGNATURES = {
+    "galois_b200_init": ([_I, _P, C.POINTER(_P)], _I),
+    "galois_b200_destroy": ([_P], _I),
+    "galois_b200_set_stream": ([_P, _P], _I),
+    "galois_b200_last_error": ([_P], C.c_char_p),
+    "galois_b200_launch_count": ([_P], _I64),
+    "galois_b200_set_mul_mat_variant": ([_P, _I], _I),
+    "galois_b200_profile_enable": ([_P, _I], _I),
+    "galois_b200_profile_read": ([_P, C.POINTER(C.c_double), C.POINTER(_I64)], _I),
+    "galois_b200_alloc": ([_P, _SZ, C.POINTER(_P)], _I),
+    "galois_b200_free": ([_P, _P], _I),
+    "galois_b200_htod": ([_P, _P, _P, _SZ], _I),
+    "galois_b200_dtoh": ([_P, _P, _P, _SZ], _I),
+    "galois_b200_synchronize": ([_P], _I),
+    "galois_b200_quantize_q8_0": ([_P, _P, _I64, _P, _I64, _I64], _I),
+    "galois_b200_block_isums_q4_0_q8_0": ([_P, _P, _P, _I64, _P], _I),
+    "galois_b200_mul_mat_q4_0_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
+    "galois_b200_mul_mat_q4_0_f32_host": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
+    "galois_b200_mul_mat_f16_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
+    "galois_b200_rms_norm_f32": ([_P, _P, _DP, _P, _DP, _F], _I),
+    "galois_b200_rope_f32": ([_P, _P, _DP, _P, _DP, _P, _DP, _I, _I, _I, _F, _F, _F, _I], _I),
+    "galois_b200_soft_max_f32": ([_P, _P, _DP, _P, _DP], _I),
+    "galois_b200_soft_max_ext_f32": ([_P, _P, _DP, _P, _DP, _F, _P], _I),
+    "galois_b200_silu_f32": ([_P, _P, _DP, _P, _DP], _I),
+    "galois_b200_mul_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
+    "galois_b200_add_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
+    "galois_b200_scale_f32": ([_P, _P, _DP, _F, _P, _DP], _I),
+    "galois_b200_cpy_f32_f32": ([_P, _P, _DP, _P, _DP], _I),
+    "galois_b200_cpy_f32_f16": ([_P, _P, _DP, _P, _DP], _I),
+    "galois_b200_shard_rows": ([_I64, _I, _I, C.POINTER(_I64), C.POINTER(_I64)], _I),
+}
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python galois_b200/build.py` (nvcc, sm_100a). "
+            "galois_b200 has no CPU or eager fallback."
+        )
+    lib = C.CDLL(LIB_PATH)
+    for name, (args, res) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.argtypes = args
+        fn.restype = res
+    return lib
+
+
+lib = _load()

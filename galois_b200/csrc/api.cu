@@ -1,0 +1,383 @@
+// Context management, memory helpers and the Q4_0 mat-mul dispatcher of the
+// galois_b200 C ABI.
+#include <math.h>
+#include <stdarg.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "mul_mat_q4_0.cuh"
+#include "mul_mat_q4_0_tc.cuh"
+#include "quantize.cuh"
+
+static char g_init_err[512] = "";
+
+int gb_fail(galois_b200_ctx* ctx, int code, const char* fmt, ...) {
+    char* buf = ctx ? ctx->err : g_init_err;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, 512, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int gb_scratch(galois_b200_ctx* ctx, size_t bytes, void** out) {
+    if (bytes > ctx->scratch_bytes) {
+        // growth: the old arena may still be in use by work already enqueued
+        GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->scratch) GB_CUDA(ctx, cudaFree(ctx->scratch));
+        ctx->scratch = nullptr;
+        ctx->scratch_bytes = 0;
+        size_t want = bytes + bytes / 4;
+        want = (want + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
+        cudaError_t e = cudaMalloc(&ctx->scratch, want);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            return gb_fail(ctx, GALOIS_B200_E_NOMEM, "scratch arena: cudaMalloc(%zu) failed: %s", want, cudaGetErrorString(e));
+        }
+        ctx->scratch_bytes = want;
+    }
+    *out = ctx->scratch;
+    return 0;
+}
+
+// IEEE binary32 -> binary16 (round to nearest even) and back, on the host, for
+// building the look-up tables without depending on F16C.
+static uint16_t host_f32_to_f16(float x) {
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    const uint32_t sign = (u >> 16) & 0x8000u;
+    const uint32_t em = u & 0x7fffffffu;
+    if (em >= 0x7f800000u) return (uint16_t)(sign | 0x7c00u | ((em > 0x7f800000u) ? (0x0200u | ((em >> 13) & 0x3ffu)) : 0));
+    if (em >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u);
+    if (em < 0x33000001u) return (uint16_t)sign;
+    const int32_t exp = (int32_t)(em >> 23) - 127;
+    uint32_t man = (em & 0x7fffffu) | 0x800000u;
+    int shift = 13;
+    uint32_t base = 0;
+    if (exp < -14) {
+        shift = 13 + (-14 - exp);
+    } else {
+        base = (uint32_t)(exp + 15) << 10;
+        man &= 0x7fffffu;
+    }
+    uint32_t q = man >> shift;
+    const uint32_t rem = man & ((1u << shift) - 1), half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (q & 1))) q++;
+    return (uint16_t)(sign | (base + q));
+}
+static float host_f16_to_f32(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    const uint32_t e = (h >> 10) & 0x1fu, m = h & 0x3ffu;
+    uint32_t u;
+    if (e == 0) {
+        if (m == 0) {
+            u = sign;
+        } else {  // subnormal
+            int s = 0;
+            uint32_t mm = m;
+            while (!(mm & 0x400u)) {
+                mm <<= 1;
+                s++;
+            }
+            u = sign | ((uint32_t)(127 - 15 - s + 1) << 23) | ((mm & 0x3ffu) << 13);
+        }
+    } else if (e == 31) {
+        u = sign | 0x7f800000u | (m << 13);
+    } else {
+        u = sign | ((e + 112u) << 23) | (m << 13);
+    }
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** out) {
+    if (!out) return gb_fail(nullptr, GALOIS_B200_E_BADARG, "init: out is null");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return gb_fail(nullptr, (int)e, "init: cudaGetDeviceCount: %s", cudaGetErrorString(e));
+    }
+    if (ordinal < 0 || ordinal >= count) return gb_fail(nullptr, GALOIS_B200_E_BADARG, "init: ordinal %d out of range (%d devices)", ordinal, count);
+    e = cudaSetDevice(ordinal);
+    if (e != cudaSuccess) return gb_fail(nullptr, (int)e, "init: cudaSetDevice: %s", cudaGetErrorString(e));
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, ordinal);
+    if (e != cudaSuccess) return gb_fail(nullptr, (int)e, "init: cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+    if (prop.major != 10) return gb_fail(nullptr, GALOIS_B200_E_STATE, "init: device %d is sm_%d%d; this library holds sm_100a code only", ordinal, prop.major, prop.minor);
+
+    galois_b200_ctx* ctx = (galois_b200_ctx*)calloc(1, sizeof(galois_b200_ctx));
+    if (!ctx) return gb_fail(nullptr, GALOIS_B200_E_NOMEM, "init: out of host memory");
+    ctx->ordinal = ordinal;
+    ctx->stream = (cudaStream_t)cu_stream;
+    ctx->sm_count = prop.multiProcessorCount;
+
+    // f16 tables of GLOBAL_CPU_DEVICE_CACHE (src/op.rs:227-252): entry i =
+    // f16(f(f32(f16::from_bits(i)))) with libm expf, built once on the host and
+    // kept in device memory (128 KB each; they stay L2-resident).
+    uint16_t* tab = (uint16_t*)malloc(2 * 65536 * sizeof(uint16_t));
+    if (!tab) {
+        free(ctx);
+        return gb_fail(nullptr, GALOIS_B200_E_NOMEM, "init: out of host memory");
+    }
+    for (uint32_t i = 0; i < 65536; i++) {
+        const float v = host_f16_to_f32((uint16_t)i);
+        tab[i] = host_f32_to_f16(expf(v));
+        tab[65536 + i] = host_f32_to_f16(v / (1.0f + expf(-v)));
+    }
+    int rc = 0;
+    do {
+        if ((e = cudaMalloc(&ctx->exp_lut, 65536 * 2)) != cudaSuccess) break;
+        if ((e = cudaMalloc(&ctx->silu_lut, 65536 * 2)) != cudaSuccess) break;
+        if ((e = cudaMalloc(&ctx->dev_status, 256)) != cudaSuccess) break;
+        if ((e = cudaMemcpy(ctx->exp_lut, tab, 65536 * 2, cudaMemcpyHostToDevice)) != cudaSuccess) break;
+        if ((e = cudaMemcpy(ctx->silu_lut, tab + 65536, 65536 * 2, cudaMemcpyHostToDevice)) != cudaSuccess) break;
+        if ((e = cudaMemset(ctx->dev_status, 0, 256)) != cudaSuccess) break;
+    } while (0);
+    free(tab);
+    if (e != cudaSuccess) {
+        rc = gb_fail(nullptr, (int)e, "init: device set-up failed: %s", cudaGetErrorString(e));
+    } else {
+        void* p;
+        rc = gb_scratch(ctx, (size_t)16 << 20, &p);
+        if (rc == 0) rc = gb_mmv_bulk_init(ctx);
+        if (rc == 0) rc = gb_mm_tc_init(ctx);
+        if (rc != 0) snprintf(g_init_err, sizeof(g_init_err), "%s", ctx->err);
+    }
+    if (rc != 0) {
+        galois_b200_destroy(ctx);
+        return rc;
+    }
+    *out = ctx;
+    return 0;
+}
+
+extern "C" int galois_b200_destroy(galois_b200_ctx* ctx) {
+    if (!ctx) return 0;
+    cudaSetDevice(ctx->ordinal);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->exp_lut) cudaFree(ctx->exp_lut);
+    if (ctx->silu_lut) cudaFree(ctx->silu_lut);
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->io) cudaFree(ctx->io);
+    if (ctx->prof_ev) {
+        for (int i = 0; i < 2 * GB_PROF_MAX; i++)
+            if (ctx->prof_ev[i]) cudaEventDestroy(ctx->prof_ev[i]);
+        free(ctx->prof_ev);
+    }
+    (void)cudaGetLastError();
+    free(ctx);
+    return 0;
+}
+
+extern "C" int galois_b200_set_stream(galois_b200_ctx* ctx, void* cu_stream) {
+    GB_CHECK_CTX(ctx);
+    ctx->stream = (cudaStream_t)cu_stream;
+    return 0;
+}
+
+extern "C" const char* galois_b200_last_error(galois_b200_ctx* ctx) { return ctx ? ctx->err : g_init_err; }
+
+extern "C" int64_t galois_b200_launch_count(galois_b200_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+extern "C" int galois_b200_set_mul_mat_variant(galois_b200_ctx* ctx, int variant) {
+    GB_CHECK_CTX(ctx);
+    if (variant < 0 || variant > 3) return gb_fail(ctx, GALOIS_B200_E_BADARG, "set_mul_mat_variant: %d not in 0..3", variant);
+    ctx->variant = variant;
+    return 0;
+}
+
+extern "C" int galois_b200_alloc(galois_b200_ctx* ctx, size_t bytes, void** out_dev) {
+    GB_CHECK_CTX(ctx);
+    if (!out_dev) return gb_fail(ctx, GALOIS_B200_E_BADARG, "alloc: out is null");
+    *out_dev = nullptr;
+    if (bytes == 0) return 0;
+    cudaError_t e = cudaMalloc(out_dev, bytes);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return gb_fail(ctx, GALOIS_B200_E_NOMEM, "alloc: cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
+    }
+    return 0;
+}
+extern "C" int galois_b200_free(galois_b200_ctx* ctx, void* dev) {
+    GB_CHECK_CTX(ctx);
+    if (dev) GB_CUDA(ctx, cudaFree(dev));
+    return 0;
+}
+extern "C" int galois_b200_htod(galois_b200_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes) {
+    GB_CHECK_CTX(ctx);
+    if (bytes == 0) return 0;
+    if (!dst_dev || !src_host) return gb_fail(ctx, GALOIS_B200_E_BADARG, "htod: null pointer");
+    GB_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return 0;
+}
+static int check_dev_status(galois_b200_ctx* ctx) {
+    int st = 0;
+    GB_CUDA(ctx, cudaMemcpyAsync(&st, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (st != 0) {
+        GB_CUDA(ctx, cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream));
+        return gb_fail(ctx, st, "a bounded device-side wait ran out (status %d)", st);
+    }
+    return 0;
+}
+extern "C" int galois_b200_dtoh(galois_b200_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes) {
+    GB_CHECK_CTX(ctx);
+    if (bytes == 0) return 0;
+    if (!dst_host || !src_dev) return gb_fail(ctx, GALOIS_B200_E_BADARG, "dtoh: null pointer");
+    GB_CUDA(ctx, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+extern "C" int galois_b200_synchronize(galois_b200_ctx* ctx) {
+    GB_CHECK_CTX(ctx);
+    return check_dev_status(ctx);
+}
+
+// ------------------------------------------------------------------ Q4_0 mat-mul
+static int validate_mul_mat(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const void* x, const galois_dim* xd,
+                            const void* dst, const galois_dim* dd) {
+    if (!wd || !xd || !dd) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0: null dim");
+    const int64_t K = wd->ne[0], N = wd->ne[1];
+    for (int i = 0; i < 4; i++)
+        if (wd->ne[i] < 0 || xd->ne[i] < 0 || dd->ne[i] < 0) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0: negative extent");
+    if (K != xd->ne[0]) return gb_fail(ctx, GALOIS_B200_E_SHAPE, "mul_mat_q4_0: K mismatch (%lld vs %lld)", (long long)K, (long long)xd->ne[0]);
+    // BlockQ8_0::from_f32 panics when K % 32 != 0 (src/ggml_quants.rs:738-740); assert!(ne00 % 32 == 0) (src/op.rs:1537)
+    if (K % GB_QK != 0) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0: %lld is not divisible by 32", (long long)K);
+    if (!(dd->ne[0] == N && dd->ne[1] == xd->ne[1] && dd->ne[2] == xd->ne[2] && dd->ne[3] == xd->ne[3]))
+        return gb_fail(ctx, GALOIS_B200_E_SHAPE, "mul_mat_q4_0: dst shape does not match (src/op.rs:1422-1425)");
+    if (wd->nb[0] != 1 || xd->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: permuted src0 or src1 not supported (src/op.rs:1428-1429)");
+    if (!(dd->nb[0] == 1 && dd->nb[0] <= dd->nb[1] && dd->nb[1] <= dd->nb[2] && dd->nb[2] <= dd->nb[3]))
+        return gb_fail(ctx, GALOIS_B200_E_DST, "mul_mat_q4_0: dst cannot be transposed or permuted (src/op.rs:1432-1435)");
+    if (wd->ne[2] < 1 || wd->ne[3] < 1 || xd->ne[2] % wd->ne[2] != 0 || xd->ne[3] % wd->ne[3] != 0)
+        return gb_fail(ctx, GALOIS_B200_E_BROADCAST, "mul_mat_q4_0: src0 dims 2/3 must divide src1 dims 2/3 (src/op.rs:1473-1474)");
+    if (N == 0 || K == 0 || xd->ne[1] * xd->ne[2] * xd->ne[3] == 0) return 0;  // nothing is read
+    if (!w || !x || !dst) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0: null pointer");
+    if ((uintptr_t)w % 2 != 0) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: weight blocks must be 2-byte aligned");
+    if ((uintptr_t)x % 4 != 0 || (uintptr_t)dst % 4 != 0) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: f32 operands must be 4-byte aligned");
+    if (xd->ne[2] * xd->ne[3] > 65535) return gb_fail(ctx, GALOIS_B200_E_SHAPE, "mul_mat_q4_0: more than 65535 batched matrices");
+    return 0;
+}
+
+extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
+                                            const galois_dim* xd, float* dst, const galois_dim* dd) {
+    GB_CHECK_CTX(ctx);
+    int rc = validate_mul_mat(ctx, w, wd, x, xd, dst, dd);
+    if (rc) return rc;
+    const int64_t K = wd->ne[0], N = wd->ne[1];
+    const int64_t nrows = xd->ne[1] * xd->ne[2] * xd->ne[3];
+    if (N == 0 || nrows == 0) return 0;
+    if (K == 0) {
+        // an empty contraction: vec_dot over zero blocks is 0.0
+        if (!dst) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0: null pointer");
+        if (!gb_is_contiguous(dd)) return gb_fail(ctx, GALOIS_B200_E_DST, "mul_mat_q4_0: K == 0 needs a contiguous dst");
+        GB_CUDA(ctx, cudaMemsetAsync(dst, 0, (size_t)gb_nelements(dd) * sizeof(float), ctx->stream));
+        return 0;
+    }
+    const bool tc_ok = gb_mm_tc_supported(ctx, w, wd, xd, dd);
+    const bool bulk_ok = gb_mmv_bulk_supported(ctx, w, wd, xd, dd);
+    int variant = ctx->variant;
+    if (variant == 0) variant = (tc_ok && xd->ne[1] >= GB_TC_MIN_BATCH) ? 3 : (bulk_ok ? 2 : 1);
+    if (variant == 2 && !bulk_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: bulk-copy variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned base, batch <= 8");
+    if (variant == 3 && !tc_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: tensor-core variant needs 2-D contiguous weights, K %% 128 == 0, 16-byte aligned base");
+
+    void* scratch = nullptr;
+    size_t need = gb_q8_soa_bytes(K, nrows);
+    if (variant == 3) need += gb_mm_tc_scratch_bytes(wd, xd);
+    rc = gb_scratch(ctx, need, &scratch);
+    if (rc) return rc;
+    gb_q8_soa xq;
+    rc = gb_quantize_q8_soa(ctx, x, xd, scratch, &xq);
+    if (rc) return rc;
+    const bool prof = ctx->profiling && ctx->prof_n < GB_PROF_MAX;
+    if (prof) GB_CUDA(ctx, cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream));
+    if (variant == 3)
+        rc = gb_mm_q4_0_tc(ctx, w, wd, xq, xd, dst, dd, (uint8_t*)scratch + gb_q8_soa_bytes(K, nrows));
+    else if (variant == 2)
+        rc = gb_mmv_q4_0_bulk(ctx, w, wd, xq, xd, dst, dd);
+    else
+        rc = gb_mmv_q4_0_direct(ctx, w, wd, xq, xd, dst, dd);
+    if (prof) {
+        GB_CUDA(ctx, cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n + 1], ctx->stream));
+        ctx->prof_n++;
+    }
+    return rc;
+}
+
+extern "C" int galois_b200_profile_enable(galois_b200_ctx* ctx, int on) {
+    GB_CHECK_CTX(ctx);
+    if (on && !ctx->prof_ev) {
+        ctx->prof_ev = (cudaEvent_t*)calloc(2 * GB_PROF_MAX, sizeof(cudaEvent_t));
+        if (!ctx->prof_ev) return gb_fail(ctx, GALOIS_B200_E_NOMEM, "profile_enable: out of host memory");
+        for (int i = 0; i < 2 * GB_PROF_MAX; i++) GB_CUDA(ctx, cudaEventCreate(&ctx->prof_ev[i]));
+    }
+    ctx->profiling = on ? 1 : 0;
+    ctx->prof_n = 0;
+    return 0;
+}
+
+extern "C" int galois_b200_profile_read(galois_b200_ctx* ctx, double* total_ms, int64_t* launches) {
+    GB_CHECK_CTX(ctx);
+    if (!total_ms || !launches) return gb_fail(ctx, GALOIS_B200_E_BADARG, "profile_read: null pointer");
+    *total_ms = 0.0;
+    *launches = 0;
+    if (!ctx->prof_ev) return 0;
+    GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int i = 0; i < ctx->prof_n; i++) {
+        float ms = 0.0f;
+        GB_CUDA(ctx, cudaEventElapsedTime(&ms, ctx->prof_ev[2 * i], ctx->prof_ev[2 * i + 1]));
+        *total_ms += ms;
+    }
+    *launches = ctx->prof_n;
+    ctx->prof_n = 0;
+    return 0;
+}
+
+extern "C" int galois_b200_mul_mat_q4_0_f32_host(galois_b200_ctx* ctx, const void* w, const galois_dim* wd,
+                                                 const float* x_host, const galois_dim* xd, float* dst_host,
+                                                 const galois_dim* dd) {
+    GB_CHECK_CTX(ctx);
+    if (!xd || !dd || !x_host || !dst_host) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_host: null pointer");
+    if (!gb_is_contiguous(xd) || !gb_is_contiguous(dd)) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0_host: host buffers must be contiguous");
+    const size_t xbytes = (size_t)gb_nelements(xd) * sizeof(float), dbytes = (size_t)gb_nelements(dd) * sizeof(float);
+    // device staging for x and dst, kept across calls
+    if (xbytes + dbytes > ctx->io_bytes) {
+        GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->io) GB_CUDA(ctx, cudaFree(ctx->io));
+        ctx->io = nullptr;
+        ctx->io_bytes = 0;
+        size_t want = ((xbytes + 255) & ~(size_t)255) + dbytes + 256;
+        cudaError_t e = cudaMalloc(&ctx->io, want);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            return gb_fail(ctx, GALOIS_B200_E_NOMEM, "mul_mat_q4_0_host: cudaMalloc(%zu): %s", want, cudaGetErrorString(e));
+        }
+        ctx->io_bytes = want;
+    }
+    float* xdev = (float*)ctx->io;
+    float* ddev = (float*)((uint8_t*)ctx->io + ((xbytes + 255) & ~(size_t)255));
+    if (xbytes) GB_CUDA(ctx, cudaMemcpyAsync(xdev, x_host, xbytes, cudaMemcpyHostToDevice, ctx->stream));
+    int rc = galois_b200_mul_mat_q4_0_f32(ctx, w, wd, xdev, xd, ddev, dd);
+    if (rc) return rc;
+    if (dbytes) GB_CUDA(ctx, cudaMemcpyAsync(dst_host, ddev, dbytes, cudaMemcpyDeviceToHost, ctx->stream));
+    GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
+extern "C" int galois_b200_shard_rows(int64_t n, int world, int rank, int64_t* row0, int64_t* nrows) {
+    if (!row0 || !nrows || world < 1 || rank < 0 || rank >= world || n < 0) return GALOIS_B200_E_BADARG;
+    // groups of 32 rows are dealt as evenly as possible; the last rank takes the ragged tail
+    const int64_t groups = (n + 31) / 32;
+    const int64_t base = groups / world, extra = groups % world;
+    const int64_t g0 = rank * base + (rank < extra ? rank : extra);
+    const int64_t g1 = g0 + base + (rank < extra ? 1 : 0);
+    int64_t r0 = g0 * 32, r1 = g1 * 32;
+    if (r0 > n) r0 = n;
+    if (r1 > n) r1 = n;
+    *row0 = r0;
+    *nrows = r1 - r0;
+    return 0;
+}

@@ -1,0 +1,99 @@
+// Shared declarations for the galois_b200 CUDA sources (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/galois_b200.h"
+
+#define GB_QK 32
+#define GB_Q4_BYTES 18
+#define GB_Q8_BYTES 34
+#define GB_PROF_MAX 4096
+
+// Context behind the opaque galois_b200_ctx handle.
+struct galois_b200_ctx {
+    int ordinal;
+    cudaStream_t stream;
+    int sm_count;
+    int variant;           // forced Q4_0 mat-mul variant (0 = automatic)
+    int64_t launches;      // kernels launched through this context
+    // f16 look-up tables (65 536 entries each), device copies
+    uint16_t* exp_lut;
+    uint16_t* silu_lut;
+    // scratch arena for quantised activations and other op-private temporaries
+    void* scratch;
+    size_t scratch_bytes;
+    // device word a kernel sets when one of its bounded waits runs out (0 = none)
+    int* dev_status;
+    // optional event pairs around the mat-mul kernel (see galois_b200_profile_enable)
+    int profiling;
+    int prof_n;
+    cudaEvent_t* prof_ev;  // 2 * GB_PROF_MAX events
+    // device staging for the entry points that take host buffers
+    void* io;
+    size_t io_bytes;
+    char err[512];
+};
+
+// Records `msg` as the context's last error and returns `code`.
+int gb_fail(galois_b200_ctx* ctx, int code, const char* fmt, ...);
+// Returns a pointer to at least `bytes` of scratch (grows the arena with
+// cudaMalloc when needed; growth synchronises the stream first).
+int gb_scratch(galois_b200_ctx* ctx, size_t bytes, void** out);
+
+#define GB_CHECK_CTX(ctx)              \
+    do {                               \
+        if ((ctx) == nullptr) return GALOIS_B200_E_STATE; \
+    } while (0)
+
+#define GB_CUDA(ctx, expr)                                                                   \
+    do {                                                                                     \
+        cudaError_t _e = (expr);                                                             \
+        if (_e != cudaSuccess) return gb_fail((ctx), (int)_e, "%s: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+// Launch-status check: picks up configuration errors without synchronising.
+#define GB_LAUNCHED(ctx, name)                                                                 \
+    do {                                                                                       \
+        cudaError_t _e = cudaGetLastError();                                                   \
+        if (_e != cudaSuccess) return gb_fail((ctx), (int)_e, "launch of %s: %s", name, cudaGetErrorString(_e)); \
+        (ctx)->launches++;                                                                     \
+    } while (0)
+
+static inline int64_t gb_nelements(const galois_dim* d) { return d->ne[0] * d->ne[1] * d->ne[2] * d->ne[3]; }
+static inline bool gb_is_contiguous(const galois_dim* d, int64_t block = 1) {
+    return d->nb[0] == 1 && d->nb[1] == d->ne[0] / block && d->nb[2] == d->nb[1] * d->ne[1] &&
+           d->nb[3] == d->nb[2] * d->ne[2];
+}
+static inline bool gb_same_shape(const galois_dim* a, const galois_dim* b) {
+    return a->ne[0] == b->ne[0] && a->ne[1] == b->ne[1] && a->ne[2] == b->ne[2] && a->ne[3] == b->ne[3];
+}
+
+// Internal activation format produced by the quantiser for the mat-mul kernels
+// (structure of arrays; same values as the 34-byte Q8_0 blocks):
+//   qs : int8  [rows][K]          16-byte aligned rows
+//   ds : float2[rows][K/32]       .x = f32(f16(d)), .y = bit pattern of the int32 sum of the block's 32 quants
+struct gb_q8_soa {
+    const int8_t* qs;
+    const float2* ds;
+};
+
+// ------------------------------------------------------------------ device helpers
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float gb_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float gb_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+#endif  // __CUDACC__

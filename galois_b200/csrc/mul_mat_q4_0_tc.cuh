@@ -1,0 +1,14 @@
+// Internal interface of the large-batch (prefill) Q4_0 mat-mul on the
+// tcgen05 int8 tensor-core path (mul_mat_q4_0_tc.cu).
+#pragma once
+#include "common.cuh"
+
+// Batches at least this large take the tensor-core path when it supports the shape.
+#define GB_TC_MIN_BATCH 32
+
+int gb_mm_tc_init(galois_b200_ctx* ctx);
+bool gb_mm_tc_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const galois_dim* xd,
+                        const galois_dim* dd);
+size_t gb_mm_tc_scratch_bytes(const galois_dim* wd, const galois_dim* xd);
+int gb_mm_q4_0_tc(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const gb_q8_soa& xq, const galois_dim* xd,
+                  float* dst, const galois_dim* dd, void* scratch);

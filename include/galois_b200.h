@@ -1,0 +1,208 @@
+/* galois_b200.h — C ABI of the B200 (sm_100a) implementation of galois's Q4_0
+ * mat-mul and attention-chain GPU ops.
+ *
+ * This is the boundary a galois maintainer binds from Rust (`extern "C"`) in
+ * place of the cudarc PTX-by-name launches in src/cuda.rs.  Each entry point
+ * names the reference interface it replaces (file:line inside the galois
+ * repository).
+ *
+ * Conventions
+ *  - Every data pointer is a DEVICE pointer unless its name ends in `_host`.
+ *  - Buffers are owned by the caller; nothing passed in is retained or freed.
+ *  - `galois_dim` is a copy of galois `Dim` (src/shape.rs:29-34): ggml order
+ *    (index 0 is the fastest dimension), strides counted in ELEMENTS — in
+ *    18-byte blocks for Q4_0 tensors (src/shape.rs:422-430).
+ *  - All work is enqueued on the context's stream (the stream handed to
+ *    galois_b200_init / galois_b200_set_stream) and is asynchronous; only the
+ *    `_host` entry points and galois_b200_dtoh synchronise.
+ *  - Return value: 0 = success; < 0 = GALOIS_B200_E_* below (the cases where
+ *    the reference `assert!`s, `panic!`s or hits `todo!()`); > 0 = a
+ *    cudaError_t.  galois_b200_last_error() gives the text.  No entry point
+ *    aborts, traps or blocks forever.
+ *  - One context is driven from one host thread at a time (the reference's
+ *    CudaDevice has no locking either, src/lib.rs:2262).
+ */
+#ifndef GALOIS_B200_H
+#define GALOIS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GALOIS_B200_OK 0
+#define GALOIS_B200_E_BADARG (-1)      /* null pointer, negative size, K not a multiple of 32 */
+#define GALOIS_B200_E_SHAPE (-2)       /* operand shapes do not agree */
+#define GALOIS_B200_E_LAYOUT (-3)      /* a stride pattern the op does not support */
+#define GALOIS_B200_E_DST (-4)         /* destination transposed / permuted */
+#define GALOIS_B200_E_BROADCAST (-5)   /* src0 dims 2/3 do not divide src1 dims 2/3 */
+#define GALOIS_B200_E_UNSUPPORTED (-6) /* rope modes the reference leaves as todo!() */
+#define GALOIS_B200_E_NOMEM (-8)       /* scratch arena could not be grown */
+#define GALOIS_B200_E_TIMEOUT (-9)     /* a bounded device-side wait ran out */
+#define GALOIS_B200_E_STATE (-10)      /* context not initialised for this call */
+
+typedef struct galois_b200_ctx galois_b200_ctx;
+
+typedef struct {
+    int32_t n_dims;
+    int64_t ne[4]; /* extent per dimension, ne[0] fastest */
+    int64_t nb[4]; /* stride per dimension in elements (blocks for Q4_0) */
+} galois_dim;
+
+/* Size in bytes of one 32-element block. */
+#define GALOIS_B200_QK 32
+#define GALOIS_B200_Q4_0_BYTES 18 /* { f16 d; u8 qs[16] }  src/ggml_quants.rs:140-145 */
+#define GALOIS_B200_Q8_0_BYTES 34 /* { f16 d; i8 qs[32] }  src/ggml_quants.rs:721-726 */
+
+/* ---- device bring-up --------------------------------------------------- */
+
+/* Replaces CudaDevice::new (src/cuda.rs:221-229) + init_cuda_function
+ * (src/kernels.rs:4-22).  Makes `ordinal` current, builds the f16 exp / silu
+ * tables the reference keeps in GLOBAL_CPU_DEVICE_CACHE (src/op.rs:227-252)
+ * and uploads them, allocates the scratch arena.  `cu_stream` is the
+ * CUstream / cudaStream_t all later calls enqueue on (NULL = legacy default
+ * stream). */
+int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** out);
+int galois_b200_destroy(galois_b200_ctx* ctx);
+int galois_b200_set_stream(galois_b200_ctx* ctx, void* cu_stream);
+/* Text of the last non-zero status returned on this context ("" if none).
+ * With ctx == NULL returns the text of the last failed galois_b200_init. */
+const char* galois_b200_last_error(galois_b200_ctx* ctx);
+/* Number of kernels this context has launched so far (for benches). */
+int64_t galois_b200_launch_count(galois_b200_ctx* ctx);
+/* Selects among equivalent implementations of the Q4_0 mat-mul:
+ * 0 = automatic, 1 = generic direct-load kernel, 2 = bulk-copy pipelined GEMV,
+ * 3 = tensor-core (tcgen05) GEMM.  Unsupported shapes for a forced variant
+ * return GALOIS_B200_E_LAYOUT. */
+int galois_b200_set_mul_mat_variant(galois_b200_ctx* ctx, int variant);
+
+/* Kernel timing for benches.  While enabled, every galois_b200_mul_mat_q4_0_f32
+ * call brackets its mat-mul kernel (not the activation quantiser) with CUDA
+ * events on the context's stream; galois_b200_profile_read synchronises, adds
+ * up the bracketed durations since the last read and returns them.  Not to be
+ * enabled during stream capture.  At most 4096 calls between reads are kept. */
+int galois_b200_profile_enable(galois_b200_ctx* ctx, int on);
+int galois_b200_profile_read(galois_b200_ctx* ctx, double* total_ms, int64_t* launches);
+
+/* Device memory and copies: replace CudaDevice::from_cpu_storage /
+ * htod_sync_copy (src/cuda.rs:231-295) and Tensor::to_cpu_tensor's
+ * dtoh_sync_copy_into (src/lib.rs:2279-2341).  htod is asynchronous on the
+ * context's stream when `src_host` is pinned; dtoh synchronises the stream. */
+int galois_b200_alloc(galois_b200_ctx* ctx, size_t bytes, void** out_dev);
+int galois_b200_free(galois_b200_ctx* ctx, void* dev);
+int galois_b200_htod(galois_b200_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+int galois_b200_dtoh(galois_b200_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+int galois_b200_synchronize(galois_b200_ctx* ctx);
+
+/* ---- quantisation ------------------------------------------------------ */
+
+/* <BlockQ8_0 as QuantType>::from_f32 (src/ggml_quants.rs:736-764), one call
+ * per activation row in MatMul::f_q_f32_f32 (src/op.rs:1409-1420); on the GPU
+ * it replaces convert_to_q8 / quantize_q8_1 (src/cuda.rs:835-863,
+ * matmul.cu:133-174).  x: [nrows][k] f32 with row stride `x_row_stride`
+ * elements; y: nrows * k/32 blocks of 34 bytes, bit-identical to the CPU. */
+int galois_b200_quantize_q8_0(galois_b200_ctx* ctx, const float* x, int64_t x_row_stride, void* y, int64_t k,
+                              int64_t nrows);
+
+/* Test hook: the per-block integer sums  sum_j (q4_j - 8) * q8_j  of one
+ * weight row against one activation row (the quantity inside
+ * BlockQ4_0::vec_dot_q8_0 / vec_dot_unopt, src/ggml_quants.rs:156-191) as the
+ * mat-mul kernels compute them.  w: nb Q4_0 blocks; xq: nb Q8_0 blocks in the
+ * 34-byte format; out: nb int32. */
+int galois_b200_block_isums_q4_0_q8_0(galois_b200_ctx* ctx, const void* w, const void* xq, int64_t nb,
+                                      int32_t* out);
+
+/* ---- mat-mul ----------------------------------------------------------- */
+
+/* CudaMap2::f_q_f32_f32 for CudaMatMul (src/cuda.rs:436-447, impl :994-1139),
+ * numerics of MatMul::f_q_f32_f32::<BlockQ4_0> (src/op.rs:1383-1598):
+ * dst[i3][i2][i1][n] = vec_dot(W[i3/r3][i2/r2][n][:], Q8_0(x[i3][i2][i1][:])).
+ * w: Q4_0 blocks, wd = {K, N, ne02, ne03}; x: f32 {K, B, ne12, ne13};
+ * dst: f32 {N, B, ne12, ne13}. */
+int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
+                                 const galois_dim* xd, float* dst, const galois_dim* dd);
+
+/* Same op with the activation and result in HOST memory: upload x, run,
+ * download dst, synchronise.  This is the sequence Tensor::from_vec(.., Gpu)
+ * -> galois_matmul -> to_cpu_tensor (src/lib.rs:2467-2523, src/op.rs:3093,
+ * src/lib.rs:2279-2341) performs around a resident weight tensor.  x_host and
+ * dst_host are contiguous in the layout xd / dd describe. */
+int galois_b200_mul_mat_q4_0_f32_host(galois_b200_ctx* ctx, const void* w, const galois_dim* wd,
+                                      const float* x_host, const galois_dim* xd, float* dst_host,
+                                      const galois_dim* dd);
+
+/* CudaMap2::f_x_y_y for CudaMatMul, F16 x F32 -> F32 (src/cuda.rs:404-418,
+ * impl :881-992, cuBLAS :698-782), numerics of
+ * MatMul::f_q_f32_f32::<f16> + vec_dot_f16 (src/ggml_quants.rs:113-135,
+ * src/op.rs:137-196): the f32 operand is rounded to f16, products and sums
+ * are f32. */
+int galois_b200_mul_mat_f16_f32(galois_b200_ctx* ctx, const void* a_f16, const galois_dim* ad, const float* x,
+                                const galois_dim* xd, float* dst, const galois_dim* dd);
+
+/* ---- attention-chain row ops ------------------------------------------- */
+
+/* CudaMap::f for CudaRmsNorm{eps} (src/cuda.rs:1142-1181, rms_norm.cu:13-49);
+ * numerics of f32::rms_norm (src/lib.rs:594-604, src/op.rs:1263-1314). */
+int galois_b200_rms_norm_f32(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, float* y,
+                             const galois_dim* yd, float eps);
+
+/* CudaMap2::f_x_y_x for CudaRope{..} (src/cuda.rs:1246-1356, rope.cu:3-28);
+ * numerics of RopeCustom::f_x_y_x (src/op.rs:2649-2756): mode 0 only, theta
+ * advanced by repeated multiplication. */
+int galois_b200_rope_f32(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, const int32_t* pos,
+                         const galois_dim* pd, float* y, const galois_dim* yd, int n_dims, int mode, int n_ctx,
+                         float freq_base, float freq_scale, float xpos_base, int xpos_down);
+
+/* CudaMap::f for CudaSoftMax (src/cuda.rs:1640-1663, softmax.cu:3-48);
+ * numerics of f32::softmax (src/lib.rs:564-592): f16 exp table. */
+int galois_b200_soft_max_f32(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, float* y,
+                             const galois_dim* yd);
+
+/* Fused scale + causal mask + soft_max.  No single counterpart in the
+ * reference: equals galois_scale (src/op.rs:3258-3279) by `scale`, then
+ * treating column c > pos[i2] as -inf, then galois_soft_max.  x, y:
+ * {columns, heads, tokens, 1}; pos: i32 per token, or NULL for no mask. */
+int galois_b200_soft_max_ext_f32(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, float* y,
+                                 const galois_dim* yd, float scale, const int32_t* pos);
+
+/* CudaMap::f for CudaSilu (src/cuda.rs:1665-1688, unary.cu:1-10); numerics of
+ * f32::vec_silu (src/lib.rs:543-549): f16 silu table. */
+int galois_b200_silu_f32(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, float* y,
+                         const galois_dim* yd);
+
+/* CudaMap2::f for CudaMul / CudaAdd (src/cuda.rs:1188-1244, mul.cu, add.cu);
+ * numerics of Mul::f / Add::f (src/op.rs:318-611): src1 broadcast by modulo
+ * over dims 1..3. */
+int galois_b200_mul_f32(galois_b200_ctx* ctx, const float* a, const galois_dim* ad, const float* b,
+                        const galois_dim* bd, float* dst, const galois_dim* dd);
+int galois_b200_add_f32(galois_b200_ctx* ctx, const float* a, const galois_dim* ad, const float* b,
+                        const galois_dim* bd, float* dst, const galois_dim* dd);
+
+/* CudaMap2::f_g_c for CudaScale (src/cuda.rs:1597-1638, scale.cu:1-11): the
+ * scalar lives on the host, as in the (Gpu, Cpu, Gpu) arm of galois_scale
+ * (src/op.rs:3271-3273). */
+int galois_b200_scale_f32(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, float scale_host, float* y,
+                          const galois_dim* yd);
+
+/* CudaMap::f / f_x_y for CudaCpy (src/cuda.rs:1382-1595, cpy.cu:79-156);
+ * numerics of Cpy::f / Cpy::f_x_y (src/op.rs:1928-2090): the k-th source
+ * element in ggml order lands on the k-th destination element in ggml order;
+ * f32 -> f16 rounds to nearest even.  This is the KV-cache append. */
+int galois_b200_cpy_f32_f32(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, float* y,
+                            const galois_dim* yd);
+int galois_b200_cpy_f32_f16(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, void* y_f16,
+                            const galois_dim* yd);
+
+/* ---- row sharding across GPUs ------------------------------------------ */
+
+/* Row range [*row0, *row0 + *nrows) of an N-row weight owned by `rank` of
+ * `world`.  The reference has no multi-GPU path; rows of a mat-mul are
+ * independent (src/op.rs:1540-1543).  Boundaries are multiples of 32 rows. */
+int galois_b200_shard_rows(int64_t n, int world, int rank, int64_t* row0, int64_t* nrows);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GALOIS_B200_H */

@@ -1,0 +1,383 @@
+"""GPU parity tests: every op runs through the C ABI (via the galois_* mirror) and is
+compared with the CPU oracle on the same seeded inputs.
+
+Bars: bit-exact for Q8_0 quantisation, per-block integer sums, f32->f16 copies and
+the table-driven silu; relative L2 <= 1e-4 and max-abs <= 1e-3 for f32 outputs
+whose summation order differs from the CPU's."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gb():
+    import galois_b200
+
+    return galois_b200
+
+
+def _gpu(gb, dev, arr, dtype=None):
+    return gb.Tensor.from_numpy(arr, dtype or gb.GGmlType.F32, gb.Device.Gpu(dev))
+
+
+def _q4(gb, dev, wbytes, n, k):
+    return gb.Tensor.from_raw(wbytes, (k, n), gb.GGmlType.Q4_0, gb.Device.Gpu(dev))
+
+
+# ------------------------------------------------------------------ quantiser
+@pytest.mark.parametrize("rows,k", [(1, 32), (1, 4096), (3, 96), (8, 11008), (5, 4096 + 32), (33, 256)])
+def test_quantize_q8_0_bit_exact(gb, dev, oracle, rows, k):
+    import torch
+
+    x = oracle.fill_normal(rows * k, 1000 + rows + k).reshape(rows, k)
+    if rows >= 3:
+        x[1, :32] = 0.0          # zero block
+        x[2, 32:64] *= 1e-20     # tiny block
+        x[0, 5] = 1e30           # huge outlier
+    want = oracle.quantize_q8_0(x)
+    out = torch.zeros(rows * (k // 32) * 34, dtype=torch.uint8, device=dev.torch_device)
+    gb.quantize_q8_0(_gpu(gb, dev, x), out)
+    dev.synchronize()
+    assert np.array_equal(out.cpu().numpy().reshape(rows, -1), want)
+
+
+def test_quantize_q8_0_golden_and_edges(gb, dev, oracle, golden):
+    import torch
+
+    x = golden["q8_x"]
+    out = torch.zeros(golden["q8_bytes"].size, dtype=torch.uint8, device=dev.torch_device)
+    gb.quantize_q8_0(_gpu(gb, dev, x), out)
+    dev.synchronize()
+    assert np.array_equal(out.cpu().numpy().reshape(4, -1), golden["q8_bytes"])
+    # subnormal scale: saturating cast, as Rust's `as i8`
+    e = np.zeros((1, 32), np.float32)
+    e[0, 0], e[0, 1] = 1e-38, -1e-38
+    out = torch.zeros(34, dtype=torch.uint8, device=dev.torch_device)
+    gb.quantize_q8_0(_gpu(gb, dev, e), out)
+    dev.synchronize()
+    assert np.array_equal(out.cpu().numpy()[None], oracle.quantize_q8_0(e))
+    # K not a multiple of 32: the reference panics; here an error code
+    bad = _gpu(gb, dev, np.zeros((1, 40), np.float32))
+    with pytest.raises(gb.GError) as ei:
+        gb.quantize_q8_0(bad, out)
+    assert ei.value.code == -1
+    # empty input is a no-op
+    rc = gb.lib.galois_b200_quantize_q8_0(dev.ctx, None, 0, None, 0, 0)
+    assert rc == 0
+
+
+# ------------------------------------------------------------------ integer block sums
+@pytest.mark.parametrize("k", [32, 96, 4096, 11008])
+def test_block_isums_bit_exact(gb, dev, oracle, k):
+    import torch
+
+    w = oracle.quantize_q4_0(oracle.fill_normal(k, 50 + k, 0, 0.02)[None])[0]
+    xq = oracle.quantize_q8_0(oracle.fill_normal(k, 60 + k)[None])[0]
+    want = oracle.block_isums(w, xq)
+    wd = torch.from_numpy(w.copy()).to(dev.torch_device)
+    xd = torch.from_numpy(xq.copy()).to(dev.torch_device)
+    out = torch.zeros(k // 32, dtype=torch.int32, device=dev.torch_device)
+    rc = gb.lib.galois_b200_block_isums_q4_0_q8_0(dev.ctx, C.c_void_p(wd.data_ptr()), C.c_void_p(xd.data_ptr()), k // 32,
+                                                  C.c_void_p(out.data_ptr()))
+    assert rc == 0
+    dev.synchronize()
+    assert np.array_equal(out.cpu().numpy(), want)
+
+
+def test_block_isums_golden_extremes(gb, dev, golden):
+    import torch
+
+    for xi, xr in enumerate((0, 2)):
+        xq = torch.from_numpy(golden["q8_bytes"][xr][: 3 * 34].copy()).to(dev.torch_device)
+        for r in range(5):
+            w = torch.from_numpy(golden["dot_w"][r].copy()).to(dev.torch_device)
+            out = torch.zeros(3, dtype=torch.int32, device=dev.torch_device)
+            assert gb.lib.galois_b200_block_isums_q4_0_q8_0(dev.ctx, C.c_void_p(w.data_ptr()), C.c_void_p(xq.data_ptr()), 3,
+                                                            C.c_void_p(out.data_ptr())) == 0
+            dev.synchronize()
+            assert np.array_equal(out.cpu().numpy(), golden["dot_isums"][xi, r])
+
+
+# ------------------------------------------------------------------ Q4_0 mat-mul
+def _mul_mat_case(gb, dev, oracle, n, k, b, seed, variant):
+    w = oracle.quantize_q4_0(oracle.fill_normal(n * k, seed, 0, 0.02).reshape(n, k))
+    x = oracle.fill_normal(b * k, seed + 1).reshape(b, k)
+    want = oracle.mul_mat_q4_0(w, x)
+    dst = gb.Tensor.zeros((n, b), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    dev.set_mul_mat_variant(variant)
+    try:
+        gb.galois_matmul(_q4(gb, dev, w, n, k), _gpu(gb, dev, x), dst)
+        got = dst.to_numpy()
+    finally:
+        dev.set_mul_mat_variant(0)
+    assert_close(got, want)
+
+
+# BASELINE config 1 (4096x4096, B=1) and odd shapes; variant 1 = direct kernel
+@pytest.mark.parametrize("n,k,b", [(4096, 4096, 1), (70, 96, 5), (1, 32, 1), (33, 4096 + 32, 3), (257, 352, 8),
+                                   (100, 256, 16), (64, 64, 33), (5, 11008, 2)])
+def test_mul_mat_q4_0_direct(gb, dev, oracle, n, k, b):
+    _mul_mat_case(gb, dev, oracle, n, k, b, 7000 + n + k + b, 1)
+
+
+# variant 2 = bulk-copy pipelined GEMV (K % 256 == 0, batch <= 8)
+@pytest.mark.parametrize("n,k,b", [(4096, 4096, 1), (11008, 4096, 1), (4096, 11008, 1), (11008, 4096, 4),
+                                   (4096, 11008, 8), (1, 256, 1), (3, 256, 2), (1185, 512, 3), (2371, 4096, 5),
+                                   (149, 8192, 7), (32000, 4096, 8)])
+def test_mul_mat_q4_0_bulk(gb, dev, oracle, n, k, b):
+    _mul_mat_case(gb, dev, oracle, n, k, b, 8000 + n + k + b, 2)
+
+
+# automatic dispatch over the BASELINE shapes (configs 2, 3, 5) incl. large batches
+@pytest.mark.parametrize("n,k,b", [(11008, 4096, 8), (4096, 4096, 512), (32000, 4096, 16), (28672, 8192, 16),
+                                   (4096, 4096, 100), (300, 4096, 37)])
+def test_mul_mat_q4_0_auto(gb, dev, oracle, n, k, b):
+    _mul_mat_case(gb, dev, oracle, n, k, b, 9000 + n + k + b, 0)
+
+
+def test_mul_mat_q4_0_linearity_full_size(gb, dev, oracle):
+    """Size-independent property at config-2 size: doubling the activations (exact in
+    f32 and in Q8_0: d doubles, quants unchanged) doubles the output exactly."""
+    n, k = 11008, 4096
+    w = oracle.quantize_q4_0(oracle.fill_normal(n * k, 123, 0, 0.02).reshape(n, k))
+    x = oracle.fill_normal(4 * k, 124).reshape(4, k)
+    wt = _q4(gb, dev, w, n, k)
+    y1 = gb.Tensor.zeros((n, 4), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    y2 = gb.Tensor.zeros((n, 4), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    gb.galois_matmul(wt, _gpu(gb, dev, x), y1)
+    gb.galois_matmul(wt, _gpu(gb, dev, 2.0 * x), y2)
+    assert np.array_equal(2.0 * y1.to_numpy(), y2.to_numpy())
+
+
+def test_mul_mat_q4_0_broadcast_and_strides(gb, dev, oracle):
+    O = oracle
+    k, n = 64, 40
+    w = O.quantize_q4_0(O.fill_normal(2 * n * k, 31, 0, 0.02).reshape(2 * n, k))  # ne02 = 2
+    x = O.fill_normal(4 * 3 * k, 32).reshape(4, 3, k)                            # ne12 = 4, ne11 = 3
+    want = np.empty((4, 3, n), np.float32)
+    O.mul_mat_q4_0_raw(w, O.Dim.contiguous([k, n, 2], 32), x, O.Dim.contiguous([k, 3, 4]), want, O.Dim.contiguous([n, 3, 4]))
+    wt = gb.Tensor.from_raw(w, (k, n, 2), gb.GGmlType.Q4_0, gb.Device.Gpu(dev))
+    dst = gb.Tensor.zeros((n, 3, 4), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    gb.galois_matmul(wt, _gpu(gb, dev, x), dst)
+    assert_close(dst.to_numpy(), want)
+    # padded activation rows (nb11 > K) and a padded destination (nb1 > N)
+    xp = np.zeros((3, k + 32), np.float32)
+    xp[:, :k] = x[0]
+    xt = _gpu(gb, dev, xp).view((k, 3), (1, k + 32, 3 * (k + 32), 3 * (k + 32)))
+    big = gb.Tensor.zeros((n + 8, 3), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    dv = big.view((n, 3), (1, n + 8, 3 * (n + 8), 3 * (n + 8)))
+    w0 = gb.Tensor.from_raw(w[:n], (k, n), gb.GGmlType.Q4_0, gb.Device.Gpu(dev))
+    gb.galois_matmul(w0, xt, dv)
+    got = big.to_numpy()
+    assert_close(got[:, :n], want[0])
+    assert not got[:, n:].any()
+
+
+def test_mul_mat_q4_0_errors(gb, dev, oracle):
+    G = gb.Device.Gpu(dev)
+    w = gb.Tensor.zeros((64, 8), gb.GGmlType.Q4_0, G)
+    x = gb.Tensor.zeros((64, 2), gb.GGmlType.F32, G)
+    for shape, code in (((8, 3), -2), ((9, 2), -2)):
+        with pytest.raises(gb.GError) as ei:
+            gb.galois_matmul(w, x, gb.Tensor.zeros(shape, gb.GGmlType.F32, G))
+        assert ei.value.code == code
+    with pytest.raises(gb.GError) as ei:   # K mismatch
+        gb.galois_matmul(w, gb.Tensor.zeros((32, 2), gb.GGmlType.F32, G), gb.Tensor.zeros((8, 2), gb.GGmlType.F32, G))
+    assert ei.value.code == -2
+    with pytest.raises(gb.GError) as ei:   # transposed destination
+        d = gb.Tensor.zeros((8, 2), gb.GGmlType.F32, G).view((8, 2), (2, 1, 16, 16))
+        gb.galois_matmul(w, x, d)
+    assert ei.value.code == -4
+    with pytest.raises(gb.GError) as ei:   # src0 batch does not divide src1 batch
+        w3 = gb.Tensor.zeros((64, 8, 3), gb.GGmlType.Q4_0, G)
+        gb.galois_matmul(w3, gb.Tensor.zeros((64, 2, 4), gb.GGmlType.F32, G), gb.Tensor.zeros((8, 2, 4), gb.GGmlType.F32, G))
+    assert ei.value.code == -5
+    # forced variants refuse shapes they cannot take
+    dev.set_mul_mat_variant(2)
+    try:
+        with pytest.raises(gb.GError) as ei:
+            gb.galois_matmul(w, x, gb.Tensor.zeros((8, 2), gb.GGmlType.F32, G))
+        assert ei.value.code == -3
+    finally:
+        dev.set_mul_mat_variant(0)
+    # empty batch is a no-op
+    gb.galois_matmul(w, gb.Tensor.zeros((64, 0), gb.GGmlType.F32, G), gb.Tensor.zeros((8, 0), gb.GGmlType.F32, G))
+
+
+def test_mul_mat_q4_0_host_entry(gb, dev, oracle):
+    n, k, b = 4096, 4096, 4
+    w = oracle.quantize_q4_0(oracle.fill_normal(n * k, 77, 0, 0.02).reshape(n, k))
+    x = oracle.fill_normal(b * k, 78).reshape(b, k)
+    wt = _q4(gb, dev, w, n, k)
+    out = np.zeros((b, n), np.float32)
+    xd = gb.Dim.ggml((k, b), gb.GGmlType.F32).c_struct()
+    dd = gb.Dim.ggml((n, b), gb.GGmlType.F32).c_struct()
+    for _ in range(2):
+        rc = gb.lib.galois_b200_mul_mat_q4_0_f32_host(dev.ctx, C.c_void_p(wt.data_ptr()), C.byref(wt.dim().c_struct()),
+                                                      x.ctypes.data_as(C.c_void_p), C.byref(xd),
+                                                      out.ctypes.data_as(C.c_void_p), C.byref(dd))
+        assert rc == 0, gb.lib.galois_b200_last_error(dev.ctx)
+        assert_close(out, oracle.mul_mat_q4_0(w, x))
+
+
+# ------------------------------------------------------------------ F16 mat-mul
+@pytest.mark.parametrize("h,hx,n,k,b", [(32, 32, 2048, 128, 1), (32, 32, 128, 2048, 1), (2, 4, 6, 75, 3), (1, 1, 300, 40, 5),
+                                        (4, 8, 64, 16, 2), (1, 1, 9, 8, 1)])
+def test_mul_mat_f16(gb, dev, oracle, h, hx, n, k, b):
+    rng = np.random.default_rng(h * 1000 + n + k)
+    a = rng.standard_normal((h, n, k)).astype(np.float16)
+    x = oracle.fill_normal(hx * b * k, 900 + n + k).reshape(hx, b, k)
+    want = oracle.mul_mat_f16(a.view(np.uint16), x)
+    at = _gpu(gb, dev, a, gb.GGmlType.F16)
+    dst = gb.Tensor.zeros((n, b, hx), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    gb.galois_matmul(at, _gpu(gb, dev, x), dst)
+    assert_close(dst.to_numpy().reshape(hx, b, n), want)
+
+
+# ------------------------------------------------------------------ row ops
+@pytest.mark.parametrize("rows,k", [(1, 4096), (3, 70), (2, 20), (4, 11008), (1, 32), (5, 1000)])
+def test_rms_norm(gb, dev, oracle, rows, k):
+    x = oracle.fill_normal(rows * k, 300 + k).reshape(rows, k)
+    y = gb.Tensor.zeros((k, rows), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    gb.galois_rms_norm(_gpu(gb, dev, x), y, 1e-6)
+    assert_close(y.to_numpy(), oracle.rms_norm(x, 1e-6))
+
+
+def test_rms_norm_golden_and_inplace(gb, dev, golden):
+    for key, eps in (("rms_a", 1e-6), ("rms_b", 1e-5)):
+        x = golden[key + "_x"][None]
+        t = _gpu(gb, dev, x)
+        gb.galois_rms_norm(t, t, eps)
+        assert_close(t.to_numpy()[0], golden[key + "_y"], rel_l2=1e-6, max_abs=1e-6)
+
+
+@pytest.mark.parametrize("toks,heads,hd,pos0", [(1, 32, 128, 2047), (3, 2, 8, 0), (5, 4, 64, 100), (2, 1, 256, 4000)])
+def test_rope(gb, dev, oracle, toks, heads, hd, pos0):
+    x = oracle.fill_normal(toks * heads * hd, 400 + hd).reshape(toks, heads, hd)
+    pos = (pos0 + np.arange(toks) * 7).astype(np.int32)
+    want = oracle.rope(x, pos, hd)
+    y = gb.Tensor.zeros((hd, heads, toks), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    gb.galois_rope_custom(gb.RopeCustomOption(n_dims=hd), _gpu(gb, dev, x), _gpu(gb, dev, pos, gb.GGmlType.I32), y)
+    assert_close(y.to_numpy(), want, rel_l2=1e-5, max_abs=1e-5)
+
+
+def test_rope_options_and_errors(gb, dev, oracle, golden):
+    G = gb.Device.Gpu(dev)
+    x, pos = golden["rope_x"], golden["rope_pos"]
+    y = gb.Tensor.zeros((8, 2, 3), gb.GGmlType.F32, G)
+    gb.galois_rope_custom(gb.RopeCustomOption(n_dims=8), _gpu(gb, dev, x), _gpu(gb, dev, pos, gb.GGmlType.I32), y)
+    assert_close(y.to_numpy(), golden["rope_y"], rel_l2=1e-6, max_abs=1e-6)
+    # freq_scale, a different base, xpos
+    for kw in (dict(freq_scale=0.5), dict(freq_base=500000.0), dict(xpos_base=512.0), dict(xpos_base=512.0, xpos_down=True)):
+        want = oracle.rope(x, pos, 8, **kw)
+        gb.galois_rope_custom(gb.RopeCustomOption(n_dims=8, **kw), _gpu(gb, dev, x), _gpu(gb, dev, pos, gb.GGmlType.I32), y)
+        assert_close(y.to_numpy(), want, rel_l2=2e-5, max_abs=2e-5)
+    for mode in (2, 4):   # todo!() in the reference
+        with pytest.raises(gb.GError) as ei:
+            gb.galois_rope_custom(gb.RopeCustomOption(n_dims=8, mode=mode), _gpu(gb, dev, x), _gpu(gb, dev, pos, gb.GGmlType.I32), y)
+        assert ei.value.code == -6
+    with pytest.raises(gb.GError):   # n_dims odd
+        gb.galois_rope_custom(gb.RopeCustomOption(n_dims=7), _gpu(gb, dev, x), _gpu(gb, dev, pos, gb.GGmlType.I32), y)
+
+
+@pytest.mark.parametrize("rows,nc", [(32, 2048), (3, 37), (1, 1), (2, 5000), (7, 1024)])
+def test_soft_max(gb, dev, oracle, rows, nc):
+    x = (oracle.fill_normal(rows * nc, 500 + nc) * 3).reshape(rows, nc)
+    if nc > 5:
+        x[0, 3] = -np.inf
+        x[-1, nc - 1] = -np.inf
+    want = oracle.soft_max(x)
+    y = gb.Tensor.zeros((nc, rows), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    gb.galois_soft_max(_gpu(gb, dev, x), y)
+    got = y.to_numpy()
+    assert_close(got, want, rel_l2=1e-5, max_abs=1e-6)
+    assert np.array_equal(got == 0, want == 0)
+
+
+def test_soft_max_golden(gb, dev, golden):
+    x = golden["softmax_x"]
+    y = gb.Tensor.zeros((37, 3), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    gb.galois_soft_max(_gpu(gb, dev, x), y)
+    assert_close(y.to_numpy(), golden["softmax_y"], rel_l2=1e-6, max_abs=1e-7)
+
+
+@pytest.mark.parametrize("toks,heads,nc", [(1, 32, 2048), (3, 4, 64), (2, 2, 37)])
+def test_soft_max_ext(gb, dev, oracle, toks, heads, nc):
+    x = (oracle.fill_normal(toks * heads * nc, 600 + nc) * 4).reshape(toks, heads, nc)
+    pos = np.array([nc - 1 - 5 * t for t in range(toks)], np.int32)
+    scale = float(1.0 / np.sqrt(np.float32(128)))
+    want = oracle.soft_max_ext(x, scale, pos)
+    y = gb.Tensor.zeros((nc, heads, toks), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    gb.galois_soft_max_ext(_gpu(gb, dev, x), y, scale, _gpu(gb, dev, pos, gb.GGmlType.I32))
+    got = y.to_numpy()
+    assert_close(got, want, rel_l2=1e-5, max_abs=1e-6)
+    for t in range(toks):
+        assert not got[t, :, pos[t] + 1:].any()
+    # without a mask it is scale + soft_max
+    gb.galois_soft_max_ext(_gpu(gb, dev, x), y, scale, None)
+    assert_close(y.to_numpy(), oracle.soft_max(oracle.scale(x, scale)), rel_l2=1e-5, max_abs=1e-6)
+
+
+@pytest.mark.parametrize("rows,nc", [(1, 11008), (3, 50), (2, 1)])
+def test_silu_bit_exact(gb, dev, oracle, rows, nc):
+    x = (oracle.fill_normal(rows * nc, 700 + nc) * 4).reshape(rows, nc)
+    y = gb.Tensor.zeros((nc, rows), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    gb.galois_unary(_gpu(gb, dev, x), y, gb.UnaryOp.Silu)
+    assert np.array_equal(y.to_numpy(), oracle.silu(x))
+    with pytest.raises(gb.GError):
+        gb.galois_unary(_gpu(gb, dev, x), y, gb.UnaryOp.Gelu)
+
+
+def test_silu_golden(gb, dev, golden):
+    y = gb.Tensor.zeros((50,), gb.GGmlType.F32, gb.Device.Gpu(dev))
+    gb.galois_unary(_gpu(gb, dev, golden["silu_x"]), y, gb.UnaryOp.Silu)
+    assert np.array_equal(y.to_numpy(), golden["silu_y"])
+
+
+def test_add_mul_scale_bit_exact(gb, dev, oracle):
+    G = gb.Device.Gpu(dev)
+    a = oracle.fill_normal(3 * 4 * 4096, 801).reshape(3, 4, 4096)
+    for bshape in ((1, 1, 4096), (1, 2, 4096), (3, 4, 4096)):
+        b = oracle.fill_normal(int(np.prod(bshape)), 802).reshape(bshape)
+        for fn, ofn in ((gb.galois_add, oracle.add), (gb.galois_mul, oracle.mul)):
+            dst = gb.Tensor.zeros((4096, 4, 3), gb.GGmlType.F32, G)
+            fn(_gpu(gb, dev, a), _gpu(gb, dev, b), dst)
+            assert np.array_equal(dst.to_numpy(), ofn(a, b))
+    s = gb.Tensor.from_numpy(np.array([0.08838835], np.float32), gb.GGmlType.F32, gb.Device.Cpu())
+    dst = gb.Tensor.zeros((4096, 4, 3), gb.GGmlType.F32, G)
+    gb.galois_scale(_gpu(gb, dev, a), s, dst)
+    assert np.array_equal(dst.to_numpy(), oracle.scale(a, 0.08838835))
+    with pytest.raises(gb.GError):   # shape mismatch
+        gb.galois_add(_gpu(gb, dev, a), _gpu(gb, dev, a), gb.Tensor.zeros((4096, 4, 2), gb.GGmlType.F32, G))
+
+
+def test_cpy_bit_exact(gb, dev, oracle):
+    G = gb.Device.Gpu(dev)
+    x = oracle.fill_normal(2 * 5 * 64, 811).reshape(2, 5, 64) * 100
+    # contiguous f32 -> f16
+    d16 = gb.Tensor.zeros((64, 5, 2), gb.GGmlType.F16, G)
+    gb.galois_cpy(_gpu(gb, dev, x), d16)
+    assert np.array_equal(d16.to_numpy().view(np.uint16), oracle.cpy_f32_f16(x))
+    # KV-cache append: one token's [heads][head_dim] row into row `p` of a [heads][ctx][head_dim] f16 cache
+    heads, hd, ctxlen, p = 4, 16, 10, 7
+    k_new = oracle.fill_normal(heads * hd, 812).reshape(heads, hd)
+    cache = gb.Tensor.zeros((hd, ctxlen, heads), gb.GGmlType.F16, G)
+    row = cache.view((hd, 1, heads), (1, hd, hd * ctxlen, hd * ctxlen * heads), offset=p * hd)
+    src = _gpu(gb, dev, k_new).view((hd, 1, heads), (1, hd, hd, hd * heads))
+    gb.galois_cpy(src, row)
+    got = cache.to_numpy().view(np.uint16)
+    want = np.zeros((heads, ctxlen, hd), np.uint16)
+    want[:, p, :] = oracle.f32_to_f16(k_new)
+    assert np.array_equal(got, want)
+    # transposed source -> contiguous f32 (galois_cont)
+    xt = _gpu(gb, dev, x[0]).view((5, 64), (64, 1, 320, 320))
+    dst = gb.Tensor.zeros((5, 64), gb.GGmlType.F32, G)
+    gb.galois_cont(xt, dst)
+    assert np.array_equal(dst.to_numpy(), x[0].T)
+    with pytest.raises(gb.GError):   # element counts differ
+        gb.galois_cpy(_gpu(gb, dev, x), gb.Tensor.zeros((64, 5), gb.GGmlType.F32, G))
