@@ -113,6 +113,13 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
     ctx->ordinal = ordinal;
     ctx->stream = (cudaStream_t)cu_stream;
     ctx->sm_count = prop.multiProcessorCount;
+    // optional tuning overrides, e.g. GALOIS_B200_TUNE="warps=16,r=1,stages=2"
+    if (const char* t = getenv("GALOIS_B200_TUNE")) {
+        const char* q;
+        if ((q = strstr(t, "warps="))) ctx->tune_warps = atoi(q + 6);
+        if ((q = strstr(t, "r="))) ctx->tune_r = atoi(q + 2);
+        if ((q = strstr(t, "stages="))) ctx->tune_stages = atoi(q + 7);
+    }
 
     // f16 tables of GLOBAL_CPU_DEVICE_CACHE (src/op.rs:227-252): entry i =
     // f16(f(f32(f16::from_bits(i)))) with libm expf, built once on the host and
@@ -249,12 +256,12 @@ static int validate_mul_mat(galois_b200_ctx* ctx, const void* w, const galois_di
     if (K % GB_QK != 0) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0: %lld is not divisible by 32", (long long)K);
     if (!(dd->ne[0] == N && dd->ne[1] == xd->ne[1] && dd->ne[2] == xd->ne[2] && dd->ne[3] == xd->ne[3]))
         return gb_fail(ctx, GALOIS_B200_E_SHAPE, "mul_mat_q4_0: dst shape does not match (src/op.rs:1422-1425)");
+    if (N == 0 || K == 0 || xd->ne[1] * xd->ne[2] * xd->ne[3] == 0) return 0;  // nothing is read or written
     if (wd->nb[0] != 1 || xd->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: permuted src0 or src1 not supported (src/op.rs:1428-1429)");
     if (!(dd->nb[0] == 1 && dd->nb[0] <= dd->nb[1] && dd->nb[1] <= dd->nb[2] && dd->nb[2] <= dd->nb[3]))
         return gb_fail(ctx, GALOIS_B200_E_DST, "mul_mat_q4_0: dst cannot be transposed or permuted (src/op.rs:1432-1435)");
     if (wd->ne[2] < 1 || wd->ne[3] < 1 || xd->ne[2] % wd->ne[2] != 0 || xd->ne[3] % wd->ne[3] != 0)
         return gb_fail(ctx, GALOIS_B200_E_BROADCAST, "mul_mat_q4_0: src0 dims 2/3 must divide src1 dims 2/3 (src/op.rs:1473-1474)");
-    if (N == 0 || K == 0 || xd->ne[1] * xd->ne[2] * xd->ne[3] == 0) return 0;  // nothing is read
     if (!w || !x || !dst) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0: null pointer");
     if ((uintptr_t)w % 2 != 0) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: weight blocks must be 2-byte aligned");
     if ((uintptr_t)x % 4 != 0 || (uintptr_t)dst % 4 != 0) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: f32 operands must be 4-byte aligned");

@@ -20,6 +20,8 @@ struct galois_b200_ctx {
     cudaStream_t stream;
     int sm_count;
     int variant;           // forced Q4_0 mat-mul variant (0 = automatic)
+    // launch-geometry overrides for the bulk-copy GEMV (0 = automatic), from GALOIS_B200_TUNE
+    int tune_warps, tune_r, tune_stages;
     int64_t launches;      // kernels launched through this context
     // f16 look-up tables (65 536 entries each), device copies
     uint16_t* exp_lut;
@@ -76,7 +78,7 @@ static inline bool gb_same_shape(const galois_dim* a, const galois_dim* b) {
 // Internal activation format produced by the quantiser for the mat-mul kernels
 // (structure of arrays; same values as the 34-byte Q8_0 blocks):
 //   qs : int8  [rows][K]          16-byte aligned rows
-//   ds : float2[rows][K/32]       .x = f32(f16(d)), .y = bit pattern of the int32 sum of the block's 32 quants
+//   ds : float2[rows][K/32]       .x = f32(f16(d)), .y = bit pattern of the int32 -8 * (sum of the block's 32 quants)
 struct gb_q8_soa {
     const int8_t* qs;
     const float2* ds;

@@ -16,7 +16,7 @@
 //                     Every warp streams whole rows through a private ring of
 //                     shared-memory stages filled by cp.async.bulk (1-D bulk
 //                     copies completing on an mbarrier); no block-wide barrier in
-//                     the main loop.  36-byte block pairs are read as nine
+//                     the main loop; 16 warps per SM.  36-byte block pairs are read as nine
 //                     aligned 32-bit words per lane (stride 9 words: no bank
 //                     conflicts) and realigned with funnel shifts.
 #include "common.cuh"
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(128) mmv_q4_0_direct_kernel(const uint8_t* __r
                 const int4 y0 = __ldg(yp), y1 = __ldg(yp + 1);
                 const int y[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
                 const float2 ds = __ldg(xds + (xrow0 + b) * nblk + ib);
-                const int isum = dot_q4_words(q, y) - 8 * __float_as_int(ds.y);
+                const int isum = dot_q4_words(q, y) + __float_as_int(ds.y);
                 acc[b] = fmaf(dw * ds.x, (float)isum, acc[b]);
             }
         }
@@ -120,24 +120,25 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ uint32_t mbar_test(uint64_t* bar, uint32_t parity) {
+// One try_wait: the thread may be suspended by the hardware for up to `hint_ns` before it
+// returns false.
+__device__ __forceinline__ uint32_t mbar_test(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok;
 }
-// Waits for the phase with the given parity; gives up after ~2^31 clocks and
-// returns false (the caller records a timeout status and stops).
+// Waits for the phase with the given parity; gives up after about two seconds and returns
+// false (the caller records a timeout status and stops).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    if (mbar_test(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_test(bar, parity)) {
-        if (clock64() - t0 > (1ll << 31)) return false;
+    while (!mbar_test(bar, parity, 20000u)) {
+        if (clock64() - t0 > (1ll << 32)) return false;
     }
     return true;
 }
@@ -149,81 +150,130 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-constexpr int BULK_WARPS = 8;
-constexpr int BULK_MAX_STAGES = 4;
+// a (u8 x4) . b (s8 x4) + c
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 
-// Shared memory layout (dynamic):
-//   [0, 512)   mbarriers: BULK_WARPS * BULK_MAX_STAGES
-//   act qs   : NB * K bytes, "piece-major": the 64 quants of block pair p are four 16-byte pieces;
-//              piece j of pair p of row b sits at b*K + j*(K/4) + p*16, so the 32 lanes of a warp
-//              (lane = pair) read consecutive 16-byte words: no bank conflicts.
-//   act ds   : NB * K/32 float2 {d, bits(sum q)}
-//   ring     : BULK_WARPS * stages * chunk_bytes of raw Q4_0 rows
-template <int NB, int R>
+// One 36-byte block pair (nine aligned words t[0..8]: {d0 | qs0[0:2]}, qs0[2:14], {qs0[14:16] | d1},
+// qs1[0:16]) against the 64 int8 activations y[0..15] of the same two blocks.
+// ds = {dx0, bits(-8 * sum y0), dx1, bits(-8 * sum y1)}.  The high nibbles are used in place
+// (16 * q as an unsigned byte), their dot product is an exact multiple of 16.
+__device__ __forceinline__ float pair_dot(const uint32_t t[9], const int y[16], const float4 ds, float acc) {
+    int lo0 = 0, hi0 = 0, lo1 = 0, hi1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t q0 = __funnelshift_r(t[i], t[i + 1], 16);
+        const uint32_t q1 = t[5 + i];
+        lo0 = dp4a_us(q0 & 0x0F0F0F0Fu, y[i], lo0);
+        hi0 = dp4a_us(q0 & 0xF0F0F0F0u, y[4 + i], hi0);
+        lo1 = dp4a_us(q1 & 0x0F0F0F0Fu, y[8 + i], lo1);
+        hi1 = dp4a_us(q1 & 0xF0F0F0F0u, y[12 + i], hi1);
+    }
+    const int i0 = lo0 + (hi0 >> 4) + __float_as_int(ds.y);
+    const int i1 = lo1 + (hi1 >> 4) + __float_as_int(ds.w);
+    const float dw0 = __half2float(__ushort_as_half((unsigned short)(t[0] & 0xffffu)));
+    const float dw1 = __half2float(__ushort_as_half((unsigned short)(t[4] >> 16)));
+    acc = fmaf(dw0 * ds.x, (float)i0, acc);
+    acc = fmaf(dw1 * ds.z, (float)i1, acc);
+    return acc;
+}
+
+constexpr int BULK_MAX_STAGES = 4;
+constexpr int BULK_SMEM_MAX = 227 * 1024;
+constexpr int BULK_BAR_BYTES = 1024;  // BULK_MAX_WARPS * BULK_MAX_STAGES mbarriers
+
+// Every warp streams whole weight rows (R per stage) through its own ring of shared-memory
+// stages filled by cp.async.bulk; there is no block-wide barrier after the prologue.
+// Lane l owns block pairs l, l + 32, ... of every row.
+//   HOIST (NB == 1, K <= 4096): the lane's activations never change from row to row, so they are
+//          loaded once from global memory into registers and shared memory holds weights only.
+//   else:  the quantised activations are staged in shared memory "piece-major": the 64 quants of
+//          block pair p are four 16-byte pieces, piece j of pair p of activation row b sits at
+//          b*K + j*(K/4) + p*16, so the 32 lanes read consecutive 16-byte words (no bank conflicts).
+// Shared memory: [0, 1024) mbarriers | activations (qs, then float2 ds) | BULK_WARPS * stages * chunk.
+// BULK_WARPS warps per CTA, one CTA per SM.
+template <int NB, int R, bool HOIST, int BULK_WARPS>
 __global__ void __launch_bounds__(BULK_WARPS * 32, 1)
     mmv_q4_0_bulk_kernel(const uint8_t* __restrict__ w, const int8_t* __restrict__ xq, const float2* __restrict__ xds,
-                         float* __restrict__ dst, int64_t nb1, int K, int N, int nbatch, int stages, int* __restrict__ status) {
+                         float* __restrict__ dst, int nb1, int K, int N, int nbatch, int stages, int* __restrict__ status) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nblk = K / GB_QK, npair = nblk >> 1;
+    const int nblk = K >> 5, npair = nblk >> 1;
     const uint32_t row_bytes = (uint32_t)nblk * GB_Q4_BYTES;
     const uint32_t chunk_bytes = row_bytes * R;
 
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-    uint8_t* act_qs = smem + 512;
-    const uint32_t act_qs_bytes = (uint32_t)NB * (uint32_t)K;
+    uint64_t* my_bars = reinterpret_cast<uint64_t*>(smem) + warp * BULK_MAX_STAGES;
+    uint8_t* act_qs = smem + BULK_BAR_BYTES;
+    const uint32_t act_qs_bytes = HOIST ? 0u : (uint32_t)NB * (uint32_t)K;
+    const uint32_t act_ds_bytes = HOIST ? 0u : (uint32_t)NB * (uint32_t)nblk * 8u;
     float2* act_ds = reinterpret_cast<float2*>(act_qs + act_qs_bytes);
-    const uint32_t act_ds_bytes = (uint32_t)NB * (uint32_t)nblk * 8u;
-    uint8_t* ring = act_qs + ((act_qs_bytes + act_ds_bytes + 127u) & ~127u) + (size_t)warp * stages * chunk_bytes;
-    uint64_t* my_bars = bars + warp * BULK_MAX_STAGES;
+    uint8_t* ring = act_qs + ((act_qs_bytes + act_ds_bytes + 127u) & ~127u) + (uint32_t)warp * stages * chunk_bytes;
 
     // chunks (groups of R rows) are dealt round-robin to CTAs, then to the warps of a CTA
     const int nchunks = (N + R - 1) / R;
-    const int cta_chunks = (nchunks - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;  // chunks blockIdx.x, +grid, ...
-    const int my_chunks = (cta_chunks - warp + BULK_WARPS - 1) / BULK_WARPS;                  // local idx warp, +8, ...
+    const int cta_chunks = (nchunks - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int my_chunks = (cta_chunks - warp + BULK_WARPS - 1) / BULK_WARPS;
     auto chunk_row0 = [&](int j) { return ((int)blockIdx.x + (int)gridDim.x * (warp + BULK_WARPS * j)) * R; };
-    auto chunk_len = [&](int j) {
+    auto issue = [&](int j, int s) {
         const int r0 = chunk_row0(j);
-        const int rows = min(R, N - r0);
-        return (uint32_t)rows * row_bytes;
+        const uint32_t bytes = (uint32_t)min(R, N - r0) * row_bytes;
+        mbar_expect_tx(&my_bars[s], bytes);
+        bulk_g2s(ring + (uint32_t)s * chunk_bytes, w + (size_t)r0 * row_bytes, bytes, &my_bars[s]);
     };
 
     if (lane == 0) {
         for (int s = 0; s < stages; s++) mbar_init(&my_bars[s], 1);
         fence_proxy_async();
+        // weights first: they do not depend on the quantiser
+        for (int s = 0; s < stages && s < my_chunks; s++) issue(s, s);
     }
-    __syncwarp();
-    // weights first: they do not depend on the quantiser
-    if (lane == 0) {
-        for (int s = 0; s < stages && s < my_chunks; s++) {
-            const uint32_t bytes = chunk_len(s);
-            mbar_expect_tx(&my_bars[s], bytes);
-            bulk_g2s(ring + (size_t)s * chunk_bytes, w + (size_t)chunk_row0(s) * row_bytes, bytes, &my_bars[s]);
+
+    // activations
+    int yreg[HOIST ? 2 : 1][16];
+    float4 dsreg[HOIST ? 2 : 1];
+    if (HOIST) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int p = lane + 32 * i;
+            if (p < npair) {
+                const int4* yp = reinterpret_cast<const int4*>(xq) + p * 4;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int4 v = __ldg(yp + j);
+                    yreg[i][4 * j] = v.x, yreg[i][4 * j + 1] = v.y, yreg[i][4 * j + 2] = v.z, yreg[i][4 * j + 3] = v.w;
+                }
+                dsreg[i] = __ldg(reinterpret_cast<const float4*>(xds) + p);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) yreg[i][j] = 0;
+                dsreg[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
-    }
-    // quantised activations: cooperative copy into the piece-major layout
-    {
+        __syncwarp();
+    } else {
         const int pieces_per_row = K >> 4;
         for (int i = threadIdx.x; i < NB * pieces_per_row; i += blockDim.x) {
             const int b = i / pieces_per_row, c = i - b * pieces_per_row;
             int4 v = make_int4(0, 0, 0, 0);
             if (b < nbatch) v = __ldg(reinterpret_cast<const int4*>(xq + (size_t)b * K) + c);
-            *reinterpret_cast<int4*>(act_qs + (size_t)b * K + (size_t)(c & 3) * (K >> 2) + (size_t)(c >> 2) * 16) = v;
+            *reinterpret_cast<int4*>(act_qs + (uint32_t)b * K + (uint32_t)(c & 3) * (K >> 2) + (uint32_t)(c >> 2) * 16) = v;
         }
         for (int i = threadIdx.x; i < NB * nblk; i += blockDim.x) {
             const int b = i / nblk;
             act_ds[i] = b < nbatch ? __ldg(xds + i) : make_float2(0.0f, 0.0f);
         }
+        __syncthreads();
     }
-    __syncthreads();
     bool ok = true;
 
-    for (int j = 0; j < my_chunks && ok; j++) {
+    for (int j = 0; j < my_chunks; j++) {
         const int s = j % stages;
-        const uint32_t parity = (uint32_t)(j / stages) & 1u;
-        ok = mbar_wait_bounded(&my_bars[s], parity);
+        ok = mbar_wait_bounded(&my_bars[s], (uint32_t)(j / stages) & 1u);
         if (!ok) break;
-        const uint8_t* buf = ring + (size_t)s * chunk_bytes;
+        const uint8_t* buf = ring + (uint32_t)s * chunk_bytes;
         const int row0 = chunk_row0(j);
         const int rows = min(R, N - row0);
 
@@ -233,62 +283,56 @@ __global__ void __launch_bounds__(BULK_WARPS * 32, 1)
 #pragma unroll
             for (int b = 0; b < NB; b++) acc[r][b] = 0.0f;
 
-        for (int p = lane; p < npair; p += 32) {
-            // weights of block pair p for up to R rows
-            uint32_t q[R][2][4];
-            float dw[R][2];
+        if (HOIST) {
 #pragma unroll
-            for (int r = 0; r < R; r++) {
-                if (r < rows) {
-                    const uint32_t* wp = reinterpret_cast<const uint32_t*>(buf + (size_t)r * row_bytes) + p * 9;
-                    uint32_t t[9];
+            for (int i = 0; i < 2; i++) {
+                const int p = lane + 32 * i;
+                if (p < npair) {
 #pragma unroll
-                    for (int i = 0; i < 9; i++) t[i] = wp[i];
-                    dw[r][0] = __half2float(__ushort_as_half((unsigned short)(t[0] & 0xffffu)));
-                    dw[r][1] = __half2float(__ushort_as_half((unsigned short)(t[4] >> 16)));
+                    for (int r = 0; r < R; r++) {
+                        if (r < rows) {
+                            const uint32_t* wp = reinterpret_cast<const uint32_t*>(buf + (uint32_t)r * row_bytes) + p * 9;
+                            uint32_t t[9];
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        q[r][0][i] = __funnelshift_r(t[i], t[i + 1], 16);
-                        q[r][1][i] = t[5 + i];
+                            for (int q = 0; q < 9; q++) t[q] = wp[q];
+                            acc[r][0] = pair_dot(t, yreg[i], dsreg[i], acc[r][0]);
+                        }
                     }
-                } else {
-                    dw[r][0] = dw[r][1] = 0.0f;
-#pragma unroll
-                    for (int i = 0; i < 4; i++) q[r][0][i] = q[r][1][i] = 0u;
                 }
             }
-#pragma unroll
-            for (int b = 0; b < NB; b++) {
-                const uint8_t* yp = act_qs + (size_t)b * K + (size_t)p * 16;
-                const int4 a0 = *reinterpret_cast<const int4*>(yp);
-                const int4 a1 = *reinterpret_cast<const int4*>(yp + (K >> 2));
-                const int4 a2 = *reinterpret_cast<const int4*>(yp + 2 * (K >> 2));
-                const int4 a3 = *reinterpret_cast<const int4*>(yp + 3 * (K >> 2));
-                const int y0[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                const int y1[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
-                const float4 ds = *reinterpret_cast<const float4*>(act_ds + (size_t)b * nblk + 2 * p);
+        } else {
+            for (int p = lane; p < npair; p += 32) {
+                uint32_t t[R][9];
 #pragma unroll
                 for (int r = 0; r < R; r++) {
-                    const int i0 = dot_q4_words(q[r][0], y0) - 8 * __float_as_int(ds.y);
-                    const int i1 = dot_q4_words(q[r][1], y1) - 8 * __float_as_int(ds.w);
-                    acc[r][b] = fmaf(dw[r][0] * ds.x, (float)i0, acc[r][b]);
-                    acc[r][b] = fmaf(dw[r][1] * ds.z, (float)i1, acc[r][b]);
+                    const uint32_t* wp = reinterpret_cast<const uint32_t*>(buf + (uint32_t)(r < rows ? r : 0) * row_bytes) + p * 9;
+#pragma unroll
+                    for (int q = 0; q < 9; q++) t[r][q] = wp[q];
+                }
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    const uint8_t* yp = act_qs + (uint32_t)b * K + (uint32_t)p * 16;
+                    const int4 a0 = *reinterpret_cast<const int4*>(yp);
+                    const int4 a1 = *reinterpret_cast<const int4*>(yp + (K >> 2));
+                    const int4 a2 = *reinterpret_cast<const int4*>(yp + 2 * (K >> 2));
+                    const int4 a3 = *reinterpret_cast<const int4*>(yp + 3 * (K >> 2));
+                    const int y[16] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w,
+                                       a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+                    const float4 ds = *reinterpret_cast<const float4*>(act_ds + (uint32_t)b * nblk + 2 * p);
+#pragma unroll
+                    for (int r = 0; r < R; r++) acc[r][b] = pair_dot(t[r], y, ds, acc[r][b]);
                 }
             }
         }
         // every lane has consumed the stage: refill it
         __syncwarp();
-        if (lane == 0 && j + stages < my_chunks) {
-            const uint32_t bytes = chunk_len(j + stages);
-            mbar_expect_tx(&my_bars[s], bytes);
-            bulk_g2s(ring + (size_t)s * chunk_bytes, w + (size_t)chunk_row0(j + stages) * row_bytes, bytes, &my_bars[s]);
-        }
+        if (lane == 0 && j + stages < my_chunks) issue(j + stages, s);
 #pragma unroll
         for (int r = 0; r < R; r++)
 #pragma unroll
             for (int b = 0; b < NB; b++) {
                 const float v = gb_warp_sum(acc[r][b]);
-                if (lane == 0 && r < rows && b < nbatch) dst[(size_t)b * nb1 + row0 + r] = v;
+                if (lane == 0 && r < rows && b < nbatch) dst[b * nb1 + row0 + r] = v;
             }
     }
     if (!ok && lane == 0) atomicExch(status, GALOIS_B200_E_TIMEOUT);
@@ -307,73 +351,99 @@ int launch_direct(galois_b200_ctx* ctx, const uint8_t* w, const galois_dim* wd, 
     return 0;
 }
 
-template <int NB, int R>
-int launch_bulk_t(galois_b200_ctx* ctx, const uint8_t* w, const gb_q8_soa& xq, float* dst, int64_t nb1, int K, int N,
+template <int NB, int R, bool HOIST, int WARPS>
+int launch_bulk_t(galois_b200_ctx* ctx, const uint8_t* w, const gb_q8_soa& xq, float* dst, int nb1, int K, int N,
                   int nbatch, int stages, size_t smem, int grid) {
-    mmv_q4_0_bulk_kernel<NB, R><<<grid, BULK_WARPS * 32, smem, ctx->stream>>>(w, xq.qs, xq.ds, dst, nb1, K, N, nbatch,
-                                                                              stages, ctx->dev_status);
+    mmv_q4_0_bulk_kernel<NB, R, HOIST, WARPS><<<grid, WARPS * 32, smem, ctx->stream>>>(w, xq.qs, xq.ds, dst, nb1, K, N,
+                                                                                       nbatch, stages, ctx->dev_status);
     GB_LAUNCHED(ctx, "mmv_q4_0_bulk");
     return 0;
+}
+
+// Launch geometry of the bulk-copy kernel for one problem.
+struct bulk_plan {
+    bool ok;
+    int nbt, r, warps, stages, grid;
+    bool hoist;
+    size_t smem;
+};
+
+bulk_plan plan_bulk(const galois_b200_ctx* ctx, int64_t K, int64_t N, int64_t B) {
+    bulk_plan p{};
+    p.ok = false;
+    p.nbt = B <= 1 ? 1 : (B <= 2 ? 2 : (B <= 4 ? 4 : 8));
+    p.hoist = p.nbt == 1 && K <= 4096;
+    const size_t row_bytes = (size_t)(K / GB_QK) * GB_Q4_BYTES;
+    const size_t act = p.hoist ? 0 : ((((size_t)p.nbt * K + (size_t)p.nbt * (K / 32) * 8) + 127) & ~(size_t)127);
+    if (BULK_BAR_BYTES + act >= (size_t)BULK_SMEM_MAX) return p;
+    const size_t budget = (size_t)BULK_SMEM_MAX - BULK_BAR_BYTES - act;
+    // more warps hide the per-row latency; two rows per stage share the activation reads
+    p.warps = (ctx->tune_warps == 16 || ctx->tune_warps == 32) ? ctx->tune_warps : 32;
+    if (p.nbt == 8 || (size_t)p.warps * 2 * row_bytes > budget) p.warps = 16;
+    if ((size_t)p.warps * 2 * row_bytes > budget) return p;
+    p.r = (ctx->tune_r == 1 || ctx->tune_r == 2) ? ctx->tune_r : ((size_t)p.warps * 3 * 2 * row_bytes <= budget ? 2 : 1);
+    if ((size_t)p.warps * 2 * p.r * row_bytes > budget) p.r = 1;
+    if (p.warps == 32 && p.nbt == 4) p.r = 1;  // the two-row instance spills at 64 registers
+    const size_t chunk = row_bytes * p.r;
+    p.stages = (int)(budget / ((size_t)p.warps * chunk));
+    if (p.stages > BULK_MAX_STAGES) p.stages = BULK_MAX_STAGES;
+    if (ctx->tune_stages >= 2 && ctx->tune_stages < p.stages) p.stages = ctx->tune_stages;
+    p.smem = BULK_BAR_BYTES + act + (size_t)p.warps * p.stages * chunk;
+    const int64_t nchunks = (N + p.r - 1) / p.r;
+    int64_t grid = ctx->sm_count;
+    if (grid > (nchunks + p.warps - 1) / p.warps) grid = (nchunks + p.warps - 1) / p.warps;
+    p.grid = (int)(grid < 1 ? 1 : grid);
+    p.ok = true;
+    return p;
 }
 
 }  // namespace
 
 bool gb_mmv_bulk_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const galois_dim* xd,
                            const galois_dim* dd) {
-    (void)ctx;
     const int64_t K = wd->ne[0], N = wd->ne[1];
     if (K % 256 != 0 || K > 32768 || N < 1 || N > (1 << 30)) return false;
     if ((uintptr_t)w % 16 != 0) return false;
     if (wd->ne[2] != 1 || wd->ne[3] != 1 || xd->ne[2] != 1 || xd->ne[3] != 1) return false;
     if (wd->nb[1] != K / GB_QK) return false;
     if (xd->ne[1] < 1 || xd->ne[1] > 8) return false;
-    (void)dd;
-    return true;
+    if (dd->nb[1] > (1 << 30)) return false;
+    return plan_bulk(ctx, K, N, xd->ne[1]).ok;
 }
 
-template <int NB, int R>
+template <int NB, int R, bool HOIST, int WARPS>
 static cudaError_t bulk_attr() {
-    return cudaFuncSetAttribute(mmv_q4_0_bulk_kernel<NB, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    return cudaFuncSetAttribute(mmv_q4_0_bulk_kernel<NB, R, HOIST, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                BULK_SMEM_MAX);
 }
+
+#define GB_BULK_INSTANCES(X) \
+    X(1, 1, true, 16) X(1, 2, true, 16) X(1, 1, true, 32) X(1, 2, true, 32)      \
+    X(1, 1, false, 16) X(1, 2, false, 16) X(1, 1, false, 32) X(1, 2, false, 32)  \
+    X(2, 1, false, 16) X(2, 2, false, 16) X(2, 1, false, 32) X(2, 2, false, 32)  \
+    X(4, 1, false, 16) X(4, 2, false, 16) X(4, 1, false, 32) X(4, 2, false, 32)  \
+    X(8, 1, false, 16) X(8, 2, false, 16)
 
 int gb_mmv_bulk_init(galois_b200_ctx* ctx) {
-    GB_CUDA(ctx, (bulk_attr<1, 1>()));
-    GB_CUDA(ctx, (bulk_attr<1, 2>()));
-    GB_CUDA(ctx, (bulk_attr<2, 1>()));
-    GB_CUDA(ctx, (bulk_attr<2, 2>()));
-    GB_CUDA(ctx, (bulk_attr<4, 1>()));
-    GB_CUDA(ctx, (bulk_attr<4, 2>()));
-    GB_CUDA(ctx, (bulk_attr<8, 1>()));
-    GB_CUDA(ctx, (bulk_attr<8, 2>()));
+#define X(NB_, R_, H_, W_) GB_CUDA(ctx, (bulk_attr<NB_, R_, H_, W_>()));
+    GB_BULK_INSTANCES(X)
+#undef X
     return 0;
 }
 
 int gb_mmv_q4_0_bulk(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const gb_q8_soa& xq,
                      const galois_dim* xd, float* dst, const galois_dim* dd) {
     const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
-    const int nblk = K / GB_QK;
-    const uint32_t row_bytes = (uint32_t)nblk * GB_Q4_BYTES;
-    const int R = row_bytes <= 2304 ? 2 : 1;
-    const uint32_t chunk_bytes = row_bytes * R;
-    const int NBT = B <= 1 ? 1 : (B <= 2 ? 2 : (B <= 4 ? 4 : 8));
-    const size_t act = (((size_t)NBT * K + (size_t)NBT * nblk * 8) + 127) & ~(size_t)127;
-    const size_t budget = 227 * 1024 - 512 - act;
-    int stages = (int)(budget / ((size_t)BULK_WARPS * chunk_bytes));
-    if (stages > BULK_MAX_STAGES) stages = BULK_MAX_STAGES;
-    if (stages < 2) return GALOIS_B200_E_LAYOUT;
-    const size_t smem = 512 + act + (size_t)BULK_WARPS * stages * chunk_bytes;
-    const int nchunks = (N + R - 1) / R;
-    int grid = ctx->sm_count;
-    if (grid > (nchunks + BULK_WARPS - 1) / BULK_WARPS) grid = (nchunks + BULK_WARPS - 1) / BULK_WARPS;
-    if (grid < 1) grid = 1;
+    const bulk_plan p = plan_bulk(ctx, K, N, B);
+    if (!p.ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: rows too long for the bulk-copy kernel");
     const uint8_t* wb = (const uint8_t*)w;
-    const int64_t nb1 = dd->nb[1];
-#define GB_BULK_CASE(nb, r) \
-    if (NBT == nb && R == r) return launch_bulk_t<nb, r>(ctx, wb, xq, dst, nb1, K, N, B, stages, smem, grid);
-    GB_BULK_CASE(1, 1) GB_BULK_CASE(1, 2) GB_BULK_CASE(2, 1) GB_BULK_CASE(2, 2) GB_BULK_CASE(4, 1) GB_BULK_CASE(4, 2)
-    GB_BULK_CASE(8, 1) GB_BULK_CASE(8, 2)
-#undef GB_BULK_CASE
-    return GALOIS_B200_E_LAYOUT;
+    const int nb1 = (int)dd->nb[1];
+#define X(NB_, R_, H_, W_)                                                    \
+    if (p.nbt == NB_ && p.r == R_ && p.hoist == H_ && p.warps == W_)          \
+        return launch_bulk_t<NB_, R_, H_, W_>(ctx, wb, xq, dst, nb1, K, N, B, p.stages, p.smem, p.grid);
+    GB_BULK_INSTANCES(X)
+#undef X
+    return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: no bulk-copy kernel instance for this shape");
 }
 
 int gb_mmv_q4_0_direct(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const gb_q8_soa& xq,

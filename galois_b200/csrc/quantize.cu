@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256) quantize_q8_soa_kernel(const float* __res
         const uint32_t packed = quantize4(v, &d16, &qsum);
         if (live) {
             *reinterpret_cast<uint32_t*>(qs + row * k + ib * GB_QK + sub * 4) = packed;
-            if (sub == 0) ds[blk] = make_float2(__half2float(d16), __int_as_float(qsum));
+            if (sub == 0) ds[blk] = make_float2(__half2float(d16), __int_as_float(-8 * qsum));
         }
     }
 }

@@ -127,14 +127,14 @@ def test_mul_mat_q4_0_direct(gb, dev, oracle, n, k, b):
 
 # variant 2 = bulk-copy pipelined GEMV (K % 256 == 0, batch <= 8)
 @pytest.mark.parametrize("n,k,b", [(4096, 4096, 1), (11008, 4096, 1), (4096, 11008, 1), (11008, 4096, 4),
-                                   (4096, 11008, 8), (1, 256, 1), (3, 256, 2), (1185, 512, 3), (2371, 4096, 5),
+                                   (4096, 11008, 4), (1, 256, 1), (3, 256, 2), (1185, 512, 3), (2371, 4096, 5),
                                    (149, 8192, 7), (32000, 4096, 8)])
 def test_mul_mat_q4_0_bulk(gb, dev, oracle, n, k, b):
     _mul_mat_case(gb, dev, oracle, n, k, b, 8000 + n + k + b, 2)
 
 
 # automatic dispatch over the BASELINE shapes (configs 2, 3, 5) incl. large batches
-@pytest.mark.parametrize("n,k,b", [(11008, 4096, 8), (4096, 4096, 512), (32000, 4096, 16), (28672, 8192, 16),
+@pytest.mark.parametrize("n,k,b", [(11008, 4096, 8), (4096, 11008, 8), (4096, 4096, 512), (32000, 4096, 16), (28672, 8192, 16),
                                    (4096, 4096, 100), (300, 4096, 37)])
 def test_mul_mat_q4_0_auto(gb, dev, oracle, n, k, b):
     _mul_mat_case(gb, dev, oracle, n, k, b, 9000 + n + k + b, 0)
