@@ -29,6 +29,7 @@ SIGNATURES = {
     "galois_b200_last_error": ([_P], C.c_char_p),
     "galois_b200_launch_count": ([_P], _I64),
     "galois_b200_set_mul_mat_variant": ([_P, _I], _I),
+    "galois_b200_set_pdl": ([_P, _I], _I),
     "galois_b200_profile_enable": ([_P, _I], _I),
     "galois_b200_profile_read": ([_P, C.POINTER(C.c_double), C.POINTER(_I64)], _I),
     "galois_b200_alloc": ([_P, _SZ, C.POINTER(_P)], _I),

@@ -5,6 +5,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "gemv_q4_0.cuh"
 #include "mul_mat_q4_0.cuh"
 #include "mul_mat_q4_0_tc.cuh"
 #include "quantize.cuh"
@@ -113,12 +114,17 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
     ctx->ordinal = ordinal;
     ctx->stream = (cudaStream_t)cu_stream;
     ctx->sm_count = prop.multiProcessorCount;
+    ctx->pdl = 1;
     // optional tuning overrides, e.g. GALOIS_B200_TUNE="warps=16,r=1,stages=2"
     if (const char* t = getenv("GALOIS_B200_TUNE")) {
         const char* q;
         if ((q = strstr(t, "warps="))) ctx->tune_warps = atoi(q + 6);
         if ((q = strstr(t, "r="))) ctx->tune_r = atoi(q + 2);
         if ((q = strstr(t, "stages="))) ctx->tune_stages = atoi(q + 7);
+        if ((q = strstr(t, "smem_kb="))) ctx->tune_smem_kb = atoi(q + 8);
+        if ((q = strstr(t, "cps="))) ctx->tune_ctas_per_sm = atoi(q + 4);
+        if ((q = strstr(t, "pdl="))) ctx->pdl = atoi(q + 4);
+        if ((q = strstr(t, "dbg="))) ctx->tune_dbg = atoi(q + 4);
     }
 
     // f16 tables of GLOBAL_CPU_DEVICE_CACHE (src/op.rs:227-252): entry i =
@@ -150,6 +156,7 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
         void* p;
         rc = gb_scratch(ctx, (size_t)16 << 20, &p);
         if (rc == 0) rc = gb_mmv_bulk_init(ctx);
+        if (rc == 0) rc = gb_gemv_init(ctx);
         if (rc == 0) rc = gb_mm_tc_init(ctx);
         if (rc != 0) snprintf(g_init_err, sizeof(g_init_err), "%s", ctx->err);
     }
@@ -285,24 +292,33 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
         return 0;
     }
     const bool tc_ok = gb_mm_tc_supported(ctx, w, wd, xd, dd);
+    const bool gemv_ok = gb_gemv_supported(ctx, w, wd, x, xd, dd);
     const bool bulk_ok = gb_mmv_bulk_supported(ctx, w, wd, xd, dd);
     int variant = ctx->variant;
-    if (variant == 0) variant = (tc_ok && xd->ne[1] >= GB_TC_MIN_BATCH) ? 3 : (bulk_ok ? 2 : 1);
-    if (variant == 2 && !bulk_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: bulk-copy variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned base, batch <= 8");
+    if (variant == 0) variant = (tc_ok && xd->ne[1] >= GB_TC_MIN_BATCH) ? 3 : ((gemv_ok || bulk_ok) ? 2 : 1);
+    if (variant == 2 && !(gemv_ok || bulk_ok)) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: streaming variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned base, batch <= 8");
     if (variant == 3 && !tc_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: tensor-core variant needs 2-D contiguous weights, K %% 128 == 0, 16-byte aligned base");
 
+    const bool gemv = variant == 2 && gemv_ok;
+    gb_q8_soa xq = {nullptr, nullptr};
     void* scratch = nullptr;
-    size_t need = gb_q8_soa_bytes(K, nrows);
-    if (variant == 3) need += gb_mm_tc_scratch_bytes(wd, xd);
-    rc = gb_scratch(ctx, need, &scratch);
-    if (rc) return rc;
-    gb_q8_soa xq;
-    rc = gb_quantize_q8_soa(ctx, x, xd, scratch, &xq);
-    if (rc) return rc;
+    if (gemv) {
+        rc = gb_scratch(ctx, gb_gemv_scratch_bytes(K, nrows), &scratch);
+        if (rc) return rc;
+    } else {
+        size_t need = gb_q8_soa_bytes(K, nrows);
+        if (variant == 3) need += gb_mm_tc_scratch_bytes(wd, xd);
+        rc = gb_scratch(ctx, need, &scratch);
+        if (rc) return rc;
+        rc = gb_quantize_q8_soa(ctx, x, xd, scratch, &xq);
+        if (rc) return rc;
+    }
     const bool prof = ctx->profiling && ctx->prof_n < GB_PROF_MAX;
     if (prof) GB_CUDA(ctx, cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream));
     if (variant == 3)
         rc = gb_mm_q4_0_tc(ctx, w, wd, xq, xd, dst, dd, (uint8_t*)scratch + gb_q8_soa_bytes(K, nrows));
+    else if (gemv)
+        rc = gb_gemv_q4_0(ctx, w, wd, x, xd, dst, dd, scratch);
     else if (variant == 2)
         rc = gb_mmv_q4_0_bulk(ctx, w, wd, xq, xd, dst, dd);
     else
@@ -312,6 +328,12 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
         ctx->prof_n++;
     }
     return rc;
+}
+
+extern "C" int galois_b200_set_pdl(galois_b200_ctx* ctx, int on) {
+    GB_CHECK_CTX(ctx);
+    ctx->pdl = on ? 1 : 0;
+    return 0;
 }
 
 extern "C" int galois_b200_profile_enable(galois_b200_ctx* ctx, int on) {

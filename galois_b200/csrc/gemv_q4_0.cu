@@ -1,0 +1,431 @@
+// Streaming Q4_0 x Q8_0 GEMV for decode (batch 1-4): a small quantiser kernel + the GEMV.
+//
+//   * the f32 activations are quantised to Q8_0 once (bit-exact with
+//     <BlockQ8_0 as QuantType>::from_f32, src/ggml_quants.rs:736-764 of galois) into a scratch
+//     laid out exactly as the GEMV wants to read it; with one activation row every lane keeps
+//     its share of them in registers for the whole kernel, so the main loop reads only weights;
+//   * the 18-byte Q4_0 blocks stream HBM -> shared memory through per-warp rings of
+//     cp.async.bulk copies (1-D bulk copies completing on mbarriers, no multicast); a lane
+//     reads a 144 / 72 / 36-byte segment (8 / 4 / 2 blocks) with 128 / 64 / 32-bit loads whose
+//     lane stride is an odd number of load widths, so shared-memory reads are conflict free;
+//   * integer dot products with dp4a (exact), f32 scale accumulation, warp shuffles;
+//   * programmatic dependent launch: both kernels release their dependents at once and the GEMV
+//     prefetches its first weight stages BEFORE waiting for the kernels in front of it, so launch
+//     latency and the first DRAM round trip hide behind the previous mat-mul.  Small CTAs (128 threads,
+//     well under half an SM's shared memory) let CTAs of consecutive kernels share an SM.
+//
+// Numerics: MatMul::f_q_f32_f32::<BlockQ4_0> (src/op.rs:1383-1598) with
+// BlockQ4_0::vec_dot_q8_0 (src/ggml_quants.rs:156-172); only the order of the f32 additions
+// of the per-block terms differs from the CPU.
+#include "common.cuh"
+#include "gemv_q4_0.cuh"
+#include "ptx.cuh"
+
+namespace {
+
+constexpr int GEMV_WARPS = 4;
+constexpr int GEMV_THREADS = GEMV_WARPS * 32;
+constexpr int GEMV_MAX_STAGES = 6;
+constexpr int GEMV_BAR_BYTES = 256;  // GEMV_WARPS * GEMV_MAX_STAGES mbarriers, padded
+
+// One 36-byte block pair held as nine aligned words t[0..8] ({d0 | qs0[0:2]}, qs0[2:14],
+// {qs0[14:16] | d1}, qs1[0:16]) against the 64 int8 activations y[0..15] of the same two blocks.
+// ds = {dx0, bits(-8 * sum y0), dx1, bits(-8 * sum y1)}.  High nibbles are used in place
+// (16 * q as an unsigned byte): their dot product is an exact multiple of 16.
+__device__ __forceinline__ float pair_dot(const uint32_t* t, const int* y, const float4 ds, float acc) {
+    int lo0 = 0, hi0 = 0, lo1 = 0, hi1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t q0 = __funnelshift_r(t[i], t[i + 1], 16);
+        const uint32_t q1 = t[5 + i];
+        lo0 = dp4a_us(q0 & 0x0F0F0F0Fu, y[i], lo0);
+        hi0 = dp4a_us(q0 & 0xF0F0F0F0u, y[4 + i], hi0);
+        lo1 = dp4a_us(q1 & 0x0F0F0F0Fu, y[8 + i], lo1);
+        hi1 = dp4a_us(q1 & 0xF0F0F0F0u, y[12 + i], hi1);
+    }
+    const int i0 = lo0 + (hi0 >> 4) + __float_as_int(ds.y);
+    const int i1 = lo1 + (hi1 >> 4) + __float_as_int(ds.w);
+    const float dw0 = __half2float(__ushort_as_half((unsigned short)(t[0] & 0xffffu)));
+    const float dw1 = __half2float(__ushort_as_half((unsigned short)(t[4] >> 16)));
+    acc = fmaf(dw0 * ds.x, (float)i0, acc);
+    acc = fmaf(dw1 * ds.z, (float)i1, acc);
+    return acc;
+}
+
+// Loads the 36 * SEG bytes of one lane segment into 9 * SEG words with the widest aligned load.
+template <int SEG>
+__device__ __forceinline__ void load_segment(const uint8_t* p, uint32_t* t) {
+    if (SEG == 4) {
+#pragma unroll
+        for (int i = 0; i < 9; i++) {
+            const uint4 v = reinterpret_cast<const uint4*>(p)[i];
+            t[4 * i] = v.x, t[4 * i + 1] = v.y, t[4 * i + 2] = v.z, t[4 * i + 3] = v.w;
+        }
+    } else if (SEG == 2) {
+#pragma unroll
+        for (int i = 0; i < 9; i++) {
+            const uint2 v = reinterpret_cast<const uint2*>(p)[i];
+            t[2 * i] = v.x, t[2 * i + 1] = v.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 9; i++) t[i] = reinterpret_cast<const uint32_t*>(p)[i];
+    }
+}
+
+// Shared-memory activation layout ("piece-major"): a row of K quants is cut into segments of
+// SEG block pairs (64 * SEG bytes = 4 * SEG pieces of 16 bytes); piece j of segment s lives at
+// j * (nsegk * 16) + s * 16, so the lanes of a warp (lane = segment) read consecutive 16-byte
+// words.  The {d, -8 * sum} pairs of the segment's 2 * SEG blocks (SEG pieces) use the same
+// scheme.
+template <int SEG>
+__device__ __forceinline__ void load_act(const uint8_t* qs, const uint8_t* ds, int nsegk, int s, int* y, float4* d4) {
+#pragma unroll
+    for (int j = 0; j < 4 * SEG; j++) {
+        const int4 v = *reinterpret_cast<const int4*>(qs + (j * nsegk + s) * 16);
+        y[4 * j] = v.x, y[4 * j + 1] = v.y, y[4 * j + 2] = v.z, y[4 * j + 3] = v.w;
+    }
+#pragma unroll
+    for (int j = 0; j < SEG; j++) d4[j] = *reinterpret_cast<const float4*>(ds + (j * nsegk + s) * 16);
+}
+
+// Quantises `nrows` rows of K floats (bit-exact with <BlockQ8_0 as QuantType>::from_f32,
+// src/ggml_quants.rs:736-764) into the piece-major layout in global memory: row b's quants at
+// qs + b * K, its {d, -8 * sum} pairs at ds + b * (K/32) * 8.  Eight lanes own a block (four
+// consecutive floats each); one block per 8-lane group, all loads of a thread issued at once.
+template <int SEG>
+__global__ void __launch_bounds__(256) quantize_q8_pm_kernel(const float* __restrict__ x, int x_stride, int K, int nrows,
+                                                             uint8_t* __restrict__ qs_out, uint8_t* __restrict__ ds_out) {
+    pdl_launch_dependents();
+    const int nblk = K >> 5, nsegk = nblk / (2 * SEG);
+    const int sub = threadIdx.x & 7;
+    const int blk = (blockIdx.x * 256 + threadIdx.x) >> 3;  // block index within the row
+    const int b = blockIdx.y;
+    const bool live = blk < nblk;
+    pdl_wait();  // x belongs to the preceding kernel; the scratch may still be read by it
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) v = __ldg(reinterpret_cast<const float4*>(x + (size_t)b * x_stride + blk * 32) + sub);
+    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+    // `as i8` in Rust saturates and maps NaN to 0; so does (int) followed by the clamp
+    const int q0 = max(-128, min(127, (int)roundf(__fmul_rn(v.x, id))));
+    const int q1 = max(-128, min(127, (int)roundf(__fmul_rn(v.y, id))));
+    const int q2 = max(-128, min(127, (int)roundf(__fmul_rn(v.z, id))));
+    const int q3 = max(-128, min(127, (int)roundf(__fmul_rn(v.w, id))));
+    int s = q0 + q1 + q2 + q3;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (live) {
+        const int seg = blk / (2 * SEG), bi = blk % (2 * SEG);
+        const uint32_t packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
+                                ((uint32_t)(q3 & 0xff) << 24);
+        const int piece = 2 * bi + (sub >> 2);
+        *reinterpret_cast<uint32_t*>(qs_out + (size_t)b * K + (piece * nsegk + seg) * 16 + (sub & 3) * 4) = packed;
+        if (sub == 0)
+            *reinterpret_cast<float2*>(ds_out + (size_t)b * nblk * 8 + ((bi >> 1) * nsegk + seg) * 16 + (bi & 1) * 8) =
+                make_float2(__half2float(__float2half_rn(d)), __int_as_float(-8 * s));
+    }
+}
+
+// NB     activation rows (1, 2 or 4)
+// SEG    block pairs per lane segment (4, 2, 1)
+// SPLIT  true : a row has nsegk <= 32 segments (a power of two); a chunk is 32 / nsegk rows =
+//               exactly one pass of the warp and lanes [r*nsegk, (r+1)*nsegk) own row r.
+//        false: a chunk is one row walked in ceil(nsegk / 32) passes.
+// NPASS  > 0 (NB == 1 only): the number of passes is a compile-time constant and the lane's
+//               activations for all of them are loaded into registers once for the whole kernel,
+//               so the main loop reads nothing but weights;
+//        0   : activations are read from shared memory in every pass.
+//
+// xq / xds: the activations quantised by quantize_q8_pm_kernel<SEG> (piece-major, NB rows).
+// Shared memory: [0, 256) mbarriers | act qs (NB * K) | act ds (NB * K/32 * 8) | GEMV_WARPS * stages * chunk.
+template <int NB, int SEG, bool SPLIT, int NPASS>
+__global__ void __launch_bounds__(GEMV_THREADS)
+    gemv_q4_0_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ xq, const uint8_t* __restrict__ xds,
+                     float* __restrict__ dst, int nb1, int K, int N, int nbatch, int stages,
+                     int* __restrict__ status, int dbg) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    pdl_launch_dependents();
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nblk = K >> 5;
+    const int nsegk = nblk / (2 * SEG);                   // segments per row
+    const int rows_per_chunk = SPLIT ? 32 / nsegk : 1;
+    const uint32_t row_bytes = (uint32_t)nblk * GB_Q4_BYTES;
+    const uint32_t chunk_bytes = row_bytes * rows_per_chunk;
+
+    constexpr bool HOIST = NPASS > 0;
+    static_assert(!HOIST || NB == 1, "hoisted activations exist for one activation row only");
+    uint64_t* my_bars = reinterpret_cast<uint64_t*>(smem) + warp * GEMV_MAX_STAGES;
+    uint64_t* act_bar = reinterpret_cast<uint64_t*>(smem) + GEMV_WARPS * GEMV_MAX_STAGES;
+    uint8_t* act_qs = smem + GEMV_BAR_BYTES;
+    const uint32_t act_qs_bytes = HOIST ? 0u : (uint32_t)NB * K, act_ds_bytes = HOIST ? 0u : (uint32_t)NB * nblk * 8;
+    uint8_t* act_ds = act_qs + act_qs_bytes;
+    uint8_t* ring = act_ds + ((act_ds_bytes + 127u) & ~127u) + (uint32_t)warp * stages * chunk_bytes;
+
+    // chunks are dealt round-robin over all warps of the grid
+    const int nchunks = (N + rows_per_chunk - 1) / rows_per_chunk;
+    const int gw = blockIdx.x * GEMV_WARPS + warp, tw = gridDim.x * GEMV_WARPS;
+    const int my_chunks = gw < nchunks ? (nchunks - gw + tw - 1) / tw : 0;
+    auto issue = [&](int j, int s) {
+        const int r0 = (gw + j * tw) * rows_per_chunk;
+        const uint32_t bytes = (uint32_t)min(rows_per_chunk, N - r0) * row_bytes;
+        mbar_expect_tx(&my_bars[s], bytes);
+        bulk_g2s(ring + (uint32_t)s * chunk_bytes, w + (size_t)r0 * row_bytes, bytes, &my_bars[s]);
+    };
+
+    // weights are not produced by the preceding kernel: prefetch them before the dependency wait
+    if (lane == 0) {
+        for (int s = 0; s < stages; s++) mbar_init(&my_bars[s], 1);
+        if (warp == 0 && !HOIST) mbar_init(act_bar, 1);
+        fence_proxy_async();
+        for (int s = 0; s < stages && s < my_chunks; s++) issue(s, s);
+    }
+    if (!HOIST) __syncthreads();  // act_bar is initialised
+    pdl_wait();  // the quantised activations (and whatever dst aliases) belong to the preceding kernels
+
+    bool ok = true;
+    int yh[HOIST ? NPASS : 1][HOIST ? 16 * SEG : 1];
+    float4 dh[HOIST ? NPASS : 1][HOIST ? SEG : 1];
+    if (HOIST) {
+        // every lane keeps its own activations in registers for the whole kernel
+#pragma unroll
+        for (int q = 0; q < NPASS; q++) {
+            const int sg = SPLIT ? (lane & (nsegk - 1)) : lane + 32 * q;
+            if (sg < nsegk && !(dbg & 2)) {
+                load_act<SEG>(xq, xds, nsegk, sg, yh[q], dh[q]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16 * SEG; i++) yh[q][i] = 0;
+#pragma unroll
+                for (int i = 0; i < SEG; i++) dh[q][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+    } else {
+        // one bulk copy each for the quants and the scales: the global layout is the shared one
+        if (threadIdx.x == 0) {
+            mbar_expect_tx(act_bar, act_qs_bytes + act_ds_bytes);
+            bulk_g2s(act_qs, xq, act_qs_bytes, act_bar);
+            bulk_g2s(act_ds, xds, act_ds_bytes, act_bar);
+        }
+        ok = mbar_wait_bounded(act_bar, 0);
+    }
+
+    for (int j = 0; j < my_chunks && ok; j++) {
+        const int s = j % stages;
+        ok = mbar_wait_bounded(&my_bars[s], (uint32_t)(j / stages) & 1u, (dbg >> 8) ? (uint32_t)(dbg >> 8) : 20000u);
+        if (!ok) break;
+        const uint8_t* buf = ring + (uint32_t)s * chunk_bytes;
+        const int row0 = (gw + j * tw) * rows_per_chunk;
+
+        float acc[NB];
+#pragma unroll
+        for (int b = 0; b < NB; b++) acc[b] = 0.0f;
+
+        if (dbg & 1) {
+            acc[0] = __uint_as_float(reinterpret_cast<const uint32_t*>(buf)[lane]);
+        } else if (HOIST) {
+#pragma unroll
+            for (int q = 0; q < NPASS; q++) {
+                const int sg = lane + 32 * q;  // SPLIT: NPASS == 1 and the chunk is exactly 32 segments
+                if (SPLIT || sg < nsegk) {
+                    uint32_t t[9 * SEG];
+                    load_segment<SEG>(buf + sg * (36 * SEG), t);
+#pragma unroll
+                    for (int p = 0; p < SEG; p++) acc[0] = pair_dot(t + 9 * p, yh[q] + 16 * p, dh[q][p], acc[0]);
+                }
+            }
+        } else {
+            for (int sg = lane; sg < (SPLIT ? 32 : nsegk); sg += 32) {
+                uint32_t t[9 * SEG];
+                load_segment<SEG>(buf + sg * (36 * SEG), t);
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    int y[16 * SEG];
+                    float4 d4[SEG];
+                    load_act<SEG>(act_qs + b * K, act_ds + b * nblk * 8, nsegk, SPLIT ? (sg & (nsegk - 1)) : sg, y, d4);
+#pragma unroll
+                    for (int p = 0; p < SEG; p++) acc[b] = pair_dot(t + 9 * p, y + 16 * p, d4[p], acc[b]);
+                }
+            }
+        }
+        // every lane has consumed the stage: refill it
+        __syncwarp();
+        if (lane == 0 && j + stages < my_chunks) issue(j + stages, s);
+
+        if (SPLIT) {
+            // lanes [r * nsegk, (r + 1) * nsegk) hold row r of the chunk
+            const int r = lane / nsegk;
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                float v = acc[b];
+                for (int o = nsegk >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if ((lane & (nsegk - 1)) == 0 && row0 + r < N && b < nbatch) dst[b * nb1 + row0 + r] = v;
+            }
+        } else {
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                const float v = gb_warp_sum(acc[b]);
+                if (lane == 0 && b < nbatch) dst[b * nb1 + row0] = v;
+            }
+        }
+    }
+    if (!ok && lane == 0) atomicExch(status, GALOIS_B200_E_TIMEOUT);
+}
+
+struct gemv_plan {
+    bool ok;
+    int nbt, seg, npass, stages, grid;
+    bool split;
+    size_t smem;
+};
+
+gemv_plan plan_gemv(const galois_b200_ctx* ctx, int64_t K, int64_t N, int64_t B) {
+    gemv_plan p{};
+    p.ok = false;
+    if (B < 1 || B > 4 || K % 256 != 0) return p;  // rows are whole multiples of 16 bytes for the bulk copies
+    p.nbt = B <= 1 ? 1 : (B <= 2 ? 2 : 4);
+    const int64_t npair = K / 64;
+    // Lane segment: 4 / 2 / 1 block pairs.  First choice: whole rows per pass (every lane busy).
+    // Else the (segment, passes) pair with the best lane utilisation; with one activation row it
+    // must keep at most 6 block pairs per lane so that the activations fit in registers.
+    const int max_seg = p.nbt == 1 ? 4 : 2;  // wider segments spill when activations are not hoisted
+    p.seg = 0;
+    for (int seg = max_seg; seg >= 1 && !p.seg; seg >>= 1) {
+        const int64_t nsegk = npair / seg;
+        if (npair % seg == 0 && nsegk <= 32 && (nsegk & (nsegk - 1)) == 0) p.seg = seg, p.split = true, p.npass = p.nbt == 1 ? 1 : 0;
+    }
+    if (!p.seg) {
+        double best = -1.0;
+        for (int seg = max_seg; seg >= 1; seg >>= 1) {
+            if (npair % seg) continue;
+            const int64_t nsegk = npair / seg, passes = (nsegk + 31) / 32;
+            const bool hoist = p.nbt == 1 && passes <= 3 && passes * seg <= 6;
+            const double util = (double)nsegk / (double)(passes * 32) + (hoist ? 1.0 : 0.0);
+            if (util > best + 0.02) best = util, p.seg = seg, p.split = false, p.npass = hoist ? (int)passes : 0;
+        }
+    }
+    if (!p.seg) return p;
+    const int64_t nsegk = npair / p.seg;
+    const int64_t rows_per_chunk = p.split ? 32 / nsegk : 1;
+    const size_t row_bytes = (size_t)(K / 32) * GB_Q4_BYTES;
+    const size_t chunk = row_bytes * rows_per_chunk;
+    const size_t act = p.npass > 0 ? 0 : (size_t)p.nbt * K + ((((size_t)p.nbt * (K / 32) * 8) + 127) & ~(size_t)127);
+    // two CTAs of one kernel per SM plus room for a third (of the next kernel): <= 72 KB per CTA
+    const size_t budget = (size_t)(ctx->tune_smem_kb > 0 ? ctx->tune_smem_kb : 72) * 1024;
+    if (GEMV_BAR_BYTES + act + (size_t)GEMV_WARPS * 2 * chunk > 200 * 1024) return p;
+    int stages = 2;
+    while (stages < GEMV_MAX_STAGES && GEMV_BAR_BYTES + act + (size_t)GEMV_WARPS * (stages + 1) * chunk <= budget) stages++;
+    if (ctx->tune_stages >= 2 && ctx->tune_stages <= GEMV_MAX_STAGES) stages = ctx->tune_stages;
+    p.stages = stages;
+    p.smem = GEMV_BAR_BYTES + act + (size_t)GEMV_WARPS * stages * chunk;
+    if (p.smem > 227 * 1024) return p;
+    const int64_t nchunks = (N + rows_per_chunk - 1) / rows_per_chunk;
+    const int cps = ctx->tune_ctas_per_sm > 0 ? ctx->tune_ctas_per_sm : 2;
+    int64_t grid = (int64_t)ctx->sm_count * cps;
+    if (grid > (nchunks + GEMV_WARPS - 1) / GEMV_WARPS) grid = (nchunks + GEMV_WARPS - 1) / GEMV_WARPS;
+    p.grid = (int)(grid < 1 ? 1 : grid);
+    p.ok = true;
+    return p;
+}
+
+// (NB, SEG, SPLIT, NPASS)
+#define GB_GEMV_INSTANCES(X)                                                        \
+    X(1, 4, true, 1) X(1, 2, true, 1) X(1, 1, true, 1)                               \
+    X(1, 4, false, 1) X(1, 2, false, 1) X(1, 2, false, 2) X(1, 2, false, 3)          \
+    X(1, 1, false, 1) X(1, 1, false, 2) X(1, 1, false, 3)                            \
+    X(1, 4, false, 0) X(1, 2, false, 0) X(1, 1, false, 0)                            \
+    X(2, 2, true, 0) X(2, 1, true, 0) X(2, 2, false, 0) X(2, 1, false, 0)            \
+    X(4, 2, true, 0) X(4, 1, true, 0) X(4, 2, false, 0) X(4, 1, false, 0)
+
+template <int NB, int SEG, bool SPLIT, int NPASS>
+cudaError_t gemv_attr() {
+    return cudaFuncSetAttribute(gemv_q4_0_kernel<NB, SEG, SPLIT, NPASS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                227 * 1024);
+}
+
+void pdl_config(const galois_b200_ctx* ctx, cudaLaunchConfig_t* cfg, cudaLaunchAttribute* at) {
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg->attrs = at;
+    cfg->numAttrs = ctx->pdl ? 1 : 0;
+    cfg->stream = ctx->stream;
+}
+
+template <int NB, int SEG, bool SPLIT, int NPASS>
+int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, const uint8_t* xq, const uint8_t* xds, float* dst,
+                int nb1, int K, int N, int B) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute at[1];
+    pdl_config(ctx, &cfg, at);
+    cfg.gridDim = dim3((unsigned)p.grid);
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = p.smem;
+    GB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_0_kernel<NB, SEG, SPLIT, NPASS>, w, xq, xds, dst, nb1, K, N, B, p.stages,
+                                    ctx->dev_status, ctx->tune_dbg));
+    ctx->launches++;
+    return 0;
+}
+
+template <int SEG>
+int launch_quantize(galois_b200_ctx* ctx, const float* x, int x_stride, int K, int B, uint8_t* qs, uint8_t* ds) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute at[1];
+    pdl_config(ctx, &cfg, at);
+    cfg.gridDim = dim3((unsigned)((K / 32 * 8 + 255) / 256), (unsigned)B);
+    cfg.blockDim = dim3(256);
+    GB_CUDA(ctx, cudaLaunchKernelEx(&cfg, quantize_q8_pm_kernel<SEG>, x, x_stride, K, B, qs, ds));
+    ctx->launches++;
+    return 0;
+}
+
+}  // namespace
+
+int gb_gemv_init(galois_b200_ctx* ctx) {
+#define X(NB_, SEG_, SPLIT_, NP_) GB_CUDA(ctx, (gemv_attr<NB_, SEG_, SPLIT_, NP_>()));
+    GB_GEMV_INSTANCES(X)
+#undef X
+    return 0;
+}
+
+bool gb_gemv_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
+                       const galois_dim* dd) {
+    const int64_t K = wd->ne[0], N = wd->ne[1];
+    if (K % 256 != 0 || K > 65536 || N < 1 || N > (1 << 30)) return false;
+    if ((uintptr_t)w % 16 != 0) return false;  // rows must start on 16-byte boundaries for the bulk copies
+    if (wd->ne[2] != 1 || wd->ne[3] != 1 || xd->ne[2] != 1 || xd->ne[3] != 1) return false;
+    if (wd->nb[1] != K / GB_QK) return false;
+    if (xd->ne[1] < 1 || xd->ne[1] > 4) return false;
+    if (dd->nb[1] > (1 << 30) || xd->nb[1] > (1 << 30)) return false;
+    if ((uintptr_t)x % 16 != 0 || xd->nb[1] % 4 != 0) return false;  // float4 loads in the quantiser
+    return plan_gemv(ctx, K, N, xd->ne[1]).ok;
+}
+
+size_t gb_gemv_scratch_bytes(int64_t K, int64_t B) {
+    const size_t qs = (((size_t)B * K) + 255) & ~(size_t)255;
+    return qs + (size_t)B * (K / 32) * 8;
+}
+
+int gb_gemv_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
+                 const galois_dim* dd, void* scratch) {
+    const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
+    const gemv_plan p = plan_gemv(ctx, K, N, B);
+    if (!p.ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: shape not supported by the streaming GEMV");
+    uint8_t* qs = (uint8_t*)scratch;
+    uint8_t* ds = qs + ((((size_t)B * K) + 255) & ~(size_t)255);
+    const int xs = (int)xd->nb[1];
+    int rc = p.seg == 4 ? launch_quantize<4>(ctx, x, xs, K, B, qs, ds)
+                        : (p.seg == 2 ? launch_quantize<2>(ctx, x, xs, K, B, qs, ds) : launch_quantize<1>(ctx, x, xs, K, B, qs, ds));
+    if (rc) return rc;
+    const uint8_t* wb = (const uint8_t*)w;
+    const int nb1 = (int)dd->nb[1];
+#define X(NB_, SEG_, SPLIT_, NP_)                                                   \
+    if (p.nbt == NB_ && p.seg == SEG_ && p.split == SPLIT_ && p.npass == NP_)       \
+        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, qs, ds, dst, nb1, K, N, B);
+    GB_GEMV_INSTANCES(X)
+#undef X
+    return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: no streaming-GEMV instance for this shape");
+}

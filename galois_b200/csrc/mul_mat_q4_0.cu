@@ -21,6 +21,7 @@
 //                     conflicts) and realigned with funnel shifts.
 #include "common.cuh"
 #include "mul_mat_q4_0.cuh"
+#include "ptx.cuh"
 #include "quantize.cuh"
 
 namespace {
@@ -113,50 +114,6 @@ __global__ void block_isums_kernel(const uint8_t* __restrict__ w, const uint8_t*
 }
 
 // ---------------------------------------------------------------- bulk-copy kernel
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// One try_wait: the thread may be suspended by the hardware for up to `hint_ns` before it
-// returns false.
-__device__ __forceinline__ uint32_t mbar_test(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
-        : "memory");
-    return ok;
-}
-// Waits for the phase with the given parity; gives up after about two seconds and returns
-// false (the caller records a timeout status and stops).
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    const long long t0 = clock64();
-    while (!mbar_test(bar, parity, 20000u)) {
-        if (clock64() - t0 > (1ll << 32)) return false;
-    }
-    return true;
-}
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-// a (u8 x4) . b (s8 x4) + c
-__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
-    int d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-
 // One 36-byte block pair (nine aligned words t[0..8]: {d0 | qs0[0:2]}, qs0[2:14], {qs0[14:16] | d1},
 // qs1[0:16]) against the 64 int8 activations y[0..15] of the same two blocks.
 // ds = {dx0, bits(-8 * sum y0), dx1, bits(-8 * sum y1)}.  The high nibbles are used in place

@@ -73,10 +73,18 @@ const char* galois_b200_last_error(galois_b200_ctx* ctx);
 /* Number of kernels this context has launched so far (for benches). */
 int64_t galois_b200_launch_count(galois_b200_ctx* ctx);
 /* Selects among equivalent implementations of the Q4_0 mat-mul:
- * 0 = automatic, 1 = generic direct-load kernel, 2 = bulk-copy pipelined GEMV,
+ * 0 = automatic, 1 = generic direct-load kernel, 2 = bulk-copy streaming GEMV (batch <= 8),
  * 3 = tensor-core (tcgen05) GEMM.  Unsupported shapes for a forced variant
  * return GALOIS_B200_E_LAYOUT. */
 int galois_b200_set_mul_mat_variant(galois_b200_ctx* ctx, int variant);
+
+/* Programmatic dependent launch (default on).  The streaming mat-mul kernels are launched so
+ * that they may start while the preceding kernel of the stream is still running: they prefetch
+ * WEIGHT bytes at once and wait for the preceding kernel only before they read activations or
+ * write results.  Turn it off when a weight tensor is produced by a kernel enqueued right
+ * before the mat-mul that consumes it (weights uploaded with galois_b200_htod or any memcpy
+ * are always safe). */
+int galois_b200_set_pdl(galois_b200_ctx* ctx, int on);
 
 /* Kernel timing for benches.  While enabled, every galois_b200_mul_mat_q4_0_f32
  * call brackets its mat-mul kernel (not the activation quantiser) with CUDA

@@ -125,12 +125,41 @@ def test_mul_mat_q4_0_direct(gb, dev, oracle, n, k, b):
     _mul_mat_case(gb, dev, oracle, n, k, b, 7000 + n + k + b, 1)
 
 
-# variant 2 = bulk-copy pipelined GEMV (K % 256 == 0, batch <= 8)
-@pytest.mark.parametrize("n,k,b", [(4096, 4096, 1), (11008, 4096, 1), (4096, 11008, 1), (11008, 4096, 4),
-                                   (4096, 11008, 4), (1, 256, 1), (3, 256, 2), (1185, 512, 3), (2371, 4096, 5),
-                                   (149, 8192, 7), (32000, 4096, 8)])
-def test_mul_mat_q4_0_bulk(gb, dev, oracle, n, k, b):
+# variant 2 = bulk-copy streaming kernels (K % 256 == 0): fused-quantiser GEMV for batch <= 2,
+# streaming GEMV on pre-quantised activations for batch 3-4, wide-batch kernel for 5-8
+@pytest.mark.parametrize("n,k,b", [(4096, 4096, 1), (11008, 4096, 1), (4096, 11008, 1), (11008, 4096, 2), (11008, 4096, 4),
+                                   (4096, 11008, 2), (4096, 11008, 4), (1, 256, 1), (3, 256, 2), (77, 512, 1), (1185, 512, 3),
+                                   (130, 1024, 1), (131, 2048, 2), (2371, 4096, 4), (2371, 4096, 5), (301, 5120, 1), (300, 768, 2),
+                                   (149, 8192, 1), (149, 8192, 3), (149, 8192, 7), (500, 14336, 1), (32000, 4096, 8)])
+def test_mul_mat_q4_0_streaming(gb, dev, oracle, n, k, b):
     _mul_mat_case(gb, dev, oracle, n, k, b, 8000 + n + k + b, 2)
+
+
+def test_mul_mat_q4_0_dependent_launch_ordering(gb, dev, oracle):
+    """The streaming GEMV starts before the kernel in front of it has finished (programmatic
+    dependent launch) and must still see that kernel's output: scale -> mat-mul -> mat-mul chains,
+    with and without the overlap, give the oracle's numbers."""
+    G = gb.Device.Gpu(dev)
+    n, k = 4096, 4096
+    w1 = oracle.quantize_q4_0(oracle.fill_normal(n * k, 41, 0, 0.02).reshape(n, k))
+    w2 = oracle.quantize_q4_0(oracle.fill_normal(n * k, 42, 0, 0.02).reshape(n, k))
+    x0 = oracle.fill_normal(k, 43).reshape(1, k)
+    x1 = oracle.scale(x0, 3.0)
+    h = oracle.mul_mat_q4_0(w1, x1)
+    want = oracle.mul_mat_q4_0(w2, h)
+    t1, t2 = _q4(gb, dev, w1, n, k), _q4(gb, dev, w2, n, k)
+    three = gb.Tensor.from_numpy(np.array([3.0], np.float32), gb.GGmlType.F32, gb.Device.Cpu())
+    for pdl in (1, 0, 1):
+        assert gb.lib.galois_b200_set_pdl(dev.ctx, pdl) == 0
+        for _ in range(3):
+            xs = gb.Tensor.zeros((k, 1), gb.GGmlType.F32, G)
+            hid = gb.Tensor.zeros((n, 1), gb.GGmlType.F32, G)
+            out = gb.Tensor.zeros((n, 1), gb.GGmlType.F32, G)
+            gb.galois_scale(_gpu(gb, dev, x0), three, xs)
+            gb.galois_matmul(t1, xs, hid)
+            gb.galois_matmul(t2, hid, out)
+            assert_close(out.to_numpy(), want)
+    gb.lib.galois_b200_set_pdl(dev.ctx, 1)
 
 
 # automatic dispatch over the BASELINE shapes (configs 2, 3, 5) incl. large batches
