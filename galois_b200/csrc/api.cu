@@ -125,6 +125,7 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
         if ((q = strstr(t, "cps="))) ctx->tune_ctas_per_sm = atoi(q + 4);
         if ((q = strstr(t, "pdl="))) ctx->pdl = atoi(q + 4);
         if ((q = strstr(t, "dbg="))) ctx->tune_dbg = atoi(q + 4);
+        if ((q = strstr(t, "cluster="))) ctx->tune_cluster = atoi(q + 8);
     }
 
     // f16 tables of GLOBAL_CPU_DEVICE_CACHE (src/op.rs:227-252): entry i =
@@ -302,10 +303,7 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
     const bool gemv = variant == 2 && gemv_ok;
     gb_q8_soa xq = {nullptr, nullptr};
     void* scratch = nullptr;
-    if (gemv) {
-        rc = gb_scratch(ctx, gb_gemv_scratch_bytes(K, nrows), &scratch);
-        if (rc) return rc;
-    } else {
+    if (!gemv) {
         size_t need = gb_q8_soa_bytes(K, nrows);
         if (variant == 3) need += gb_mm_tc_scratch_bytes(wd, xd);
         rc = gb_scratch(ctx, need, &scratch);
@@ -318,7 +316,7 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
     if (variant == 3)
         rc = gb_mm_q4_0_tc(ctx, w, wd, xq, xd, dst, dd, (uint8_t*)scratch + gb_q8_soa_bytes(K, nrows));
     else if (gemv)
-        rc = gb_gemv_q4_0(ctx, w, wd, x, xd, dst, dd, scratch);
+        rc = gb_gemv_q4_0(ctx, w, wd, x, xd, dst, dd);
     else if (variant == 2)
         rc = gb_mmv_q4_0_bulk(ctx, w, wd, xq, xd, dst, dd);
     else

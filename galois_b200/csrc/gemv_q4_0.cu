@@ -1,18 +1,21 @@
-// Streaming Q4_0 x Q8_0 GEMV for decode (batch 1-4): a small quantiser kernel + the GEMV.
+// Streaming Q4_0 x Q8_0 GEMV for decode (batch 1-4): ONE kernel per mat-mul, no scratch memory.
 //
-//   * the f32 activations are quantised to Q8_0 once (bit-exact with
-//     <BlockQ8_0 as QuantType>::from_f32, src/ggml_quants.rs:736-764 of galois) into a scratch
-//     laid out exactly as the GEMV wants to read it; with one activation row every lane keeps
-//     its share of them in registers for the whole kernel, so the main loop reads only weights;
+//   * the f32 activations are quantised to Q8_0 inside the kernel, bit-exact with
+//     <BlockQ8_0 as QuantType>::from_f32 (src/ggml_quants.rs:736-764 of galois).  The CTAs of a
+//     thread-block cluster split that work: each quantises 1/C of the row(s) and stores the result
+//     into the shared memory of every CTA of its cluster (distributed shared memory), so the cost
+//     per CTA is 1/C of the row and nothing goes through global memory;
+//   * with one activation row every lane then keeps its share of the quants in registers for the
+//     whole kernel, so the main loop reads only weights;
 //   * the 18-byte Q4_0 blocks stream HBM -> shared memory through per-warp rings of
 //     cp.async.bulk copies (1-D bulk copies completing on mbarriers, no multicast); a lane
 //     reads a 144 / 72 / 36-byte segment (8 / 4 / 2 blocks) with 128 / 64 / 32-bit loads whose
 //     lane stride is an odd number of load widths, so shared-memory reads are conflict free;
 //   * integer dot products with dp4a (exact), f32 scale accumulation, warp shuffles;
-//   * programmatic dependent launch: both kernels release their dependents at once and the GEMV
-//     prefetches its first weight stages BEFORE waiting for the kernels in front of it, so launch
-//     latency and the first DRAM round trip hide behind the previous mat-mul.  Small CTAs (128 threads,
-//     well under half an SM's shared memory) let CTAs of consecutive kernels share an SM.
+//   * programmatic dependent launch: the kernel releases its dependents at once and prefetches its
+//     first weight stages BEFORE waiting for the kernel in front of it, so launch latency and the
+//     first DRAM round trip hide behind the previous op.  Small CTAs (128 threads, well under half
+//     an SM's shared memory) let CTAs of consecutive kernels share an SM.
 //
 // Numerics: MatMul::f_q_f32_f32::<BlockQ4_0> (src/op.rs:1383-1598) with
 // BlockQ4_0::vec_dot_q8_0 (src/ggml_quants.rs:156-172); only the order of the f32 additions
@@ -89,44 +92,66 @@ __device__ __forceinline__ void load_act(const uint8_t* qs, const uint8_t* ds, i
     for (int j = 0; j < SEG; j++) d4[j] = *reinterpret_cast<const float4*>(ds + (j * nsegk + s) * 16);
 }
 
-// Quantises `nrows` rows of K floats (bit-exact with <BlockQ8_0 as QuantType>::from_f32,
-// src/ggml_quants.rs:736-764) into the piece-major layout in global memory: row b's quants at
-// qs + b * K, its {d, -8 * sum} pairs at ds + b * (K/32) * 8.  Eight lanes own a block (four
-// consecutive floats each); one block per 8-lane group, all loads of a thread issued at once.
+// Cluster-cooperative Q8_0 quantiser.  The NB * K/32 blocks are split evenly over the CTAs of the
+// cluster; eight lanes own a block (four consecutive floats each).  Every result word is stored
+// into the activation area of all `csize` CTAs (this one included) in the piece-major layout:
+// row b's quants at act_qs + b * K, its {d, -8 * sum} pairs at act_ds + b * (K/32) * 8.
 template <int SEG>
-__global__ void __launch_bounds__(256) quantize_q8_pm_kernel(const float* __restrict__ x, int x_stride, int K, int nrows,
-                                                             uint8_t* __restrict__ qs_out, uint8_t* __restrict__ ds_out) {
-    pdl_launch_dependents();
-    const int nblk = K >> 5, nsegk = nblk / (2 * SEG);
+__device__ __forceinline__ void quantize_rows_cluster(const float* __restrict__ x, int x_stride, int K, int nbatch, int NB,
+                                                      uint8_t* act_qs, uint8_t* act_ds, int nsegk, uint32_t crank, uint32_t csize) {
+    const int nblk = K >> 5;
+    const int total = NB * nblk;
+    const int per = (total + (int)csize - 1) / (int)csize;
+    const int first = (int)crank * per, last = min(first + per, total);
     const int sub = threadIdx.x & 7;
-    const int blk = (blockIdx.x * 256 + threadIdx.x) >> 3;  // block index within the row
-    const int b = blockIdx.y;
-    const bool live = blk < nblk;
-    pdl_wait();  // x belongs to the preceding kernel; the scratch may still be read by it
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (live) v = __ldg(reinterpret_cast<const float4*>(x + (size_t)b * x_stride + blk * 32) + sub);
-    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    const int groups = GEMV_THREADS >> 3;
+    const uint32_t qs_base = smem_u32(act_qs), ds_base = smem_u32(act_ds);
+    // loop bounds are uniform per warp (every lane takes part in the shuffles); U blocks per lane
+    // group are loaded before any is processed, so a CTA's whole slice is one round trip to L2
+    constexpr int U = 4;
+    for (int g0 = first + (int)(threadIdx.x >> 3);; g0 += U * groups) {
+        if (g0 - (int)((threadIdx.x & 31) >> 3) >= last) break;
+        float4 v[U];
 #pragma unroll
-    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    const float d = __fdiv_rn(amax, 127.0f);
-    const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
-    // `as i8` in Rust saturates and maps NaN to 0; so does (int) followed by the clamp
-    const int q0 = max(-128, min(127, (int)roundf(__fmul_rn(v.x, id))));
-    const int q1 = max(-128, min(127, (int)roundf(__fmul_rn(v.y, id))));
-    const int q2 = max(-128, min(127, (int)roundf(__fmul_rn(v.z, id))));
-    const int q3 = max(-128, min(127, (int)roundf(__fmul_rn(v.w, id))));
-    int s = q0 + q1 + q2 + q3;
+        for (int u = 0; u < U; u++) {
+            const int g = g0 + u * groups;
+            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (g < last) {
+                const int b = g / nblk, blk = g - b * nblk;
+                if (b < nbatch) v[u] = __ldg(reinterpret_cast<const float4*>(x + (size_t)b * x_stride + blk * 32) + sub);
+            }
+        }
 #pragma unroll
-    for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (live) {
-        const int seg = blk / (2 * SEG), bi = blk % (2 * SEG);
-        const uint32_t packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
-                                ((uint32_t)(q3 & 0xff) << 24);
-        const int piece = 2 * bi + (sub >> 2);
-        *reinterpret_cast<uint32_t*>(qs_out + (size_t)b * K + (piece * nsegk + seg) * 16 + (sub & 3) * 4) = packed;
-        if (sub == 0)
-            *reinterpret_cast<float2*>(ds_out + (size_t)b * nblk * 8 + ((bi >> 1) * nsegk + seg) * 16 + (bi & 1) * 8) =
-                make_float2(__half2float(__float2half_rn(d)), __int_as_float(-8 * s));
+        for (int u = 0; u < U; u++) {
+            const int g = g0 + u * groups;
+            if (g - (int)((threadIdx.x & 31) >> 3) >= last) break;  // uniform per warp
+            float amax = fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float d = __fdiv_rn(amax, 127.0f);
+            const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+            // `as i8` in Rust saturates and maps NaN to 0; so does (int) followed by the clamp
+            const int q0 = max(-128, min(127, (int)roundf(__fmul_rn(v[u].x, id))));
+            const int q1 = max(-128, min(127, (int)roundf(__fmul_rn(v[u].y, id))));
+            const int q2 = max(-128, min(127, (int)roundf(__fmul_rn(v[u].z, id))));
+            const int q3 = max(-128, min(127, (int)roundf(__fmul_rn(v[u].w, id))));
+            int s = q0 + q1 + q2 + q3;
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (g < last) {
+                const int b = g / nblk, blk = g - b * nblk;
+                const int seg = blk / (2 * SEG), bi = blk % (2 * SEG);
+                const uint32_t packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
+                                        ((uint32_t)(q3 & 0xff) << 24);
+                const uint32_t qoff = (uint32_t)b * K + ((2 * bi + (sub >> 2)) * nsegk + seg) * 16 + (sub & 3) * 4;
+                const uint32_t doff = (uint32_t)b * nblk * 8 + ((bi >> 1) * nsegk + seg) * 16 + (bi & 1) * 8;
+                const uint32_t dbits = __float_as_uint(__half2float(__float2half_rn(d)));
+                for (uint32_t r = 0; r < csize; r++) {
+                    cluster_st_u32(cluster_map(qs_base + qoff, r), packed);
+                    if (sub == 0) cluster_st_v2(cluster_map(ds_base + doff, r), dbits, (uint32_t)(-8 * s));
+                }
+            }
+        }
     }
 }
 
@@ -140,12 +165,10 @@ __global__ void __launch_bounds__(256) quantize_q8_pm_kernel(const float* __rest
 //               so the main loop reads nothing but weights;
 //        0   : activations are read from shared memory in every pass.
 //
-// xq / xds: the activations quantised by quantize_q8_pm_kernel<SEG> (piece-major, NB rows).
 // Shared memory: [0, 256) mbarriers | act qs (NB * K) | act ds (NB * K/32 * 8) | GEMV_WARPS * stages * chunk.
 template <int NB, int SEG, bool SPLIT, int NPASS>
 __global__ void __launch_bounds__(GEMV_THREADS)
-    gemv_q4_0_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ xq, const uint8_t* __restrict__ xds,
-                     float* __restrict__ dst, int nb1, int K, int N, int nbatch, int stages,
+    gemv_q4_0_kernel(const uint8_t* __restrict__ w, const float* __restrict__ x, int x_stride, float* __restrict__ dst, int nb1, int K, int N, int nbatch, int stages,
                      int* __restrict__ status, int dbg) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
@@ -160,9 +183,8 @@ __global__ void __launch_bounds__(GEMV_THREADS)
     constexpr bool HOIST = NPASS > 0;
     static_assert(!HOIST || NB == 1, "hoisted activations exist for one activation row only");
     uint64_t* my_bars = reinterpret_cast<uint64_t*>(smem) + warp * GEMV_MAX_STAGES;
-    uint64_t* act_bar = reinterpret_cast<uint64_t*>(smem) + GEMV_WARPS * GEMV_MAX_STAGES;
     uint8_t* act_qs = smem + GEMV_BAR_BYTES;
-    const uint32_t act_qs_bytes = HOIST ? 0u : (uint32_t)NB * K, act_ds_bytes = HOIST ? 0u : (uint32_t)NB * nblk * 8;
+    const uint32_t act_qs_bytes = (uint32_t)NB * K, act_ds_bytes = (uint32_t)NB * nblk * 8;
     uint8_t* act_ds = act_qs + act_qs_bytes;
     uint8_t* ring = act_ds + ((act_ds_bytes + 127u) & ~127u) + (uint32_t)warp * stages * chunk_bytes;
 
@@ -180,12 +202,16 @@ __global__ void __launch_bounds__(GEMV_THREADS)
     // weights are not produced by the preceding kernel: prefetch them before the dependency wait
     if (lane == 0) {
         for (int s = 0; s < stages; s++) mbar_init(&my_bars[s], 1);
-        if (warp == 0 && !HOIST) mbar_init(act_bar, 1);
         fence_proxy_async();
         for (int s = 0; s < stages && s < my_chunks; s++) issue(s, s);
     }
-    if (!HOIST) __syncthreads();  // act_bar is initialised
-    pdl_wait();  // the quantised activations (and whatever dst aliases) belong to the preceding kernels
+    const uint32_t crank = cluster_ctarank(), csize = cluster_nctarank();
+    cluster_arrive();  // this CTA's shared memory exists
+    pdl_wait();        // the activations (and whatever dst aliases) belong to the preceding kernels
+    cluster_wait();    // so does every peer's
+    if (!(dbg & 2)) quantize_rows_cluster<SEG>(x, x_stride, K, nbatch, NB, act_qs, act_ds, nsegk, crank, csize);
+    cluster_arrive();
+    cluster_wait();    // all slices of the quantised activations have landed in this CTA
 
     bool ok = true;
     int yh[HOIST ? NPASS : 1][HOIST ? 16 * SEG : 1];
@@ -195,8 +221,8 @@ __global__ void __launch_bounds__(GEMV_THREADS)
 #pragma unroll
         for (int q = 0; q < NPASS; q++) {
             const int sg = SPLIT ? (lane & (nsegk - 1)) : lane + 32 * q;
-            if (sg < nsegk && !(dbg & 2)) {
-                load_act<SEG>(xq, xds, nsegk, sg, yh[q], dh[q]);
+            if (sg < nsegk) {
+                load_act<SEG>(act_qs, act_ds, nsegk, sg, yh[q], dh[q]);
             } else {
 #pragma unroll
                 for (int i = 0; i < 16 * SEG; i++) yh[q][i] = 0;
@@ -204,14 +230,6 @@ __global__ void __launch_bounds__(GEMV_THREADS)
                 for (int i = 0; i < SEG; i++) dh[q][i] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
-    } else {
-        // one bulk copy each for the quants and the scales: the global layout is the shared one
-        if (threadIdx.x == 0) {
-            mbar_expect_tx(act_bar, act_qs_bytes + act_ds_bytes);
-            bulk_g2s(act_qs, xq, act_qs_bytes, act_bar);
-            bulk_g2s(act_ds, xds, act_ds_bytes, act_bar);
-        }
-        ok = mbar_wait_bounded(act_bar, 0);
     }
 
     for (int j = 0; j < my_chunks && ok; j++) {
@@ -278,7 +296,7 @@ __global__ void __launch_bounds__(GEMV_THREADS)
 
 struct gemv_plan {
     bool ok;
-    int nbt, seg, npass, stages, grid;
+    int nbt, seg, npass, stages, grid, cluster;
     bool split;
     size_t smem;
 };
@@ -313,7 +331,7 @@ gemv_plan plan_gemv(const galois_b200_ctx* ctx, int64_t K, int64_t N, int64_t B)
     const int64_t rows_per_chunk = p.split ? 32 / nsegk : 1;
     const size_t row_bytes = (size_t)(K / 32) * GB_Q4_BYTES;
     const size_t chunk = row_bytes * rows_per_chunk;
-    const size_t act = p.npass > 0 ? 0 : (size_t)p.nbt * K + ((((size_t)p.nbt * (K / 32) * 8) + 127) & ~(size_t)127);
+    const size_t act = (size_t)p.nbt * K + ((((size_t)p.nbt * (K / 32) * 8) + 127) & ~(size_t)127);
     // two CTAs of one kernel per SM plus room for a third (of the next kernel): <= 72 KB per CTA
     const size_t budget = (size_t)(ctx->tune_smem_kb > 0 ? ctx->tune_smem_kb : 72) * 1024;
     if (GEMV_BAR_BYTES + act + (size_t)GEMV_WARPS * 2 * chunk > 200 * 1024) return p;
@@ -327,7 +345,12 @@ gemv_plan plan_gemv(const galois_b200_ctx* ctx, int64_t K, int64_t N, int64_t B)
     const int cps = ctx->tune_ctas_per_sm > 0 ? ctx->tune_ctas_per_sm : 2;
     int64_t grid = (int64_t)ctx->sm_count * cps;
     if (grid > (nchunks + GEMV_WARPS - 1) / GEMV_WARPS) grid = (nchunks + GEMV_WARPS - 1) / GEMV_WARPS;
-    p.grid = (int)(grid < 1 ? 1 : grid);
+    if (grid < 1) grid = 1;
+    // the grid is a whole number of clusters; the CTAs of a cluster share the quantiser's work
+    int cluster = (ctx->tune_cluster == 1 || ctx->tune_cluster == 2 || ctx->tune_cluster == 4 || ctx->tune_cluster == 8) ? ctx->tune_cluster : 8;
+    while (cluster > 1 && grid < cluster) cluster >>= 1;
+    p.cluster = cluster;
+    p.grid = (int)(grid / cluster * cluster);
     p.ok = true;
     return p;
 }
@@ -347,37 +370,30 @@ cudaError_t gemv_attr() {
                                 227 * 1024);
 }
 
-void pdl_config(const galois_b200_ctx* ctx, cudaLaunchConfig_t* cfg, cudaLaunchAttribute* at) {
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg->attrs = at;
-    cfg->numAttrs = ctx->pdl ? 1 : 0;
-    cfg->stream = ctx->stream;
-}
-
 template <int NB, int SEG, bool SPLIT, int NPASS>
-int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, const uint8_t* xq, const uint8_t* xds, float* dst,
-                int nb1, int K, int N, int B) {
+int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, const float* x, int x_stride, float* dst, int nb1,
+                int K, int N, int B) {
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute at[1];
-    pdl_config(ctx, &cfg, at);
+    cudaLaunchAttribute at[2];
+    int na = 0;
+    at[na].id = cudaLaunchAttributeClusterDimension;
+    at[na].val.clusterDim.x = (unsigned)p.cluster;
+    at[na].val.clusterDim.y = 1;
+    at[na].val.clusterDim.z = 1;
+    na++;
+    if (ctx->pdl) {
+        at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    cfg.attrs = at;
+    cfg.numAttrs = na;
+    cfg.stream = ctx->stream;
     cfg.gridDim = dim3((unsigned)p.grid);
     cfg.blockDim = dim3(GEMV_THREADS);
     cfg.dynamicSmemBytes = p.smem;
-    GB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_0_kernel<NB, SEG, SPLIT, NPASS>, w, xq, xds, dst, nb1, K, N, B, p.stages,
+    GB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_0_kernel<NB, SEG, SPLIT, NPASS>, w, x, x_stride, dst, nb1, K, N, B, p.stages,
                                     ctx->dev_status, ctx->tune_dbg));
-    ctx->launches++;
-    return 0;
-}
-
-template <int SEG>
-int launch_quantize(galois_b200_ctx* ctx, const float* x, int x_stride, int K, int B, uint8_t* qs, uint8_t* ds) {
-    cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute at[1];
-    pdl_config(ctx, &cfg, at);
-    cfg.gridDim = dim3((unsigned)((K / 32 * 8 + 255) / 256), (unsigned)B);
-    cfg.blockDim = dim3(256);
-    GB_CUDA(ctx, cudaLaunchKernelEx(&cfg, quantize_q8_pm_kernel<SEG>, x, x_stride, K, B, qs, ds));
     ctx->launches++;
     return 0;
 }
@@ -404,27 +420,16 @@ bool gb_gemv_supported(const galois_b200_ctx* ctx, const void* w, const galois_d
     return plan_gemv(ctx, K, N, xd->ne[1]).ok;
 }
 
-size_t gb_gemv_scratch_bytes(int64_t K, int64_t B) {
-    const size_t qs = (((size_t)B * K) + 255) & ~(size_t)255;
-    return qs + (size_t)B * (K / 32) * 8;
-}
-
 int gb_gemv_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
-                 const galois_dim* dd, void* scratch) {
+                 const galois_dim* dd) {
     const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
     const gemv_plan p = plan_gemv(ctx, K, N, B);
     if (!p.ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: shape not supported by the streaming GEMV");
-    uint8_t* qs = (uint8_t*)scratch;
-    uint8_t* ds = qs + ((((size_t)B * K) + 255) & ~(size_t)255);
-    const int xs = (int)xd->nb[1];
-    int rc = p.seg == 4 ? launch_quantize<4>(ctx, x, xs, K, B, qs, ds)
-                        : (p.seg == 2 ? launch_quantize<2>(ctx, x, xs, K, B, qs, ds) : launch_quantize<1>(ctx, x, xs, K, B, qs, ds));
-    if (rc) return rc;
     const uint8_t* wb = (const uint8_t*)w;
-    const int nb1 = (int)dd->nb[1];
+    const int nb1 = (int)dd->nb[1], xs = (int)xd->nb[1];
 #define X(NB_, SEG_, SPLIT_, NP_)                                                   \
     if (p.nbt == NB_ && p.seg == SEG_ && p.split == SPLIT_ && p.npass == NP_)       \
-        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, qs, ds, dst, nb1, K, N, B);
+        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, x, xs, dst, nb1, K, N, B);
     GB_GEMV_INSTANCES(X)
 #undef X
     return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: no streaming-GEMV instance for this shape");

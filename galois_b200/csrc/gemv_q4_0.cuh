@@ -8,9 +8,7 @@ int gb_gemv_init(galois_b200_ctx* ctx);
 // aligned rows (K % 256 == 0), batch <= 4, 16-byte aligned f32 activations.
 bool gb_gemv_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
                        const galois_dim* dd);
-// Scratch the quantised activations of B rows of K floats need.
-size_t gb_gemv_scratch_bytes(int64_t K, int64_t B);
-// Quantises x into `scratch` and runs the GEMV (two launches, both with programmatic
-// dependent launch when the context allows it).
+// One launch: quantises x inside the kernel and runs the GEMV (cluster launch, with programmatic
+// dependent launch when the context allows it).  Needs no scratch memory.
 int gb_gemv_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
-                 const galois_dim* dd, void* scratch);
+                 const galois_dim* dd);
