@@ -126,6 +126,7 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
         if ((q = strstr(t, "pdl="))) ctx->pdl = atoi(q + 4);
         if ((q = strstr(t, "dbg="))) ctx->tune_dbg = atoi(q + 4);
         if ((q = strstr(t, "cluster="))) ctx->tune_cluster = atoi(q + 8);
+        if ((q = strstr(t, "variant="))) ctx->variant = atoi(q + 8);
     }
 
     // f16 tables of GLOBAL_CPU_DEVICE_CACHE (src/op.rs:227-252): entry i =
@@ -292,21 +293,22 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
         GB_CUDA(ctx, cudaMemsetAsync(dst, 0, (size_t)gb_nelements(dd) * sizeof(float), ctx->stream));
         return 0;
     }
-    const bool tc_ok = gb_mm_tc_supported(ctx, w, wd, xd, dd);
+    const bool tc_ok = gb_mm_tc_supported(ctx, w, wd, x, xd, dd);
     const bool gemv_ok = gb_gemv_supported(ctx, w, wd, x, xd, dd);
     const bool bulk_ok = gb_mmv_bulk_supported(ctx, w, wd, xd, dd);
     int variant = ctx->variant;
     if (variant == 0) variant = (tc_ok && xd->ne[1] >= GB_TC_MIN_BATCH) ? 3 : ((gemv_ok || bulk_ok) ? 2 : 1);
     if (variant == 2 && !(gemv_ok || bulk_ok)) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: streaming variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned base, batch <= 8");
-    if (variant == 3 && !tc_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: tensor-core variant needs 2-D contiguous weights, K %% 128 == 0, 16-byte aligned base");
+    if (variant == 3 && !tc_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: tensor-core variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned operands");
 
     const bool gemv = variant == 2 && gemv_ok;
     gb_q8_soa xq = {nullptr, nullptr};
     void* scratch = nullptr;
-    if (!gemv) {
-        size_t need = gb_q8_soa_bytes(K, nrows);
-        if (variant == 3) need += gb_mm_tc_scratch_bytes(wd, xd);
-        rc = gb_scratch(ctx, need, &scratch);
+    if (variant == 3) {
+        rc = gb_scratch(ctx, gb_mm_tc_scratch_bytes(wd, xd), &scratch);
+        if (rc) return rc;
+    } else if (!gemv) {
+        rc = gb_scratch(ctx, gb_q8_soa_bytes(K, nrows), &scratch);
         if (rc) return rc;
         rc = gb_quantize_q8_soa(ctx, x, xd, scratch, &xq);
         if (rc) return rc;
@@ -314,7 +316,7 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
     const bool prof = ctx->profiling && ctx->prof_n < GB_PROF_MAX;
     if (prof) GB_CUDA(ctx, cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream));
     if (variant == 3)
-        rc = gb_mm_q4_0_tc(ctx, w, wd, xq, xd, dst, dd, (uint8_t*)scratch + gb_q8_soa_bytes(K, nrows));
+        rc = gb_mm_q4_0_tc(ctx, w, wd, x, xd, dst, dd, scratch);
     else if (gemv)
         rc = gb_gemv_q4_0(ctx, w, wd, x, xd, dst, dd);
     else if (variant == 2)

@@ -1,12 +1,380 @@
-// Large-batch (prefill) Q4_0 x Q8_0 mat-mul on the tcgen05 int8 tensor-core path.
+// Large-batch (prefill) Q4_0 x Q8_0 mat-mul on the 5th-generation tensor cores:
+// tcgen05.mma kind::i8 with int32 accumulators in tensor memory (TMEM).
+//
+// Numerics follow MatMul::f_q_f32_f32::<BlockQ4_0> (src/op.rs:1383-1598 of galois) with
+// BlockQ4_0::vec_dot_q8_0 (src/ggml_quants.rs:156-172): every 32-element block contributes
+//   f32(d_w) * f32(d_x) * (sum_j (q4_j - 8) * q8_j)
+// and the integer sum must be exact.  One tcgen05.mma of K = 32 is exactly one Q4_0 / Q8_0 block,
+// so each block gets its OWN int32 accumulator tile (no accumulation across blocks in TMEM); the
+// epilogue warps read it back with tcgen05.ld, add the -8 * sum(q8) correction, convert and
+// apply the two f16 block scales in f32.  The tensor pipe is therefore far from saturated: the
+// CUDA-core epilogue (about 4.5 instructions per output element per block) bounds the kernel.
+//
+// Operand roles are swapped with respect to the usual GEMM: the 128 weight rows of a CTA tile are
+// the MMA's M side (TMEM lanes = weight rows), the batch is the N side (TMEM columns).
+//
+//   warps 0-7   epilogue: warp w owns TMEM lanes 32*(w%4)..+31 (= weight rows) and the column half
+//               w/4; f32 accumulators live in registers (BN/2 per thread)
+//   warps 8-11  unpack: thread = weight row; reads 144 raw bytes (8 blocks) per K step straight
+//               from global memory, writes the nibbles as unsigned bytes into the canonical K-major
+//               UMMA layout (8-row x 16-byte core matrices, no swizzle) and the f32 block scales
+//   warp 12     MMA issuer (one elected lane) and TMEM allocation
+//   warp 13     loader: 1-D bulk copies (no multicast) of the quantised activations, which the
+//               quantiser kernel below already wrote in the canonical UMMA layout
+//
+// Every mbarrier wait is bounded; on a timeout the kernel records a status word, leaves its
+// loops, frees its TMEM and returns.
 #include "mul_mat_q4_0_tc.cuh"
 
-int gb_mm_tc_init(galois_b200_ctx*) { return 0; }
-bool gb_mm_tc_supported(const galois_b200_ctx*, const void*, const galois_dim*, const galois_dim*, const galois_dim*) {
-    return false;
+#include "ptx.cuh"
+
+namespace {
+
+constexpr int TC_M = 128;            // weight rows per CTA tile (UMMA M)
+constexpr int TC_KC = 8;             // blocks per K step (144 raw bytes per row)
+constexpr int TC_STAGES = 2;
+constexpr int TC_EPI_WARPS = 8;
+constexpr int TC_THREADS = (TC_EPI_WARPS + 4 + 2) * 32;  // 448
+constexpr uint32_t TC_MAGIC = 0x4B400000u;               // 12582912.0f: int -> float by bit tricks
+
+// ---- tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
 }
-size_t gb_mm_tc_scratch_bytes(const galois_dim*, const galois_dim*) { return 0; }
-int gb_mm_q4_0_tc(galois_b200_ctx* ctx, const void*, const galois_dim*, const gb_q8_soa&, const galois_dim*, float*,
-                  const galois_dim*, void*) {
-    return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: tensor-core variant not available");
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D[tmem] = A[smem] * B[smem] (accumulate == 0: overwrite), u8 x s8 -> s32, M = 128, N = BN, K = 32
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// mbarrier arrives once all tcgen05.mma issued so far by this thread have completed
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane (base + i)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, no-swizzle shared-memory matrix descriptor: 8-row x 16-byte core matrices; `lbo` =
+// byte distance between the two 16-byte K chunks of a K = 32 slice, `sbo` = byte distance between
+// consecutive 8-row groups.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);
+    d |= (uint64_t)((lbo >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+    return d;                // base offset 0, layout type 0 (no swizzle)
+}
+
+// Shared memory of one CTA (dynamic, 1024-byte aligned):
+//   per stage: A (TC_KC * 128 * 32 unsigned bytes), B (TC_KC * BN * 32 int8), dw (TC_KC * 128 f32),
+//              xs (TC_KC * BN * {f32 d_x, i32 MAGIC - 8 * sum}), then the barriers.
+template <int BN>
+struct tc_smem {
+    static constexpr uint32_t A_BLOCK = TC_M * 32, B_BLOCK = BN * 32;
+    static constexpr uint32_t A_BYTES = TC_KC * A_BLOCK, B_BYTES = TC_KC * B_BLOCK;
+    static constexpr uint32_t DW_BYTES = TC_KC * TC_M * 4, XS_BYTES = TC_KC * BN * 8;
+    static constexpr uint32_t STAGE = A_BYTES + B_BYTES + DW_BYTES + XS_BYTES;
+    static constexpr uint32_t BAR_OFF = TC_STAGES * STAGE;
+    static constexpr uint32_t TOTAL = BAR_OFF + 256;
+};
+
+// Quantises the activations into the layout the tensor-core kernel consumes (bit-exact with
+// <BlockQ8_0 as QuantType>::from_f32, src/ggml_quants.rs:736-764).  Columns are padded to a
+// multiple of BN with zeros.
+//   qs: [col tile][block][2 K chunks][BN/8 col groups][8 cols][16 bytes]
+//   xs: [col tile][block][BN] {f32 d, i32 MAGIC - 8 * sum q}
+__global__ void __launch_bounds__(256) quantize_q8_tc_kernel(const float* __restrict__ x, int64_t x_stride, int K, int B, int BN,
+                                                             uint8_t* __restrict__ qs, int2* __restrict__ xs) {
+    const int nkb = K >> 5;
+    const int sub = threadIdx.x & 7;
+    const int kb = (blockIdx.x * 256 + threadIdx.x) >> 3;
+    const int col = blockIdx.y;  // padded column
+    const bool live = kb < nkb;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live && col < B) v = __ldg(reinterpret_cast<const float4*>(x + (size_t)col * x_stride + kb * 32) + sub);
+    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+    const int q0 = max(-128, min(127, (int)roundf(__fmul_rn(v.x, id))));
+    const int q1 = max(-128, min(127, (int)roundf(__fmul_rn(v.y, id))));
+    const int q2 = max(-128, min(127, (int)roundf(__fmul_rn(v.z, id))));
+    const int q3 = max(-128, min(127, (int)roundf(__fmul_rn(v.w, id))));
+    int s = q0 + q1 + q2 + q3;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (live) {
+        const int tile = col / BN, ci = col % BN;
+        const uint32_t packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
+                                ((uint32_t)(q3 & 0xff) << 24);
+        const size_t blk_base = ((size_t)tile * nkb + kb) * (size_t)(BN * 32);
+        const size_t off = blk_base + (size_t)(sub >> 2) * (BN * 16) + (size_t)(ci >> 3) * 128 + (ci & 7) * 16 + (sub & 3) * 4;
+        *reinterpret_cast<uint32_t*>(qs + off) = packed;
+        if (sub == 0)
+            xs[((size_t)tile * nkb + kb) * BN + ci] = make_int2(__float_as_int(__half2float(__float2half_rn(d))), (int)TC_MAGIC - 8 * s);
+    }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+    mm_q4_0_tc_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ qs, const uint8_t* __restrict__ xs,
+                      float* __restrict__ dst, int64_t nb1, int K, int N, int B, int* __restrict__ status) {
+    using L = tc_smem<BN>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nkb = K >> 5, nsteps = nkb / TC_KC;
+    const int row_tile = blockIdx.x, col_tile = blockIdx.y;
+    const uint32_t row_bytes = (uint32_t)nkb * GB_Q4_BYTES;
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+    uint64_t* a_full = bars;                         // [TC_STAGES] 128 unpack threads
+    uint64_t* b_full = bars + TC_STAGES;             // [TC_STAGES] loader + bytes
+    uint64_t* stage_empty = bars + 2 * TC_STAGES;    // [TC_STAGES] 8 epilogue warps
+    uint64_t* tmem_full = bars + 3 * TC_STAGES;      // [2] MMA commit
+    uint64_t* tmem_empty = bars + 3 * TC_STAGES + 2; // [2] 8 epilogue warps
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 3 * TC_STAGES + 4);
+    constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; s++) {
+            mbar_init(&a_full[s], 128);
+            mbar_init(&b_full[s], 1);
+            mbar_init(&stage_empty[s], TC_EPI_WARPS);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], TC_EPI_WARPS);
+        }
+        fence_proxy_async();
+    }
+    if (warp == 12) {
+        tmem_alloc(tmem_base_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+    bool ok = true;
+
+    if (warp < TC_EPI_WARPS) {
+        // ------------------------------------------------------------ epilogue
+        const int lane_grp = warp & 3, half = warp >> 2;
+        const int row_in_tile = lane_grp * 32 + lane;
+        constexpr int NC = BN / 2;  // columns of this warp
+        float acc[NC];
+#pragma unroll
+        for (int c = 0; c < NC; c++) acc[c] = 0.0f;
+        for (int g = 0; g < nkb && ok; g++) {
+            const int buf = g & 1, step = g / TC_KC, kb = g % TC_KC, s = step % TC_STAGES;
+            ok = mbar_wait_bounded(&tmem_full[buf], (uint32_t)(g >> 1) & 1u);
+            if (!ok) break;
+            tc_fence_after();
+            const uint8_t* stage = smem + (uint32_t)s * L::STAGE;
+            const float dw = reinterpret_cast<const float*>(stage + L::A_BYTES + L::B_BYTES)[kb * TC_M + row_in_tile];
+            const int4* xsp = reinterpret_cast<const int4*>(stage + L::A_BYTES + L::B_BYTES + L::DW_BYTES) + (kb * BN + half * NC) / 2;
+#pragma unroll
+            for (int c0 = 0; c0 < NC; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(buf * BN + half * NC + c0), r);
+                tmem_ld_wait();
+                if (c0 + 32 >= NC) {
+                    // all of this warp's columns of the tile have been read: hand the buffer back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                }
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    const int4 sc = xsp[(c0 + c) >> 1];  // {d_x, magic - 8 sum} of two columns (same for all lanes)
+                    const float f0 = __int_as_float((int)r[c] + sc.y) - 12582912.0f;
+                    const float f1 = __int_as_float((int)r[c + 1] + sc.w) - 12582912.0f;
+                    acc[c0 + c] = fmaf(dw, __int_as_float(sc.x) * f0, acc[c0 + c]);
+                    acc[c0 + c + 1] = fmaf(dw, __int_as_float(sc.z) * f1, acc[c0 + c + 1]);
+                }
+            }
+            if (kb == TC_KC - 1) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&stage_empty[s]);
+            }
+        }
+        if (ok) {
+            const int row = row_tile * TC_M + row_in_tile;
+            if (row < N) {
+#pragma unroll
+                for (int c = 0; c < NC; c++) {
+                    const int col = col_tile * BN + half * NC + c;
+                    if (col < B) dst[(size_t)col * nb1 + row] = acc[c];
+                }
+            }
+        }
+    } else if (warp < 12) {
+        // ------------------------------------------------------------ unpack (thread = weight row)
+        const int r = threadIdx.x - TC_EPI_WARPS * 32;
+        int row = row_tile * TC_M + r;
+        if (row >= N) row = N - 1;  // ragged last tile: recompute a valid row, never stored
+        const uint4* src = reinterpret_cast<const uint4*>(w + (size_t)row * row_bytes);
+        uint4 cur[9], nxt[9];
+#pragma unroll
+        for (int i = 0; i < 9; i++) cur[i] = __ldg(src + i);
+        for (int step = 0; step < nsteps && ok; step++) {
+            const int s = step % TC_STAGES;
+            if (step + 1 < nsteps) {
+#pragma unroll
+                for (int i = 0; i < 9; i++) nxt[i] = __ldg(src + (step + 1) * 9 + i);
+            }
+            ok = mbar_wait_bounded(&stage_empty[s], ((uint32_t)(step / TC_STAGES) & 1u) ^ 1u);
+            if (!ok) break;
+            uint8_t* stage = smem + (uint32_t)s * L::STAGE;
+            float* dwp = reinterpret_cast<float*>(stage + L::A_BYTES + L::B_BYTES);
+            const uint32_t* t = reinterpret_cast<const uint32_t*>(cur);
+#pragma unroll
+            for (int p = 0; p < TC_KC / 2; p++) {  // block pairs: 9 words each
+                const uint32_t* tp = t + 9 * p;
+                uint32_t q0[4], q1[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    q0[i] = __funnelshift_r(tp[i], tp[i + 1], 16);
+                    q1[i] = tp[5 + i];
+                }
+                uint8_t* a0 = stage + (2 * p) * L::A_BLOCK + (r >> 3) * 128 + (r & 7) * 16;
+                uint8_t* a1 = a0 + L::A_BLOCK;
+                // elements 0..15 = low nibbles (K chunk 0), elements 16..31 = high nibbles (K chunk 1)
+                *reinterpret_cast<uint4*>(a0) = make_uint4(q0[0] & 0x0F0F0F0Fu, q0[1] & 0x0F0F0F0Fu, q0[2] & 0x0F0F0F0Fu, q0[3] & 0x0F0F0F0Fu);
+                *reinterpret_cast<uint4*>(a0 + TC_M * 16) = make_uint4((q0[0] >> 4) & 0x0F0F0F0Fu, (q0[1] >> 4) & 0x0F0F0F0Fu, (q0[2] >> 4) & 0x0F0F0F0Fu, (q0[3] >> 4) & 0x0F0F0F0Fu);
+                *reinterpret_cast<uint4*>(a1) = make_uint4(q1[0] & 0x0F0F0F0Fu, q1[1] & 0x0F0F0F0Fu, q1[2] & 0x0F0F0F0Fu, q1[3] & 0x0F0F0F0Fu);
+                *reinterpret_cast<uint4*>(a1 + TC_M * 16) = make_uint4((q1[0] >> 4) & 0x0F0F0F0Fu, (q1[1] >> 4) & 0x0F0F0F0Fu, (q1[2] >> 4) & 0x0F0F0F0Fu, (q1[3] >> 4) & 0x0F0F0F0Fu);
+                dwp[(2 * p) * TC_M + r] = __half2float(__ushort_as_half((unsigned short)(tp[0] & 0xffffu)));
+                dwp[(2 * p + 1) * TC_M + r] = __half2float(__ushort_as_half((unsigned short)(tp[4] >> 16)));
+            }
+            fence_proxy_async();  // the tensor core reads shared memory through the async proxy
+            mbar_arrive(&a_full[s]);
+#pragma unroll
+            for (int i = 0; i < 9; i++) cur[i] = nxt[i];
+        }
+    } else if (warp == 12) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            // instruction descriptor: D = s32, A = unsigned 8 bit, B = signed 8 bit, both K-major
+            const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+            for (int step = 0; step < nsteps && ok; step++) {
+                const int s = step % TC_STAGES;
+                const uint32_t ph = (uint32_t)(step / TC_STAGES) & 1u;
+                ok = mbar_wait_bounded(&a_full[s], ph) && mbar_wait_bounded(&b_full[s], ph);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + (uint32_t)s * L::STAGE);
+                const uint32_t b_addr = a_addr + L::A_BYTES;
+                for (int kb = 0; kb < TC_KC; kb++) {
+                    const int g = step * TC_KC + kb, buf = g & 1;
+                    ok = mbar_wait_bounded(&tmem_empty[buf], ((uint32_t)(g >> 1) & 1u) ^ 1u);
+                    if (!ok) break;
+                    tc_fence_after();
+                    umma_i8(tmem_base + (uint32_t)(buf * BN), umma_desc(a_addr + kb * L::A_BLOCK, TC_M * 16, 128),
+                            umma_desc(b_addr + kb * L::B_BLOCK, BN * 16, 128), idesc, 0u);
+                    umma_commit(&tmem_full[buf]);
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ loader (activations)
+        if (lane == 0) {
+            const uint8_t* qsrc = qs + (size_t)col_tile * nkb * L::B_BLOCK;
+            const uint8_t* xsrc = xs + (size_t)col_tile * nkb * (BN * 8);
+            for (int step = 0; step < nsteps && ok; step++) {
+                const int s = step % TC_STAGES;
+                ok = mbar_wait_bounded(&stage_empty[s], ((uint32_t)(step / TC_STAGES) & 1u) ^ 1u);
+                if (!ok) break;
+                uint8_t* stage = smem + (uint32_t)s * L::STAGE;
+                mbar_expect_tx(&b_full[s], L::B_BYTES + L::XS_BYTES);
+                bulk_g2s(stage + L::A_BYTES, qsrc + (size_t)step * L::B_BYTES, L::B_BYTES, &b_full[s]);
+                bulk_g2s(stage + L::A_BYTES + L::B_BYTES + L::DW_BYTES, xsrc + (size_t)step * L::XS_BYTES, L::XS_BYTES, &b_full[s]);
+            }
+        }
+        __syncwarp();
+    }
+
+    if (!ok && lane == 0) atomicExch(status, GALOIS_B200_E_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 12) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+int pick_bn(int64_t B) { return B <= 64 ? 64 : 128; }
+
+template <int BN>
+int launch_tc(galois_b200_ctx* ctx, const uint8_t* w, const uint8_t* qs, const uint8_t* xs, float* dst, int64_t nb1, int K, int N,
+              int B) {
+    dim3 grid((unsigned)((N + TC_M - 1) / TC_M), (unsigned)((B + BN - 1) / BN));
+    mm_q4_0_tc_kernel<BN><<<grid, TC_THREADS, tc_smem<BN>::TOTAL, ctx->stream>>>(w, qs, xs, dst, nb1, K, N, B, ctx->dev_status);
+    GB_LAUNCHED(ctx, "mm_q4_0_tc");
+    return 0;
+}
+
+}  // namespace
+
+int gb_mm_tc_init(galois_b200_ctx* ctx) {
+    GB_CUDA(ctx, cudaFuncSetAttribute(mm_q4_0_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem<64>::TOTAL));
+    GB_CUDA(ctx, cudaFuncSetAttribute(mm_q4_0_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem<128>::TOTAL));
+    return 0;
+}
+
+bool gb_mm_tc_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
+                        const galois_dim* dd) {
+    (void)ctx;
+    const int64_t K = wd->ne[0], N = wd->ne[1];
+    if (K % 256 != 0 || K > (1 << 20) || N < 1 || N > (1 << 30)) return false;  // 144-byte K steps, 16-byte aligned rows
+    if ((uintptr_t)w % 16 != 0) return false;
+    if (wd->ne[2] != 1 || wd->ne[3] != 1 || xd->ne[2] != 1 || xd->ne[3] != 1) return false;
+    if (wd->nb[1] != K / GB_QK) return false;
+    if (xd->ne[1] < 1 || xd->ne[1] > 65535 - 128) return false;  // one quantiser grid row per padded column
+    if ((uintptr_t)x % 16 != 0 || xd->nb[1] % 4 != 0) return false;
+    (void)dd;
+    return true;
+}
+
+size_t gb_mm_tc_scratch_bytes(const galois_dim* wd, const galois_dim* xd) {
+    const int64_t K = wd->ne[0], B = xd->ne[1];
+    const int BN = pick_bn(B);
+    const int64_t Bp = (B + BN - 1) / BN * BN;
+    return (size_t)Bp * K + (size_t)Bp * (K / 32) * 8 + 512;
+}
+
+int gb_mm_q4_0_tc(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
+                  const galois_dim* dd, void* scratch) {
+    const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
+    const int BN = pick_bn(B);
+    const int Bp = (B + BN - 1) / BN * BN;
+    uint8_t* qs = (uint8_t*)scratch;
+    uint8_t* xs = qs + (((size_t)Bp * K + 255) & ~(size_t)255);
+    dim3 qgrid((unsigned)((K / 32 * 8 + 255) / 256), (unsigned)Bp);
+    quantize_q8_tc_kernel<<<qgrid, 256, 0, ctx->stream>>>(x, xd->nb[1], K, B, BN, qs, (int2*)xs);
+    GB_LAUNCHED(ctx, "quantize_q8_tc");
+    const uint8_t* wb = (const uint8_t*)w;
+    if (BN == 64) return launch_tc<64>(ctx, wb, qs, xs, dst, dd->nb[1], K, N, B);
+    return launch_tc<128>(ctx, wb, qs, xs, dst, dd->nb[1], K, N, B);
 }

@@ -4,11 +4,14 @@
 #include "common.cuh"
 
 // Batches at least this large take the tensor-core path when it supports the shape.
-#define GB_TC_MIN_BATCH 32
+#define GB_TC_MIN_BATCH 9
 
 int gb_mm_tc_init(galois_b200_ctx* ctx);
-bool gb_mm_tc_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const galois_dim* xd,
+// 2-D contiguous weights with K % 256 == 0 and a 16-byte aligned base; 16-byte aligned activations.
+bool gb_mm_tc_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
                         const galois_dim* dd);
+// Scratch for the quantised activations in the tensor-core operand layout.
 size_t gb_mm_tc_scratch_bytes(const galois_dim* wd, const galois_dim* xd);
-int gb_mm_q4_0_tc(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const gb_q8_soa& xq, const galois_dim* xd,
-                  float* dst, const galois_dim* dd, void* scratch);
+// Quantises x into `scratch` and runs the GEMM (two launches).
+int gb_mm_q4_0_tc(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
+                  const galois_dim* dd, void* scratch);

@@ -1,0 +1,121 @@
+"""One decode step of a LLaMA-shaped decoder layer built from ``galois_*`` ops only.
+
+galois itself holds no model code: a caller crate composes a layer from the free functions
+``galois_rms_norm / mul / matmul / rope_custom / cpy / soft_max / unary / add``
+(src/op.rs:3034-3341).  This module is that caller for BASELINE config 4: hidden 4096,
+32 heads x 128, FFN 11008, Q4_0 projections, f16 KV cache, batch 1.
+
+KV-cache layout (both present the contraction dimension contiguously, as
+``galois_matmul`` requires of its first operand, src/op.rs:1428):
+  K cache  [heads][ctx][head_dim] f16     scores = matmul(K, q)      -> [heads][1][ctx]
+  V cache  [heads][head_dim][ctx] f16     context = matmul(V, probs) -> [heads][1][head_dim]
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+
+from .op import (RopeCustomOption, UnaryOp, galois_add, galois_cpy, galois_matmul, galois_mul, galois_rms_norm,
+                 galois_rope_custom, galois_soft_max_ext, galois_unary)
+from .tensor import Device, GGmlType, Tensor
+
+
+@dataclass
+class LayerShape:
+    hidden: int = 4096
+    heads: int = 32
+    head_dim: int = 128
+    ffn: int = 11008
+    ctx: int = 2048
+    eps: float = 1e-6
+    rope_theta: float = 10000.0
+
+
+WEIGHT_NAMES = ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")
+
+
+def weight_shapes(s: LayerShape):
+    """name -> (N rows, K columns) of each Q4_0 projection."""
+    h, f = s.hidden, s.ffn
+    return {"wq": (h, h), "wk": (h, h), "wv": (h, h), "wo": (h, h), "w_gate": (f, h), "w_up": (f, h), "w_down": (h, f)}
+
+
+class DecodeLayer:
+    """Weights (Q4_0 bytes, host numpy), norm gains and the two caches live on one GPU; `step`
+    enqueues the ~22 kernels of one token on the device's stream and returns the output tensor."""
+
+    def __init__(self, dev, shape: LayerShape, weights: dict, attn_norm: np.ndarray, ffn_norm: np.ndarray,
+                 k_cache: np.ndarray, v_cache: np.ndarray):
+        s, G = shape, Device.Gpu(dev)
+        self.shape, self.dev = s, dev
+        self.w = {}
+        for name, (n, k) in weight_shapes(s).items():
+            self.w[name] = Tensor.from_raw(weights[name], (k, n), GGmlType.Q4_0, G)
+        self.attn_norm = Tensor.from_numpy(attn_norm.reshape(1, s.hidden), GGmlType.F32, G)
+        self.ffn_norm = Tensor.from_numpy(ffn_norm.reshape(1, s.hidden), GGmlType.F32, G)
+        # caches arrive as f16 arrays [heads][ctx][head_dim] and [heads][head_dim][ctx]
+        self.k_cache = Tensor.from_numpy(k_cache, GGmlType.F16, G)
+        self.v_cache = Tensor.from_numpy(v_cache, GGmlType.F16, G)
+        z = lambda *ne: Tensor.zeros(ne, GGmlType.F32, G)
+        self.h = z(s.hidden, 1)
+        self.q, self.k, self.v = z(s.hidden, 1), z(s.hidden, 1), z(s.hidden, 1)
+        self.qr, self.kr = z(s.head_dim, s.heads, 1), z(s.head_dim, s.heads, 1)
+        self.scores, self.probs = z(s.ctx, 1, s.heads), z(s.ctx, 1, s.heads)
+        self.ctxv = z(s.head_dim, 1, s.heads)
+        self.o, self.x2, self.h2 = z(s.hidden, 1), z(s.hidden, 1), z(s.hidden, 1)
+        self.g, self.u, self.a = z(s.ffn, 1), z(s.ffn, 1), z(s.ffn, 1)
+        self.d, self.out = z(s.hidden, 1), z(s.hidden, 1)
+        self.rope = RopeCustomOption(n_dims=s.head_dim, mode=0, n_ctx=s.ctx, freq_base=s.rope_theta, freq_scale=1.0)
+        self.scale = 1.0 / math.sqrt(s.head_dim)
+
+    def step(self, x: Tensor, pos: Tensor, position: int) -> Tensor:
+        """x: f32 {hidden, 1}; pos: i32 {1} holding `position` (the row of the caches to fill)."""
+        s = self.shape
+        hd, nh, ctx = s.head_dim, s.heads, s.ctx
+        # attention block
+        galois_rms_norm(x, self.h, s.eps)
+        galois_mul(self.h, self.attn_norm, self.h)
+        galois_matmul(self.w["wq"], self.h, self.q)
+        galois_matmul(self.w["wk"], self.h, self.k)
+        galois_matmul(self.w["wv"], self.h, self.v)
+        q3 = self.q.view((hd, nh, 1), (1, hd, hd * nh, hd * nh))
+        k3 = self.k.view((hd, nh, 1), (1, hd, hd * nh, hd * nh))
+        galois_rope_custom(self.rope, q3, pos, self.qr)
+        galois_rope_custom(self.rope, k3, pos, self.kr)
+        # KV-cache append: K row `position` of every head; V column `position` of every head
+        k_src = self.kr.view((hd, 1, nh), (1, hd, hd, hd * nh))
+        k_dst = self.k_cache.view((hd, 1, nh), (1, hd, hd * ctx, hd * ctx * nh), offset=position * hd)
+        galois_cpy(k_src, k_dst)
+        v_src = self.v.view((1, hd, nh), (1, 1, hd, hd * nh))
+        v_dst = self.v_cache.view((1, hd, nh), (1, ctx, hd * ctx, hd * ctx * nh), offset=position)
+        galois_cpy(v_src, v_dst)
+        # scores over the cache, causal soft-max, context
+        qh = self.qr.view((hd, 1, nh), (1, hd, hd, hd * nh))
+        galois_matmul(self.k_cache, qh, self.scores)
+        sc = self.scores.view((ctx, nh, 1), (1, ctx, ctx * nh, ctx * nh))
+        pr = self.probs.view((ctx, nh, 1), (1, ctx, ctx * nh, ctx * nh))
+        galois_soft_max_ext(sc, pr, self.scale, pos)
+        galois_matmul(self.v_cache, self.probs, self.ctxv)
+        ctx_flat = self.ctxv.view((s.hidden, 1), (1, s.hidden, s.hidden, s.hidden))
+        galois_matmul(self.w["wo"], ctx_flat, self.o)
+        galois_add(x, self.o, self.x2)
+        # feed-forward block (SwiGLU)
+        galois_rms_norm(self.x2, self.h2, s.eps)
+        galois_mul(self.h2, self.ffn_norm, self.h2)
+        galois_matmul(self.w["w_gate"], self.h2, self.g)
+        galois_matmul(self.w["w_up"], self.h2, self.u)
+        galois_unary(self.g, self.a, UnaryOp.Silu)
+        galois_mul(self.a, self.u, self.a)
+        galois_matmul(self.w["w_down"], self.a, self.d)
+        galois_add(self.x2, self.d, self.out)
+        return self.out
+
+    def algorithmic_bytes(self) -> int:
+        """Q4_0 weights once + both f16 caches once + the f32 activations once."""
+        s = self.shape
+        wb = sum(n * (k // 32) * 18 for n, k in weight_shapes(s).values())
+        kv = 2 * s.heads * s.ctx * s.head_dim * 2
+        act = 4 * (12 * s.hidden + 3 * s.ffn + 2 * s.heads * s.ctx)
+        return wb + kv + act

@@ -162,6 +162,13 @@ def test_mul_mat_q4_0_dependent_launch_ordering(gb, dev, oracle):
     gb.lib.galois_b200_set_pdl(dev.ctx, 1)
 
 
+# variant 3 = tcgen05 int8 tensor-core GEMM (K % 256 == 0); BASELINE config 3 is 4096 x 4096 x 512
+@pytest.mark.parametrize("n,k,b", [(128, 256, 64), (128, 512, 1), (200, 768, 33), (77, 256, 130), (4096, 4096, 512),
+                                   (300, 4096, 37), (4096, 4096, 100), (1000, 11008, 65)])
+def test_mul_mat_q4_0_tensor_core(gb, dev, oracle, n, k, b):
+    _mul_mat_case(gb, dev, oracle, n, k, b, 9500 + n + k + b, 3)
+
+
 # automatic dispatch over the BASELINE shapes (configs 2, 3, 5) incl. large batches
 @pytest.mark.parametrize("n,k,b", [(11008, 4096, 8), (4096, 11008, 8), (4096, 4096, 512), (32000, 4096, 16), (28672, 8192, 16),
                                    (4096, 4096, 100), (300, 4096, 37)])
