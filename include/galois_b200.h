@@ -141,6 +141,22 @@ int galois_b200_mul_mat_q4_0_f32_host(galois_b200_ctx* ctx, const void* w, const
                                       const float* x_host, const galois_dim* xd, float* dst_host,
                                       const galois_dim* dd);
 
+/* The same op for callers that must not allocate device memory (no counterpart in the
+ * reference; it exists for hosts where cudaMalloc is unavailable at call time: device memory
+ * owned by another allocator, a fixed memory budget, a real-time loop that must not synchronise).  It needs no context.  The quantised
+ * activations go to a 4 MiB array that is part of the library image (every GPU that loads the
+ * library holds it until the process exits) instead of the context's arena, so this entry point
+ * and everything it calls perform no cudaMalloc / cudaFree.  Limit: activation rows * (K + K/4)
+ * must fit in 4 MiB (e.g. 800 rows of K = 4096); larger problems return GALOIS_B200_E_NOMEM.
+ * The first call on each device resolves the array's device address (that device must be
+ * current) and should come before any stream capture; later calls only enqueue two kernels on
+ * `cu_stream`.  All calls on one device share the array: calls whose kernels could overlap on
+ * the GPU (different streams, no dependency) race on it and must be ordered by the caller.
+ * `errbuf` (may be NULL) receives the text of a non-zero status. */
+int galois_b200_mul_mat_q4_0_f32_static(void* cu_stream, const void* w, const galois_dim* wd, const float* x,
+                                        const galois_dim* xd, float* dst, const galois_dim* dd, char* errbuf,
+                                        size_t errbuf_len);
+
 /* CudaMap2::f_x_y_y for CudaMatMul, F16 x F32 -> F32 (src/cuda.rs:404-418,
  * impl :881-992, cuBLAS :698-782), numerics of
  * MatMul::f_q_f32_f32::<f16> + vec_dot_f16 (src/ggml_quants.rs:113-135,
