@@ -315,9 +315,12 @@ def run_ours(args):
     tot, cnt = C.c_double(), C.c_int64()
     lib.galois_b200_profile_read(ctx, C.byref(tot), C.byref(cnt))
     lib.galois_b200_profile_enable(ctx, 0)
-    kernel_ms = tot.value / max(1, cnt.value)
+    isolated_ms = tot.value / max(1, cnt.value)  # launch latency included: the events serialise consecutive launches
     local_bytes_call = sum(algorithmic_bytes(bands[name][1], k, B) for name, n, k in shapes) / len(shapes)
     peak, peak_kind = measured_peak_gbs()
+    # Average launch duration of the mat-mul kernel over the timed region: consecutive launches overlap
+    # (programmatic dependent launch), so it is the region's device time divided by its launches of that kernel.
+    kernel_ms = ms_step / calls_step
     achieved = local_bytes_call / (kernel_ms * 1e-3) / 1e9 if kernel_ms > 0 else 0.0
 
     # ---- e2e: the host-buffer entry point; activations from pinned host memory, results read back
@@ -349,6 +352,95 @@ def run_ours(args):
                "d2h_bytes_per_step": nsets * sum(B * n * 4 for _, n, k in shapes), "ms_per_step": e2e_ms}
     sampler.stop()
 
+    # ---- other BASELINE configs measured beside the headline (N = 1 only; reported under "extra")
+    extra = None
+    if world == 1 and not args.no_extra:
+        extra = {}
+        # config 4: one decode step of a LLaMA-7B-shaped layer built from galois ops, 4 distinct layers in rotation
+        from galois_b200.decode import DecodeLayer, LayerShape, weight_shapes
+        shp = LayerShape()
+        layers = []
+        for li in range(4):
+            wq4 = {name: make_q4_0(n, k, 31000 + 100 * li + i, device).cpu().numpy()
+                   for i, (name, (n, k)) in enumerate(weight_shapes(shp).items())}
+            gk = torch.Generator(device=device)
+            gk.manual_seed(32000 + li)
+            kc = torch.randn(shp.heads, shp.ctx, shp.head_dim, generator=gk, device=device).to(torch.float16).cpu().numpy()
+            vc = torch.randn(shp.heads, shp.head_dim, shp.ctx, generator=gk, device=device).to(torch.float16).cpu().numpy()
+            layers.append(DecodeLayer(dev, shp, wq4, np.ones(shp.hidden, np.float32), np.ones(shp.hidden, np.float32), kc, vc))
+        G = gb.Device.Gpu(dev)
+        xin = gb.Tensor.from_numpy(xs[HIDDEN][:1].cpu().numpy(), gb.GGmlType.F32, G)
+        post = gb.Tensor.from_numpy(np.array([shp.ctx - 1], np.int32), gb.GGmlType.I32, G)
+
+        def layer_pass():
+            for L in layers:
+                L.step(xin, post, shp.ctx - 1)
+
+        for _ in range(3):
+            layer_pass()
+        torch.cuda.synchronize()
+        l0 = dev.launch_count()
+        lg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(lg, stream=stream):
+            layer_pass()
+        layer_launches = (dev.launch_count() - l0) // len(layers)
+        for _ in range(3):
+            lg.replay()
+        torch.cuda.synchronize()
+        reps = max(10, args.steps // 4)
+        e0.record(stream)
+        for _ in range(reps):
+            lg.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        us_layer = e0.elapsed_time(e1) * 1e3 / (reps * len(layers))
+        lbytes = layers[0].algorithmic_bytes()
+        extra["decode_layer"] = {"config": "config4: hidden 4096, 32 heads x 128, FFN 11008, f16 KV cache 2048, batch 1, position 2047",
+                                 "layer_steps_per_s": 1e6 / us_layer, "us_per_layer": us_layer, "kernels_per_layer": layer_launches,
+                                 "algorithmic_bytes": lbytes, "hbm_gbs": lbytes / us_layer / 1e3,
+                                 "frac_of_measured_hbm": lbytes / us_layer / 1e3 / peak}
+        del layers, lg
+        # config 3: prefill 4096 x 4096 x 512 tokens on the tcgen05 int8 path; config 2 at batch 4 and 8
+        def time_mm(n, k, b, copies):
+            ws = [make_q4_0(n, k, 33000 + c, device) for c in range(copies)]
+            wdim = gb.Dim.ggml((k, n), gb.GGmlType.Q4_0).c_struct()
+            xb = torch.randn(b, k, device=device, dtype=torch.float32)
+            yb = torch.zeros(b, n, device=device, dtype=torch.float32)
+            xd_, yd_ = gb.Dim.ggml((k, b), gb.GGmlType.F32).c_struct(), gb.Dim.ggml((n, b), gb.GGmlType.F32).c_struct()
+
+            def run():
+                for wbuf in ws:
+                    rc = lib.galois_b200_mul_mat_q4_0_f32(ctx, C.c_void_p(wbuf.data_ptr()), C.byref(wdim), C.c_void_p(xb.data_ptr()),
+                                                          C.byref(xd_), C.c_void_p(yb.data_ptr()), C.byref(yd_))
+                    if rc != 0:
+                        raise RuntimeError(f"mul_mat_q4_0 failed: {lib.galois_b200_last_error(ctx)} ({rc})")
+            for _ in range(3):
+                run()
+            torch.cuda.synchronize()
+            gg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gg, stream=stream):
+                run()
+            gg.replay()
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(10):
+                gg.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e3 / (10 * copies)
+
+        us = time_mm(4096, 4096, 512, 16)
+        ops = 2.0 * 512 * 4096 * 4096
+        extra["prefill"] = {"config": "config3: 4096 x 4096 Q4_0 weight x 512 tokens, tcgen05 kind::i8", "us": us,
+                            "int8_tops": ops / us / 1e6, "frac_of_4500_nominal_int8_tops": ops / us / 1e6 / 4500.0,
+                            "hbm_gbs": algorithmic_bytes(4096, 4096, 512) / us / 1e3}
+        for bb in (4, 8):
+            us_g, us_d = time_mm(FFN, HIDDEN, bb, 16), time_mm(HIDDEN, FFN, bb, 16)
+            ab = algorithmic_bytes(FFN, HIDDEN, bb)
+            extra[f"config2_batch{bb}"] = {"us_gate_up": us_g, "us_down": us_d, "hbm_gbs": 3 * ab / (2 * us_g + us_d) / 1e3}
+        us_h = time_mm(32000, 4096, 16, 8)
+        extra["config5_head_batch16"] = {"us": us_h, "hbm_gbs": algorithmic_bytes(32000, 4096, 16) / us_h / 1e3}
+
     # ---- CPU baseline (rank 0, N = 1): the oracle's restatement of the reference CPU path, 4 tasks
     cpu = None
     if world == 1 and not args.no_cpu:
@@ -375,10 +467,11 @@ def run_ours(args):
                        "l2": f"inputs larger than L2: {weight_bytes / L2_BYTES:.1f}x the 126 MB L2 streamed between reuses",
                        "launch": "cuda_graph" if use_graph else "stream",
                        "parallelism": f"rows/{world} + nccl all_gather" if world > 1 else "single gpu"},
-            "roofline": {"bound": "hbm", "kernel": "mmv_q4_0_bulk", "achieved": achieved, "peak": peak, "unit": UNIT,
+            "roofline": {"bound": "hbm", "kernel": "gemv_q4_0_kernel" if B <= 4 else ("mmv_q4_0_bulk_kernel" if B <= 8 else "mm_q4_0_tc_kernel"), "achieved": achieved, "peak": peak, "unit": UNIT,
                          "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
                          "kernel_us": kernel_ms * 1e3, "algorithmic_bytes_per_launch": local_bytes_call,
-                         "timed_launches": cnt.value, "frac_of_8000_nominal": achieved / 8000.0},
+                         "timed_launches": calls_step * args.steps, "launches_per_mat_mul": launches_step / calls_step,
+                         "isolated_kernel_us": isolated_ms * 1e3, "isolated_launches": cnt.value, "frac_of_8000_nominal": achieved / 8000.0},
             "gpu_launches": launches_step * args.steps,
             "clocks": sampler.summary(),
         }
@@ -386,6 +479,8 @@ def run_ours(args):
             line["e2e"] = e2e
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if extra is not None:
+            line["extra"] = extra
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -402,6 +497,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-graph", action="store_true", help="plain stream launches instead of one CUDA graph per step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the decode-layer / prefill / batch 4-8 side measurements")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     args = ap.parse_args()
     if args.impl == "reference":
