@@ -94,18 +94,20 @@ __device__ __forceinline__ void load_act(const uint8_t* qs, const uint8_t* ds, i
 
 // Cluster-cooperative Q8_0 quantiser.  The NB * K/32 blocks are split evenly over the CTAs of the
 // cluster; eight lanes own a block (four consecutive floats each).  Every result word is stored
-// into the activation area of all `csize` CTAs (this one included) in the piece-major layout:
+// asynchronously into the activation area of all `csize` CTAs (this one included), each store
+// counting its bytes on the destination's `act_bar`, in the piece-major layout:
 // row b's quants at act_qs + b * K, its {d, -8 * sum} pairs at act_ds + b * (K/32) * 8.
 template <int SEG>
 __device__ __forceinline__ void quantize_rows_cluster(const float* __restrict__ x, int x_stride, int K, int nbatch, int NB,
-                                                      uint8_t* act_qs, uint8_t* act_ds, int nsegk, uint32_t crank, uint32_t csize) {
+                                                      uint8_t* act_qs, uint8_t* act_ds, int nsegk, uint32_t crank, uint32_t csize,
+                                                      uint64_t* act_bar) {
     const int nblk = K >> 5;
     const int total = NB * nblk;
     const int per = (total + (int)csize - 1) / (int)csize;
     const int first = (int)crank * per, last = min(first + per, total);
     const int sub = threadIdx.x & 7;
     const int groups = GEMV_THREADS >> 3;
-    const uint32_t qs_base = smem_u32(act_qs), ds_base = smem_u32(act_ds);
+    const uint32_t qs_base = smem_u32(act_qs), ds_base = smem_u32(act_ds), bar_base = smem_u32(act_bar);
     // loop bounds are uniform per warp (every lane takes part in the shuffles); U blocks per lane
     // group are loaded before any is processed, so a CTA's whole slice is one round trip to L2
     constexpr int U = 4;
@@ -147,8 +149,9 @@ __device__ __forceinline__ void quantize_rows_cluster(const float* __restrict__ 
                 const uint32_t doff = (uint32_t)b * nblk * 8 + ((bi >> 1) * nsegk + seg) * 16 + (bi & 1) * 8;
                 const uint32_t dbits = __float_as_uint(__half2float(__float2half_rn(d)));
                 for (uint32_t r = 0; r < csize; r++) {
-                    cluster_st_u32(cluster_map(qs_base + qoff, r), packed);
-                    if (sub == 0) cluster_st_v2(cluster_map(ds_base + doff, r), dbits, (uint32_t)(-8 * s));
+                    const uint32_t rbar = cluster_map(bar_base, r);
+                    cluster_st_async_u32(cluster_map(qs_base + qoff, r), packed, rbar);
+                    if (sub == 0) cluster_st_async_v2(cluster_map(ds_base + doff, r), dbits, (uint32_t)(-8 * s), rbar);
                 }
             }
         }
@@ -183,6 +186,7 @@ __global__ void __launch_bounds__(GEMV_THREADS)
     constexpr bool HOIST = NPASS > 0;
     static_assert(!HOIST || NB == 1, "hoisted activations exist for one activation row only");
     uint64_t* my_bars = reinterpret_cast<uint64_t*>(smem) + warp * GEMV_MAX_STAGES;
+    uint64_t* act_bar = reinterpret_cast<uint64_t*>(smem) + GEMV_WARPS * GEMV_MAX_STAGES;
     uint8_t* act_qs = smem + GEMV_BAR_BYTES;
     const uint32_t act_qs_bytes = (uint32_t)NB * K, act_ds_bytes = (uint32_t)NB * nblk * 8;
     uint8_t* act_ds = act_qs + act_qs_bytes;
@@ -202,18 +206,26 @@ __global__ void __launch_bounds__(GEMV_THREADS)
     // weights are not produced by the preceding kernel: prefetch them before the dependency wait
     if (lane == 0) {
         for (int s = 0; s < stages; s++) mbar_init(&my_bars[s], 1);
+        if (warp == 0) {
+            // every CTA of the cluster receives the whole quantised activation set exactly once
+            mbar_init(act_bar, 1);
+            mbar_expect_tx(act_bar, act_qs_bytes + act_ds_bytes);
+            fence_mbarrier_init_cluster();
+        }
         fence_proxy_async();
         for (int s = 0; s < stages && s < my_chunks; s++) issue(s, s);
     }
     const uint32_t crank = cluster_ctarank(), csize = cluster_nctarank();
-    cluster_arrive();  // this CTA's shared memory exists
-    pdl_wait();        // the activations (and whatever dst aliases) belong to the preceding kernels
-    cluster_wait();    // so does every peer's
-    if (!(dbg & 2)) quantize_rows_cluster<SEG>(x, x_stride, K, nbatch, NB, act_qs, act_ds, nsegk, crank, csize);
-    cluster_arrive();
-    cluster_wait();    // all slices of the quantised activations have landed in this CTA
-
+    __syncwarp();
+    cluster_arrive_relaxed();  // this CTA's shared memory and act_bar exist
+    pdl_wait();                // the activations (and whatever dst aliases) belong to the preceding kernels
+    cluster_wait();            // so do every peer's
     bool ok = true;
+    if (!(dbg & 2)) {
+        quantize_rows_cluster<SEG>(x, x_stride, K, nbatch, NB, act_qs, act_ds, nsegk, crank, csize, act_bar);
+        ok = mbar_wait_bounded(act_bar, 0);  // all slices of the quantised activations have landed here
+    }
+
     int yh[HOIST ? NPASS : 1][HOIST ? 16 * SEG : 1];
     float4 dh[HOIST ? NPASS : 1][HOIST ? SEG : 1];
     if (HOIST) {

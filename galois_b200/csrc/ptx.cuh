@@ -76,8 +76,19 @@ __device__ __forceinline__ void cluster_st_u32(uint32_t addr, uint32_t v) {
 __device__ __forceinline__ void cluster_st_v2(uint32_t addr, uint32_t a, uint32_t b) {
     asm volatile("st.shared::cluster.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
+// Asynchronous stores into another CTA's shared memory; each adds its size to the transaction
+// count of an mbarrier of the DESTINATION CTA when it lands.
+__device__ __forceinline__ void cluster_st_async_u32(uint32_t addr, uint32_t v, uint32_t remote_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(addr), "r"(v), "r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ void cluster_st_async_v2(uint32_t addr, uint32_t a, uint32_t b, uint32_t remote_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b32 [%0], {%1, %2}, [%3];" ::"r"(addr), "r"(a), "r"(b), "r"(remote_bar) : "memory");
+}
+// Makes mbarrier initialisations visible to the other CTAs of the cluster.
+__device__ __forceinline__ void fence_mbarrier_init_cluster() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // All threads of all CTAs of the cluster must execute both halves (convergently within a warp).
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 // a (u8 x4) . b (s8 x4) + c
