@@ -277,7 +277,7 @@ def run_ours(args):
     sync_all()
 
     # ---- `value`: whole-job throughput, inputs resident in HBM; one CUDA graph per step at N = 1
-    use_graph = world == 1 and not args.no_graph
+    use_graph = world == 1 and not args.no_graph  # the sharded step (with its NCCL all-gathers) runs as plain stream launches
     launches0 = dev.launch_count()
     if use_graph:
         graph = torch.cuda.CUDAGraph()
