@@ -388,10 +388,21 @@ extern "C" int galois_b200_mul_mat_q4_0_f32_host(galois_b200_ctx* ctx, const voi
     }
     float* xdev = (float*)ctx->io;
     float* ddev = (float*)((uint8_t*)ctx->io + ((xbytes + 255) & ~(size_t)255));
+    // A pinned, device-mapped result buffer is written by the kernel directly (posted stores over the
+    // host link): one copy call and its latency less.  Pageable memory goes through the staging buffer.
+    bool direct = false;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, dst_host) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer != nullptr &&
+        (uintptr_t)attr.devicePointer % 4 == 0) {
+        ddev = (float*)attr.devicePointer;
+        direct = true;
+    } else {
+        (void)cudaGetLastError();
+    }
     if (xbytes) GB_CUDA(ctx, cudaMemcpyAsync(xdev, x_host, xbytes, cudaMemcpyHostToDevice, ctx->stream));
     int rc = galois_b200_mul_mat_q4_0_f32(ctx, w, wd, xdev, xd, ddev, dd);
     if (rc) return rc;
-    if (dbytes) GB_CUDA(ctx, cudaMemcpyAsync(dst_host, ddev, dbytes, cudaMemcpyDeviceToHost, ctx->stream));
+    if (dbytes && !direct) GB_CUDA(ctx, cudaMemcpyAsync(dst_host, ddev, dbytes, cudaMemcpyDeviceToHost, ctx->stream));
     GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return 0;
 }

@@ -88,6 +88,32 @@ struct gb_q8_soa {
 // ------------------------------------------------------------------ device helpers
 #ifdef __CUDACC__
 
+// Launches `kern` on the context's stream; with programmatic dependent launch enabled on the
+// context the kernel may start while the kernel in front of it is still running (every kernel
+// launched this way calls griddepcontrol.wait before it touches global memory).
+template <typename... KArgs, typename... Args>
+inline cudaError_t gb_launch(const galois_b200_ctx* ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// First statements of a kernel launched with gb_launch: let the next kernel start launching, then
+// wait until everything in front of this kernel has completed.
+__device__ __forceinline__ void gb_pdl_entry() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ float gb_warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

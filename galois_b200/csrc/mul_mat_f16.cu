@@ -19,6 +19,7 @@ __global__ void __launch_bounds__(256) mul_mat_f16_kernel(const __half* __restri
                                                           int64_t nb13, float* __restrict__ dst, int64_t nb1, int64_t nb2,
                                                           int64_t nb3, int64_t K, int64_t N, int64_t ne11, int64_t ne12,
                                                           int64_t ne13) {
+    gb_pdl_entry();
     constexpr int ROWS_PER_BLOCK = 256 / LPR;
     const int sub = threadIdx.x % LPR;
     const int64_t row = (int64_t)blockIdx.x * ROWS_PER_BLOCK + threadIdx.x / LPR;
@@ -80,11 +81,11 @@ int launch(galois_b200_ctx* ctx, bool vec, const __half* a, const galois_dim* ad
     constexpr int RPB = 256 / LPR;
     dim3 grid((unsigned)((N + RPB - 1) / RPB), (unsigned)((xd->ne[1] + NB - 1) / NB), (unsigned)(xd->ne[2] * xd->ne[3]));
     if (vec)
-        mul_mat_f16_kernel<LPR, NB, true><<<grid, 256, 0, ctx->stream>>>(
+        gb_launch(ctx, mul_mat_f16_kernel<LPR, NB, true>, grid, dim3(256), 0, 
             a, ad->nb[1], ad->nb[2], ad->nb[3], ad->ne[2], ad->ne[3], x, xd->nb[1], xd->nb[2], xd->nb[3], dst, dd->nb[1],
             dd->nb[2], dd->nb[3], K, N, xd->ne[1], xd->ne[2], xd->ne[3]);
     else
-        mul_mat_f16_kernel<LPR, NB, false><<<grid, 256, 0, ctx->stream>>>(
+        gb_launch(ctx, mul_mat_f16_kernel<LPR, NB, false>, grid, dim3(256), 0, 
             a, ad->nb[1], ad->nb[2], ad->nb[3], ad->ne[2], ad->ne[3], x, xd->nb[1], xd->nb[2], xd->nb[3], dst, dd->nb[1],
             dd->nb[2], dd->nb[3], K, N, xd->ne[1], xd->ne[2], xd->ne[3]);
     GB_LAUNCHED(ctx, "mul_mat_f16");

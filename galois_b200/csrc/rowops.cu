@@ -42,6 +42,7 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // elements only, mean = sum / K, scale = 1 / sqrt(mean + eps), y = x * scale.
 __global__ void rms_norm_kernel(const float* __restrict__ x, int64_t xb1, int64_t xb2, int64_t xb3, float* __restrict__ y,
                                 int64_t yb1, int64_t yb2, int64_t yb3, int64_t K, int64_t ne1, int64_t ne2, float eps) {
+    gb_pdl_entry();
     __shared__ float red[33];
     const int64_t r = blockIdx.x;
     const int64_t i1 = r % ne1, i2 = (r / ne1) % ne2, i3 = r / (ne1 * ne2);
@@ -68,6 +69,7 @@ __global__ void rope_kernel(const float* __restrict__ x, int64_t xb1, int64_t xb
                             const int32_t* __restrict__ pos, float* __restrict__ y, int64_t yb1, int64_t yb2,
                             int64_t yb3, int64_t ne0, int64_t ne1, int64_t ne2, float theta_scale, float freq_scale,
                             float xpos_base, int xpos_down) {
+    gb_pdl_entry();
     const int64_t r = blockIdx.x;
     const int64_t i1 = r % ne1, i2 = (r / ne1) % ne2, i3 = r / (ne1 * ne2);
     const float p = (float)pos[i2];
@@ -99,6 +101,7 @@ template <bool EXT>
 __global__ void soft_max_kernel(const float* __restrict__ x, int64_t xb1, int64_t xb2, int64_t xb3, float* __restrict__ y,
                                 int64_t yb1, int64_t yb2, int64_t yb3, int64_t nc, int64_t ne1, int64_t ne2,
                                 const uint16_t* __restrict__ exp_lut, float scale, const int32_t* __restrict__ pos) {
+    gb_pdl_entry();
     __shared__ float red[33];
     const int64_t r = blockIdx.x;
     const int64_t i1 = r % ne1, i2 = (r / ne1) % ne2, i3 = r / (ne1 * ne2);
@@ -137,6 +140,7 @@ __global__ void soft_max_kernel(const float* __restrict__ x, int64_t xb1, int64_
 // f32::vec_silu (src/lib.rs:543-549): y = f32(SILU_LUT[bits(f16(x))]).
 __global__ void silu_kernel(const float* __restrict__ x, int64_t xb1, float* __restrict__ y, int64_t yb1, int64_t nc,
                             int64_t nr, const uint16_t* __restrict__ lut) {
+    gb_pdl_entry();
     const int64_t total = nc * nr;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / nc, c = i - r * nc;
@@ -153,6 +157,7 @@ __global__ void add_mul_kernel(const float* __restrict__ a, int64_t ab1, int64_t
                                const float* __restrict__ b, int64_t bb1, int64_t bb2, int64_t bb3, float* __restrict__ dst,
                                int64_t ne00, int64_t ne01, int64_t ne02, int64_t ne03, int64_t ne11, int64_t ne12,
                                int64_t ne13) {
+    gb_pdl_entry();
     const int64_t total = ne00 * ne01 * ne02 * ne03;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t ir = i / ne00, c = i - ir * ne00;
@@ -166,6 +171,7 @@ __global__ void add_mul_kernel(const float* __restrict__ a, int64_t ab1, int64_t
 // ---------------------------------------------------------------- scale
 __global__ void scale_kernel(const float* __restrict__ x, int64_t xb1, float* __restrict__ y, int64_t yb1, int64_t nc,
                              int64_t nr, float s) {
+    gb_pdl_entry();
     const int64_t total = nc * nr;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / nc, c = i - r * nc;
@@ -182,6 +188,7 @@ struct dim4 {
 };
 template <typename OUT>
 __global__ void cpy_kernel(const float* __restrict__ x, dim4 xd, OUT* __restrict__ y, dim4 yd, int64_t total) {
+    gb_pdl_entry();
     for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < total; k += (int64_t)gridDim.x * blockDim.x) {
         int64_t t = k;
         const int64_t i00 = t % xd.ne[0];
@@ -232,7 +239,7 @@ extern "C" int galois_b200_rms_norm_f32(galois_b200_ctx* ctx, const float* x, co
     if (xd->nb[0] != 1 || yd->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "rms_norm: rows must be contiguous");
     const int64_t K = xd->ne[0], nr = xd->ne[1] * xd->ne[2] * xd->ne[3];
     if (K == 0 || nr == 0) return 0;
-    rms_norm_kernel<<<(unsigned)nr, row_threads(K), 0, ctx->stream>>>(x, xd->nb[1], xd->nb[2], xd->nb[3], y, yd->nb[1],
+    gb_launch(ctx, rms_norm_kernel, dim3((unsigned)nr), dim3(row_threads(K)), 0, x, xd->nb[1], xd->nb[2], xd->nb[3], y, yd->nb[1],
                                                                       yd->nb[2], yd->nb[3], K, xd->ne[1], xd->ne[2], eps);
     GB_LAUNCHED(ctx, "rms_norm");
     return 0;
@@ -259,7 +266,7 @@ extern "C" int galois_b200_rope_f32(galois_b200_ctx* ctx, const float* x, const 
     const float theta_scale = powf(freq_base, -2.0f / (float)n_dims);
     int threads = (int)(((ne0 / 2 + 31) / 32) * 32);
     if (threads > 256) threads = 256;
-    rope_kernel<<<(unsigned)nr, threads, 0, ctx->stream>>>(x, xd->nb[1], xd->nb[2], xd->nb[3], pos, y, yd->nb[1], yd->nb[2],
+    gb_launch(ctx, rope_kernel, dim3((unsigned)nr), dim3(threads), 0, x, xd->nb[1], xd->nb[2], xd->nb[3], pos, y, yd->nb[1], yd->nb[2],
                                                            yd->nb[3], ne0, ne1, ne2, theta_scale, freq_scale, xpos_base,
                                                            xpos_down);
     GB_LAUNCHED(ctx, "rope");
@@ -283,10 +290,10 @@ static int soft_max_impl(galois_b200_ctx* ctx, const float* x, const galois_dim*
     }
     const int threads = row_threads(nc);
     if (ext)
-        soft_max_kernel<true><<<(unsigned)nr, threads, 0, ctx->stream>>>(x, xb1, xb2, xb3, y, yb1, yb2, yb3, nc, ne1, ne2,
+        gb_launch(ctx, soft_max_kernel<true>, dim3((unsigned)nr), dim3(threads), 0, x, xb1, xb2, xb3, y, yb1, yb2, yb3, nc, ne1, ne2,
                                                                          ctx->exp_lut, scale, pos);
     else
-        soft_max_kernel<false><<<(unsigned)nr, threads, 0, ctx->stream>>>(x, xb1, xb2, xb3, y, yb1, yb2, yb3, nc, ne1, ne2,
+        gb_launch(ctx, soft_max_kernel<false>, dim3((unsigned)nr), dim3(threads), 0, x, xb1, xb2, xb3, y, yb1, yb2, yb3, nc, ne1, ne2,
                                                                           ctx->exp_lut, 1.0f, nullptr);
     GB_LAUNCHED(ctx, "soft_max");
     return 0;
@@ -311,7 +318,7 @@ extern "C" int galois_b200_silu_f32(galois_b200_ctx* ctx, const float* x, const 
     if (xd->nb[0] != 1 || yd->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "silu: rows must be contiguous");
     const int64_t nc = xd->ne[0], nr = xd->ne[1] * xd->ne[2] * xd->ne[3];
     if (nc == 0 || nr == 0) return 0;
-    silu_kernel<<<ew_grid(nc * nr, ctx->sm_count), 256, 0, ctx->stream>>>(x, xd->nb[1], y, yd->nb[1], nc, nr, ctx->silu_lut);
+    gb_launch(ctx, silu_kernel, dim3(ew_grid(nc * nr, ctx->sm_count)), dim3(256), 0, x, xd->nb[1], y, yd->nb[1], nc, nr, ctx->silu_lut);
     GB_LAUNCHED(ctx, "silu");
     return 0;
 }
@@ -328,11 +335,11 @@ static int add_mul_impl(galois_b200_ctx* ctx, bool mul, const float* a, const ga
     if (total == 0) return 0;
     const int grid = ew_grid(total, ctx->sm_count);
     if (mul)
-        add_mul_kernel<true><<<grid, 256, 0, ctx->stream>>>(a, ad->nb[1], ad->nb[2], ad->nb[3], b, bd->nb[1], bd->nb[2],
+        gb_launch(ctx, add_mul_kernel<true>, dim3(grid), dim3(256), 0, a, ad->nb[1], ad->nb[2], ad->nb[3], b, bd->nb[1], bd->nb[2],
                                                             bd->nb[3], dst, ad->ne[0], ad->ne[1], ad->ne[2], ad->ne[3],
                                                             bd->ne[1], bd->ne[2], bd->ne[3]);
     else
-        add_mul_kernel<false><<<grid, 256, 0, ctx->stream>>>(a, ad->nb[1], ad->nb[2], ad->nb[3], b, bd->nb[1], bd->nb[2],
+        gb_launch(ctx, add_mul_kernel<false>, dim3(grid), dim3(256), 0, a, ad->nb[1], ad->nb[2], ad->nb[3], b, bd->nb[1], bd->nb[2],
                                                              bd->nb[3], dst, ad->ne[0], ad->ne[1], ad->ne[2], ad->ne[3],
                                                              bd->ne[1], bd->ne[2], bd->ne[3]);
     GB_LAUNCHED(ctx, name);
@@ -358,7 +365,7 @@ extern "C" int galois_b200_scale_f32(galois_b200_ctx* ctx, const float* x, const
     if (!gb_is_contiguous(xd) || !gb_is_contiguous(yd)) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "scale: src and dst must be contiguous");
     const int64_t nc = xd->ne[0], nr = xd->ne[1] * xd->ne[2] * xd->ne[3];
     if (nc == 0 || nr == 0) return 0;
-    scale_kernel<<<ew_grid(nc * nr, ctx->sm_count), 256, 0, ctx->stream>>>(x, xd->nb[1], y, yd->nb[1], nc, nr, scale_host);
+    gb_launch(ctx, scale_kernel, dim3(ew_grid(nc * nr, ctx->sm_count)), dim3(256), 0, x, xd->nb[1], y, yd->nb[1], nc, nr, scale_host);
     GB_LAUNCHED(ctx, "scale");
     return 0;
 }
@@ -377,7 +384,7 @@ static int cpy_impl(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, 
         b.ne[i] = yd->ne[i];
         b.nb[i] = yd->nb[i];
     }
-    cpy_kernel<OUT><<<ew_grid(total, ctx->sm_count), 256, 0, ctx->stream>>>(x, a, y, b, total);
+    gb_launch(ctx, cpy_kernel<OUT>, dim3(ew_grid(total, ctx->sm_count)), dim3(256), 0, x, a, y, b, total);
     GB_LAUNCHED(ctx, "cpy");
     return 0;
 }

@@ -259,6 +259,17 @@ def test_mul_mat_q4_0_host_entry(gb, dev, oracle):
                                                       out.ctypes.data_as(C.c_void_p), C.byref(dd))
         assert rc == 0, gb.lib.galois_b200_last_error(dev.ctx)
         assert_close(out, oracle.mul_mat_q4_0(w, x))
+    # pinned (device-mapped) host buffers: the kernel writes the result into host memory itself
+    import torch
+
+    xp = torch.from_numpy(x).pin_memory()
+    op = torch.zeros(b, n, dtype=torch.float32).pin_memory()
+    for _ in range(2):
+        rc = gb.lib.galois_b200_mul_mat_q4_0_f32_host(dev.ctx, C.c_void_p(wt.data_ptr()), C.byref(wt.dim().c_struct()),
+                                                      C.c_void_p(xp.data_ptr()), C.byref(xd), C.c_void_p(op.data_ptr()), C.byref(dd))
+        assert rc == 0, gb.lib.galois_b200_last_error(dev.ctx)
+        assert_close(op.numpy().copy(), oracle.mul_mat_q4_0(w, x))
+        op.zero_()
 
 
 # ------------------------------------------------------------------ F16 mat-mul
