@@ -16,7 +16,7 @@ LIB = os.path.join(HERE, "libgalois_b200.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-lineinfo", "-O3", "-std=c++17", *(["-DGB_TC_SCALAR_EPILOGUE"] if os.environ.get("GB_TC_SCALAR") else []),
+    "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
     "--shared",
     "-cudart", "static",

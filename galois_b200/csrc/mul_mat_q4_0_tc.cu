@@ -8,17 +8,15 @@
 // so each block gets its OWN int32 accumulator tile (no accumulation across blocks in TMEM); the
 // epilogue warps read it back with tcgen05.ld, add the -8 * sum(q8) correction, convert and
 // apply the two f16 block scales in f32.  The tensor pipe is therefore far from saturated: the
-// CUDA-core epilogue (about 3 instructions per output element per block, packed f32x2 math)
-// bounds the kernel.
+// CUDA-core epilogue (about 4.5 instructions per output element per block) bounds the kernel.
 //
 // Operand roles are swapped with respect to the usual GEMM: the 128 weight rows of a CTA tile are
-// the MMA's M side (TMEM lanes = weight rows), the batch is the N side (TMEM columns).  The 512
-// TMEM columns form a ring of 4 (N = 128) or 8 (N = 64) accumulator tiles.
+// the MMA's M side (TMEM lanes = weight rows), the batch is the N side (TMEM columns).
 //
 //   warps 0-7   epilogue: warp w owns TMEM lanes 32*(w%4)..+31 (= weight rows) and the column half
 //               w/4; f32 accumulators live in registers (BN/2 per thread)
-//   warps 8-11  unpack: thread = weight row; keeps three K steps of 144 raw bytes (8 blocks) in
-//               flight with cp.async, writes the nibbles as unsigned bytes into the canonical K-major
+//   warps 8-11  unpack: thread = weight row; reads 144 raw bytes (8 blocks) per K step straight
+//               from global memory, writes the nibbles as unsigned bytes into the canonical K-major
 //               UMMA layout (8-row x 16-byte core matrices, no swizzle) and the f32 block scales
 //   warp 12     MMA issuer (one elected lane) and TMEM allocation
 //   warp 13     loader: 1-D bulk copies (no multicast) of the quantised activations, which the
@@ -35,7 +33,6 @@ namespace {
 constexpr int TC_M = 128;            // weight rows per CTA tile (UMMA M)
 constexpr int TC_KC = 8;             // blocks per K step (144 raw bytes per row)
 constexpr int TC_STAGES = 2;
-constexpr int TC_RAW = 3;             // K steps of raw weights in flight per row (cp.async)
 constexpr int TC_EPI_WARPS = 8;
 constexpr int TC_THREADS = (TC_EPI_WARPS + 4 + 2) * 32;  // 448
 constexpr uint32_t TC_MAGIC = 0x4B400000u;               // 12582912.0f: int -> float by bit tricks
@@ -63,31 +60,18 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// 32 lanes x 16 consecutive 32-bit columns: thread i of the warp gets lane (base + i)
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane (base + i)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
-}
-// packed two-wide f32 arithmetic
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
-    unsigned long long d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)), "l"(*reinterpret_cast<unsigned long long*>(&c)));
-    return *reinterpret_cast<float2*>(&d);
-}
-__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
-    unsigned long long d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
-    return *reinterpret_cast<float2*>(&d);
-}
-__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
-    unsigned long long d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
-    return *reinterpret_cast<float2*>(&d);
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -105,16 +89,14 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo, 
 
 // Shared memory of one CTA (dynamic, 1024-byte aligned):
 //   per stage: A (TC_KC * 128 * 32 unsigned bytes), B (TC_KC * BN * 32 int8), dw (TC_KC * 128 f32),
-//              xs (TC_KC * BN/2 column pairs * {d_x0, d_x1, MAGIC - 8 sum0, MAGIC - 8 sum1});
-//   then the raw-weight ring of the unpack warps and the barriers.
+//              xs (TC_KC * BN * {f32 d_x, i32 MAGIC - 8 * sum}), then the barriers.
 template <int BN>
 struct tc_smem {
     static constexpr uint32_t A_BLOCK = TC_M * 32, B_BLOCK = BN * 32;
     static constexpr uint32_t A_BYTES = TC_KC * A_BLOCK, B_BYTES = TC_KC * B_BLOCK;
     static constexpr uint32_t DW_BYTES = TC_KC * TC_M * 4, XS_BYTES = TC_KC * BN * 8;
     static constexpr uint32_t STAGE = A_BYTES + B_BYTES + DW_BYTES + XS_BYTES;
-    static constexpr uint32_t RAW_OFF = TC_STAGES * STAGE;           // TC_RAW x 128 rows x 144 raw bytes
-    static constexpr uint32_t BAR_OFF = RAW_OFF + TC_RAW * TC_M * 144;
+    static constexpr uint32_t BAR_OFF = TC_STAGES * STAGE;
     static constexpr uint32_t TOTAL = BAR_OFF + 256;
 };
 
@@ -122,7 +104,7 @@ struct tc_smem {
 // <BlockQ8_0 as QuantType>::from_f32, src/ggml_quants.rs:736-764).  Columns are padded to a
 // multiple of BN with zeros.
 //   qs: [col tile][block][2 K chunks][BN/8 col groups][8 cols][16 bytes]
-//   xs: [col tile][block][BN / 2 column pairs] {f32 d0, f32 d1, i32 MAGIC - 8 * sum q0, i32 MAGIC - 8 * sum q1}
+//   xs: [col tile][block][BN] {f32 d, i32 MAGIC - 8 * sum q}
 __global__ void __launch_bounds__(256) quantize_q8_tc_kernel(const float* __restrict__ x, int64_t x_stride, int K, int B, int BN,
                                                              uint8_t* __restrict__ qs, int2* __restrict__ xs) {
     const int nkb = K >> 5;
@@ -151,18 +133,15 @@ __global__ void __launch_bounds__(256) quantize_q8_tc_kernel(const float* __rest
         const size_t blk_base = ((size_t)tile * nkb + kb) * (size_t)(BN * 32);
         const size_t off = blk_base + (size_t)(sub >> 2) * (BN * 16) + (size_t)(ci >> 3) * 128 + (ci & 7) * 16 + (sub & 3) * 4;
         *reinterpret_cast<uint32_t*>(qs + off) = packed;
-        if (sub == 0) {
-            int* pair = reinterpret_cast<int*>(xs) + (((size_t)tile * nkb + kb) * BN + (ci & ~1)) * 2;
-            pair[ci & 1] = __float_as_int(__half2float(__float2half_rn(d)));
-            pair[2 + (ci & 1)] = (int)TC_MAGIC - 8 * s;
-        }
+        if (sub == 0)
+            xs[((size_t)tile * nkb + kb) * BN + ci] = make_int2(__float_as_int(__half2float(__float2half_rn(d))), (int)TC_MAGIC - 8 * s);
     }
 }
 
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     mm_q4_0_tc_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ qs, const uint8_t* __restrict__ xs,
-                      float* __restrict__ dst, int64_t nb1, int K, int N, int B, int* __restrict__ status, int dbg) {
+                      float* __restrict__ dst, int64_t nb1, int K, int N, int B, int* __restrict__ status) {
     using L = tc_smem<BN>;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -174,14 +153,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     uint64_t* a_full = bars;                         // [TC_STAGES] 128 unpack threads
     uint64_t* b_full = bars + TC_STAGES;             // [TC_STAGES] loader + bytes
     uint64_t* stage_empty = bars + 2 * TC_STAGES;    // [TC_STAGES] 8 epilogue warps
-    // All 512 TMEM columns are used as a ring of NBUF accumulator tiles so that the MMA warp runs
-    // several blocks ahead of the epilogue (the full/empty hand-shake latency is amortised).
-    constexpr int NBUF = 512 / BN;
-    constexpr uint32_t TMEM_COLS = 512;
-    uint64_t* tmem_full = bars + 3 * TC_STAGES;              // [NBUF] MMA commit
-    uint64_t* tmem_empty = bars + 3 * TC_STAGES + NBUF;      // [NBUF] 8 epilogue warps
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 3 * TC_STAGES + 2 * NBUF);
-    static_assert((3 * TC_STAGES + 2 * NBUF + 1) * 8 <= 256, "barrier area");
+    uint64_t* tmem_full = bars + 3 * TC_STAGES;      // [2] MMA commit
+    uint64_t* tmem_empty = bars + 3 * TC_STAGES + 2; // [2] 8 epilogue warps
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 3 * TC_STAGES + 4);
+    constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; s++) {
@@ -189,7 +164,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             mbar_init(&b_full[s], 1);
             mbar_init(&stage_empty[s], TC_EPI_WARPS);
         }
-        for (int b = 0; b < NBUF; b++) {
+        for (int b = 0; b < 2; b++) {
             mbar_init(&tmem_full[b], 1);
             mbar_init(&tmem_empty[b], TC_EPI_WARPS);
         }
@@ -207,63 +182,38 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 
     if (warp < TC_EPI_WARPS) {
         // ------------------------------------------------------------ epilogue
-        // Software pipeline over (block, 16-column chunk): the tcgen05.ld of the next chunk is in
-        // flight while the current one is scaled and accumulated.
         const int lane_grp = warp & 3, half = warp >> 2;
         const int row_in_tile = lane_grp * 32 + lane;
-        constexpr int NC = BN / 2;   // columns of this warp
-        constexpr int CH = NC / 16;  // chunks per block
-        static_assert(CH % 2 == 0, "the two register sets alternate across block boundaries");
-        float2 acc[NC / 2];
+        constexpr int NC = BN / 2;  // columns of this warp
+        float acc[NC];
 #pragma unroll
-        for (int c = 0; c < NC / 2; c++) acc[c] = make_float2(0.0f, 0.0f);
-        const int total = nkb * CH;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(half * NC);
-        auto issue = [&](int q, uint32_t* r) -> bool {
-            const int g = q / CH, ch = q % CH, buf = g % NBUF;
-            if (ch == 0) {
-                if (!mbar_wait_bounded(&tmem_full[buf], (uint32_t)(g / NBUF) & 1u)) return false;
-                tc_fence_after();
-            }
-            if (!(dbg & 4)) tmem_ld16(lane_addr + (uint32_t)(buf * BN + ch * 16), r);
-            return true;
-        };
-        uint32_t ra[16], rb[16];
-        ok = issue(0, ra);
+        for (int c = 0; c < NC; c++) acc[c] = 0.0f;
         for (int g = 0; g < nkb && ok; g++) {
-            const int kb = g % TC_KC, s = (g / TC_KC) % TC_STAGES;
+            const int buf = g & 1, step = g / TC_KC, kb = g % TC_KC, s = step % TC_STAGES;
+            ok = mbar_wait_bounded(&tmem_full[buf], (uint32_t)(g >> 1) & 1u);
+            if (!ok) break;
+            tc_fence_after();
             const uint8_t* stage = smem + (uint32_t)s * L::STAGE;
             const float dw = reinterpret_cast<const float*>(stage + L::A_BYTES + L::B_BYTES)[kb * TC_M + row_in_tile];
-            const float2 dw2 = make_float2(dw, dw), bias = make_float2(-12582912.0f, -12582912.0f);
-            // per column pair {d_x0, d_x1, magic - 8 sum0, magic - 8 sum1}: the same for all lanes (broadcast reads)
             const int4* xsp = reinterpret_cast<const int4*>(stage + L::A_BYTES + L::B_BYTES + L::DW_BYTES) + (kb * BN + half * NC) / 2;
 #pragma unroll
-            for (int ch = 0; ch < CH; ch++) {  // fully unrolled: ch, the register set and the accumulators are static
-                const int q = g * CH + ch;
-                uint32_t* cur = (ch & 1) ? rb : ra;
-                uint32_t* nxt = (ch & 1) ? ra : rb;
-                tmem_ld_wait();  // chunk q has landed in `cur`
-                if (ch == CH - 1) {
-                    // the whole block has been read out of TMEM: hand the buffer back to the MMA warp
+            for (int c0 = 0; c0 < NC; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(buf * BN + half * NC + c0), r);
+                tmem_ld_wait();
+                if (c0 + 32 >= NC) {
+                    // all of this warp's columns of the tile have been read: hand the buffer back
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&tmem_empty[g % NBUF]);
+                    if (lane == 0) mbar_arrive(&tmem_empty[buf]);
                 }
-                if (q + 1 < total) ok = issue(q + 1, nxt) && ok;
-                if (!(dbg & 1))
 #pragma unroll
-                for (int c = 0; c < 16; c += 2) {
-                    const int4 sc = xsp[(ch * 16 + c) >> 1];
-#ifdef GB_TC_SCALAR_EPILOGUE
-                    const float f0 = __int_as_float((int)cur[c] + sc.z) - 12582912.0f;
-                    const float f1 = __int_as_float((int)cur[c + 1] + sc.w) - 12582912.0f;
-                    acc[(ch * 16 + c) >> 1].x = fmaf(dw, __int_as_float(sc.x) * f0, acc[(ch * 16 + c) >> 1].x);
-                    acc[(ch * 16 + c) >> 1].y = fmaf(dw, __int_as_float(sc.y) * f1, acc[(ch * 16 + c) >> 1].y);
-#else
-                    const float2 f = make_float2(__int_as_float((int)cur[c] + sc.z), __int_as_float((int)cur[c + 1] + sc.w));
-                    const float2 t = fmul2(make_float2(__int_as_float(sc.x), __int_as_float(sc.y)), fadd2(f, bias));
-                    acc[(ch * 16 + c) >> 1] = ffma2(dw2, t, acc[(ch * 16 + c) >> 1]);
-#endif
+                for (int c = 0; c < 32; c += 2) {
+                    const int4 sc = xsp[(c0 + c) >> 1];  // {d_x, magic - 8 sum} of two columns (same for all lanes)
+                    const float f0 = __int_as_float((int)r[c] + sc.y) - 12582912.0f;
+                    const float f1 = __int_as_float((int)r[c + 1] + sc.w) - 12582912.0f;
+                    acc[c0 + c] = fmaf(dw, __int_as_float(sc.x) * f0, acc[c0 + c]);
+                    acc[c0 + c + 1] = fmaf(dw, __int_as_float(sc.z) * f1, acc[c0 + c + 1]);
                 }
             }
             if (kb == TC_KC - 1) {
@@ -277,7 +227,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 #pragma unroll
                 for (int c = 0; c < NC; c++) {
                     const int col = col_tile * BN + half * NC + c;
-                    if (col < B) dst[(size_t)col * nb1 + row] = (c & 1) ? acc[c >> 1].y : acc[c >> 1].x;
+                    if (col < B) dst[(size_t)col * nb1 + row] = acc[c];
                 }
             }
         }
@@ -287,32 +237,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         int row = row_tile * TC_M + r;
         if (row >= N) row = N - 1;  // ragged last tile: recompute a valid row, never stored
         const uint4* src = reinterpret_cast<const uint4*>(w + (size_t)row * row_bytes);
-        // raw weights: TC_RAW K steps of this row (144 bytes each) are kept in flight with cp.async;
-        // a thread only ever reads back what it copied itself, so no cross-thread hand-shake is needed
-        uint8_t* raw = smem + L::RAW_OFF + (uint32_t)r * 144;
-        auto fetch = [&](int step) {
-            if (step < nsteps) {
-                const uint32_t dst = smem_u32(raw + (uint32_t)(step % TC_RAW) * (TC_M * 144));
+        uint4 cur[9], nxt[9];
 #pragma unroll
-                for (int i = 0; i < 9; i++)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + i * 16), "l"(src + step * 9 + i) : "memory");
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");  // one group per step, empty past the end
-        };
-        for (int st = 0; st < TC_RAW; st++) fetch(st);
+        for (int i = 0; i < 9; i++) cur[i] = __ldg(src + i);
         for (int step = 0; step < nsteps && ok; step++) {
             const int s = step % TC_STAGES;
-            asm volatile("cp.async.wait_group %0;" ::"n"(TC_RAW - 1) : "memory");
-            uint4 cur[9];
+            if (step + 1 < nsteps) {
 #pragma unroll
-            for (int i = 0; i < 9; i++) cur[i] = reinterpret_cast<const uint4*>(raw + (uint32_t)(step % TC_RAW) * (TC_M * 144))[i];
-            fetch(step + TC_RAW);
+                for (int i = 0; i < 9; i++) nxt[i] = __ldg(src + (step + 1) * 9 + i);
+            }
             ok = mbar_wait_bounded(&stage_empty[s], ((uint32_t)(step / TC_STAGES) & 1u) ^ 1u);
             if (!ok) break;
             uint8_t* stage = smem + (uint32_t)s * L::STAGE;
             float* dwp = reinterpret_cast<float*>(stage + L::A_BYTES + L::B_BYTES);
             const uint32_t* t = reinterpret_cast<const uint32_t*>(cur);
-            if (!(dbg & 2))
 #pragma unroll
             for (int p = 0; p < TC_KC / 2; p++) {  // block pairs: 9 words each
                 const uint32_t* tp = t + 9 * p;
@@ -334,8 +272,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             }
             fence_proxy_async();  // the tensor core reads shared memory through the async proxy
             mbar_arrive(&a_full[s]);
+#pragma unroll
+            for (int i = 0; i < 9; i++) cur[i] = nxt[i];
         }
-        asm volatile("cp.async.wait_all;" ::: "memory");  // nothing of this thread is in flight when it leaves
     } else if (warp == 12) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
@@ -350,8 +289,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 const uint32_t a_addr = smem_u32(smem + (uint32_t)s * L::STAGE);
                 const uint32_t b_addr = a_addr + L::A_BYTES;
                 for (int kb = 0; kb < TC_KC; kb++) {
-                    const int g = step * TC_KC + kb, buf = g % (512 / BN);
-                    ok = mbar_wait_bounded(&tmem_empty[buf], ((uint32_t)(g / (512 / BN)) & 1u) ^ 1u);
+                    const int g = step * TC_KC + kb, buf = g & 1;
+                    ok = mbar_wait_bounded(&tmem_empty[buf], ((uint32_t)(g >> 1) & 1u) ^ 1u);
                     if (!ok) break;
                     tc_fence_after();
                     umma_i8(tmem_base + (uint32_t)(buf * BN), umma_desc(a_addr + kb * L::A_BLOCK, TC_M * 16, 128),
@@ -391,7 +330,7 @@ template <int BN>
 int launch_tc(galois_b200_ctx* ctx, const uint8_t* w, const uint8_t* qs, const uint8_t* xs, float* dst, int64_t nb1, int K, int N,
               int B) {
     dim3 grid((unsigned)((N + TC_M - 1) / TC_M), (unsigned)((B + BN - 1) / BN));
-    mm_q4_0_tc_kernel<BN><<<grid, TC_THREADS, tc_smem<BN>::TOTAL, ctx->stream>>>(w, qs, xs, dst, nb1, K, N, B, ctx->dev_status, ctx->tune_dbg);
+    mm_q4_0_tc_kernel<BN><<<grid, TC_THREADS, tc_smem<BN>::TOTAL, ctx->stream>>>(w, qs, xs, dst, nb1, K, N, B, ctx->dev_status);
     GB_LAUNCHED(ctx, "mm_q4_0_tc");
     return 0;
 }
