@@ -254,7 +254,7 @@ extern "C" int galois_b200_synchronize(galois_b200_ctx* ctx) {
 }
 
 // ------------------------------------------------------------------ Q4_0 mat-mul
-static int validate_mul_mat(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const void* x, const galois_dim* xd,
+int gb_validate_mul_mat(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const void* x, const galois_dim* xd,
                             const void* dst, const galois_dim* dd) {
     if (!wd || !xd || !dd) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0: null dim");
     const int64_t K = wd->ne[0], N = wd->ne[1];
@@ -281,7 +281,7 @@ static int validate_mul_mat(galois_b200_ctx* ctx, const void* w, const galois_di
 extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
                                             const galois_dim* xd, float* dst, const galois_dim* dd) {
     GB_CHECK_CTX(ctx);
-    int rc = validate_mul_mat(ctx, w, wd, x, xd, dst, dd);
+    int rc = gb_validate_mul_mat(ctx, w, wd, x, xd, dst, dd);
     if (rc) return rc;
     const int64_t K = wd->ne[0], N = wd->ne[1];
     const int64_t nrows = xd->ne[1] * xd->ne[2] * xd->ne[3];

@@ -48,6 +48,10 @@ int gb_fail(galois_b200_ctx* ctx, int code, const char* fmt, ...);
 // cudaMalloc when needed; growth synchronises the stream first).
 int gb_scratch(galois_b200_ctx* ctx, size_t bytes, void** out);
 
+// Argument checks of MatMul::f_q_f32_f32 shared by the mat-mul entry points (0 = valid).
+int gb_validate_mul_mat(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const void* x, const galois_dim* xd,
+                        const void* dst, const galois_dim* dd);
+
 #define GB_CHECK_CTX(ctx)              \
     do {                               \
         if ((ctx) == nullptr) return GALOIS_B200_E_STATE; \

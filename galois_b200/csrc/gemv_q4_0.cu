@@ -21,15 +21,19 @@
 // BlockQ4_0::vec_dot_q8_0 (src/ggml_quants.rs:156-172); only the order of the f32 additions
 // of the per-block terms differs from the CPU.
 #include "common.cuh"
+#include "gather.cuh"
 #include "gemv_q4_0.cuh"
 #include "ptx.cuh"
 
 namespace {
 
-constexpr int GEMV_WARPS = 4;
+#ifndef GB_GEMV_WARPS
+#define GB_GEMV_WARPS 4
+#endif
+constexpr int GEMV_WARPS = GB_GEMV_WARPS;
 constexpr int GEMV_THREADS = GEMV_WARPS * 32;
 constexpr int GEMV_MAX_STAGES = 6;
-constexpr int GEMV_BAR_BYTES = 256;  // GEMV_WARPS * GEMV_MAX_STAGES mbarriers, padded
+constexpr int GEMV_BAR_BYTES = ((GEMV_WARPS * GEMV_MAX_STAGES + 1) * 8 + 127) & ~127;  // the mbarriers, padded
 
 // One 36-byte block pair held as nine aligned words t[0..8] ({d0 | qs0[0:2]}, qs0[2:14],
 // {qs0[14:16] | d1}, qs1[0:16]) against the 64 int8 activations y[0..15] of the same two blocks.
@@ -172,7 +176,7 @@ __device__ __forceinline__ void quantize_rows_cluster(const float* __restrict__ 
 template <int NB, int SEG, bool SPLIT, int NPASS>
 __global__ void __launch_bounds__(GEMV_THREADS)
     gemv_q4_0_kernel(const uint8_t* __restrict__ w, const float* __restrict__ x, int x_stride, float* __restrict__ dst, int nb1, int K, int N, int nbatch, int stages,
-                     int* __restrict__ status, int dbg) {
+                     int* __restrict__ status, int dbg, const galois_b200_peers P, uint32_t epoch, unsigned* __restrict__ counter) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
 
@@ -293,17 +297,37 @@ __global__ void __launch_bounds__(GEMV_THREADS)
             for (int b = 0; b < NB; b++) {
                 float v = acc[b];
                 for (int o = nsegk >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if ((lane & (nsegk - 1)) == 0 && row0 + r < N && b < nbatch) dst[b * nb1 + row0 + r] = v;
+                if ((lane & (nsegk - 1)) == 0 && row0 + r < N && b < nbatch) {
+                    dst[b * nb1 + row0 + r] = v;
+                    for (int q = 0; q < P.nranks; q++)
+                        if (q != P.rank) P.dst[q][b * nb1 + row0 + r] = v;
+                }
             }
         } else {
 #pragma unroll
             for (int b = 0; b < NB; b++) {
                 const float v = gb_warp_sum(acc[b]);
-                if (lane == 0 && b < nbatch) dst[b * nb1 + row0] = v;
+                if (lane == 0 && b < nbatch) {
+                    dst[b * nb1 + row0] = v;
+                    for (int q = 0; q < P.nranks; q++)
+                        if (q != P.rank) P.dst[q][b * nb1 + row0] = v;
+                }
             }
         }
     }
     if (!ok && lane == 0) atomicExch(status, GALOIS_B200_E_TIMEOUT);
+    if (P.nranks > 0) {
+        // sharded call: this rank's rows went to every peer as well; the last CTA to finish
+        // publishes the band and waits for the peers' bands
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            if (atomicAdd(counter, 1u) == gridDim.x - 1) {
+                *counter = 0;
+                gb_gather_signal_and_wait(P, epoch, 2000000000ull, status);
+            }
+        }
+    }
 }
 
 struct gemv_plan {
@@ -322,7 +346,8 @@ gemv_plan plan_gemv(const galois_b200_ctx* ctx, int64_t K, int64_t N, int64_t B)
     // Lane segment: 4 / 2 / 1 block pairs.  First choice: whole rows per pass (every lane busy).
     // Else the (segment, passes) pair with the best lane utilisation; with one activation row it
     // must keep at most 6 block pairs per lane so that the activations fit in registers.
-    const int max_seg = p.nbt == 1 ? 4 : 2;  // wider segments spill when activations are not hoisted
+    int max_seg = p.nbt == 1 ? 4 : 2;  // wider segments spill when activations are not hoisted
+    if (ctx->tune_r == 1 || ctx->tune_r == 2) max_seg = ctx->tune_r;
     p.seg = 0;
     for (int seg = max_seg; seg >= 1 && !p.seg; seg >>= 1) {
         const int64_t nsegk = npair / seg;
@@ -345,7 +370,7 @@ gemv_plan plan_gemv(const galois_b200_ctx* ctx, int64_t K, int64_t N, int64_t B)
     const size_t chunk = row_bytes * rows_per_chunk;
     const size_t act = (size_t)p.nbt * K + ((((size_t)p.nbt * (K / 32) * 8) + 127) & ~(size_t)127);
     // two CTAs of one kernel per SM plus room for a third (of the next kernel): <= 72 KB per CTA
-    const size_t budget = (size_t)(ctx->tune_smem_kb > 0 ? ctx->tune_smem_kb : 72) * 1024;
+    const size_t budget = (size_t)(ctx->tune_smem_kb > 0 ? ctx->tune_smem_kb : (GEMV_WARPS == 8 ? 110 : 72)) * 1024;
     if (GEMV_BAR_BYTES + act + (size_t)GEMV_WARPS * 2 * chunk > 200 * 1024) return p;
     int stages = 2;
     while (stages < GEMV_MAX_STAGES && GEMV_BAR_BYTES + act + (size_t)GEMV_WARPS * (stages + 1) * chunk <= budget) stages++;
@@ -354,7 +379,7 @@ gemv_plan plan_gemv(const galois_b200_ctx* ctx, int64_t K, int64_t N, int64_t B)
     p.smem = GEMV_BAR_BYTES + act + (size_t)GEMV_WARPS * stages * chunk;
     if (p.smem > 227 * 1024) return p;
     const int64_t nchunks = (N + rows_per_chunk - 1) / rows_per_chunk;
-    const int cps = ctx->tune_ctas_per_sm > 0 ? ctx->tune_ctas_per_sm : 2;
+    const int cps = ctx->tune_ctas_per_sm > 0 ? ctx->tune_ctas_per_sm : (GEMV_WARPS == 8 ? 1 : 2);
     int64_t grid = (int64_t)ctx->sm_count * cps;
     if (grid > (nchunks + GEMV_WARPS - 1) / GEMV_WARPS) grid = (nchunks + GEMV_WARPS - 1) / GEMV_WARPS;
     if (grid < 1) grid = 1;
@@ -384,7 +409,7 @@ cudaError_t gemv_attr() {
 
 template <int NB, int SEG, bool SPLIT, int NPASS>
 int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, const float* x, int x_stride, float* dst, int nb1,
-                int K, int N, int B) {
+                int K, int N, int B, const galois_b200_peers& peers, uint32_t epoch) {
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute at[2];
     int na = 0;
@@ -405,7 +430,8 @@ int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, cons
     cfg.blockDim = dim3(GEMV_THREADS);
     cfg.dynamicSmemBytes = p.smem;
     GB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_0_kernel<NB, SEG, SPLIT, NPASS>, w, x, x_stride, dst, nb1, K, N, B, p.stages,
-                                    ctx->dev_status, ctx->tune_dbg));
+                                    ctx->dev_status, ctx->tune_dbg, peers, epoch,
+                                    reinterpret_cast<unsigned*>(ctx->dev_status) + GB_STATUS_GATHER_COUNTER));
     ctx->launches++;
     return 0;
 }
@@ -434,6 +460,12 @@ bool gb_gemv_supported(const galois_b200_ctx* ctx, const void* w, const galois_d
 
 int gb_gemv_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
                  const galois_dim* dd) {
+    galois_b200_peers none = {};
+    return gb_gemv_q4_0_gather(ctx, w, wd, x, xd, dst, dd, &none, 0);
+}
+
+int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
+                        const galois_dim* dd, const galois_b200_peers* peers, uint32_t epoch) {
     const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
     const gemv_plan p = plan_gemv(ctx, K, N, B);
     if (!p.ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: shape not supported by the streaming GEMV");
@@ -441,7 +473,7 @@ int gb_gemv_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, cons
     const int nb1 = (int)dd->nb[1], xs = (int)xd->nb[1];
 #define X(NB_, SEG_, SPLIT_, NP_)                                                   \
     if (p.nbt == NB_ && p.seg == SEG_ && p.split == SPLIT_ && p.npass == NP_)       \
-        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, x, xs, dst, nb1, K, N, B);
+        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, x, xs, dst, nb1, K, N, B, *peers, epoch);
     GB_GEMV_INSTANCES(X)
 #undef X
     return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: no streaming-GEMV instance for this shape");

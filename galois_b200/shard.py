@@ -7,6 +7,12 @@ holds the (tiny) activations, runs the same kernel on its band and the f32
 outputs are all-gathered into ``[B][N]`` on every rank.  One process per GPU,
 ``torch.distributed`` (NCCL over NVLink on GPUs; gloo in the CPU tests of the
 host logic).
+
+Two exchange steps exist.  ``PeerArena`` + ``PeerShardedMatMul``: the mat-mul
+kernel itself stores its band into every rank's result buffer over NVLink peer
+memory and a device-side arrival protocol replaces the collective (one kernel
+per mat-mul at decode batches).  ``RowShardedMatMul``: NCCL all-gather, kept as
+the baseline and for process groups whose ranks cannot map each other's memory.
 """
 from __future__ import annotations
 
@@ -14,8 +20,8 @@ import ctypes as C
 
 import numpy as np
 
-from ._lib import lib
-from .tensor import Device, Dim, GError, GGmlType, Tensor
+from ._lib import IPC_HANDLE_BYTES, MAX_RANKS, GaloisPeers, lib
+from .tensor import Device, Dim, GError, GGmlType, Tensor, _check
 
 
 def shard_rows(n: int, world: int, rank: int) -> tuple[int, int]:
@@ -33,6 +39,130 @@ def shard_q4_0_bytes(w_bytes: np.ndarray, n: int, k: int, world: int, rank: int)
     w = np.ascontiguousarray(w_bytes).view(np.uint8).reshape(n, row_bytes)
     r0, nr = shard_rows(n, world, rank)
     return w[r0 : r0 + nr].reshape(-1)
+
+
+class _RawDeviceBytes:
+    """Lets torch alias memory that galois_b200_alloc returned (CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerArena:
+    """One device buffer per rank, mapped into every other rank of `group` (CUDA IPC over
+    NVLink).  The first 256 bytes hold the arrival words of the exchange protocol; result buffers
+    are carved out behind them at the same offset on every rank, so a buffer's address on any
+    peer is that peer's base plus the offset.  Every rank must make the same sequence of
+    ``alloc_f32`` calls."""
+
+    HEADER = 256
+
+    def __init__(self, dev, nbytes: int, group=None):
+        import torch
+        import torch.distributed as dist
+
+        self.dev, self.group = dev, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if not 2 <= self.world <= MAX_RANKS:
+            raise GError(f"PeerArena: {self.world} ranks (2..{MAX_RANKS})")
+        self.nbytes = (int(nbytes) + self.HEADER + 255) // 256 * 256
+        base = C.c_void_p()
+        _check(dev.ctx, lib.galois_b200_alloc(dev.ctx, self.nbytes, C.byref(base)), "PeerArena alloc")
+        self.base = base.value
+        self.bytes = torch.as_tensor(_RawDeviceBytes(self.base, self.nbytes), device=dev.torch_device)
+        self.bytes.zero_()
+        torch.cuda.synchronize(dev.torch_device)
+        handle = C.create_string_buffer(IPC_HANDLE_BYTES)
+        _check(dev.ctx, lib.galois_b200_ipc_export(dev.ctx, C.c_void_p(self.base), handle), "ipc_export")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.bases = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.bases.append(self.base)
+                continue
+            ptr = C.c_void_p()
+            _check(dev.ctx, lib.galois_b200_ipc_import(dev.ctx, h, C.byref(ptr)), f"ipc_import (rank {r})")
+            self.bases.append(ptr.value)
+        dist.barrier(group=group)  # every rank has zeroed its words and mapped its peers
+        self._top = self.HEADER
+        self.epoch = 0
+        self._last_target = None
+
+    def alloc_f32(self, n: int):
+        """(offset in bytes, flat torch f32 tensor over the local copy) of a buffer of n floats."""
+        import torch
+
+        off = self._top
+        size = (4 * int(n) + 255) // 256 * 256
+        if off + size > self.nbytes:
+            raise GError(f"PeerArena: out of space ({off + size} > {self.nbytes} bytes)")
+        self._top = off + size
+        return off, self.bytes[off : off + 4 * int(n)].view(torch.float32)
+
+    def peers(self, offset: int) -> GaloisPeers:
+        p = GaloisPeers()
+        p.rank, p.nranks = self.rank, self.world
+        for r in range(self.world):
+            p.dst[r] = self.bases[r] + offset
+            p.flags[r] = self.bases[r]
+        return p
+
+    def next_epoch(self, offset: int) -> int:
+        """Epoch of the next exchange into the buffer at `offset`; two exchanges in a row must not
+        target the same buffer (a peer could still be reading the earlier result)."""
+        if offset == self._last_target:
+            raise GError("PeerArena: two exchanges in a row into the same buffer; alternate two buffers")
+        self._last_target = offset
+        self.epoch += 1
+        return self.epoch
+
+    def close(self):
+        if getattr(self, "base", None):
+            import torch
+
+            torch.cuda.synchronize(self.dev.torch_device)
+            self.bytes = None
+            for r, b in enumerate(self.bases):
+                if r != self.rank:
+                    lib.galois_b200_ipc_close(self.dev.ctx, C.c_void_p(b))
+            lib.galois_b200_free(self.dev.ctx, C.c_void_p(self.base))
+            self.base = None
+
+
+class PeerShardedMatMul:
+    """`W` [N][K] Q4_0 sharded by rows over the ranks of the arena's group; ``forward(x)``
+    returns the full ``[B][N]`` f32 result on every rank.  The exchange is part of the mat-mul
+    call (``galois_b200_mul_mat_q4_0_f32_gather``): peer stores over NVLink and a device-side
+    arrival protocol, no collective library call.  Results alternate between two buffers."""
+
+    def __init__(self, w_local: Tensor, n_total: int, arena: PeerArena, max_batch: int = 1):
+        self.arena = arena
+        self.n_total = n_total
+        self.k = w_local.dim().shape[0]
+        self.r0, self.nr = shard_rows(n_total, arena.world, arena.rank)
+        if w_local.dim().shape[1] != self.nr:
+            raise GError(f"rank {arena.rank} holds {w_local.dim().shape[1]} rows, expected {self.nr}")
+        self.w_local = w_local
+        self.max_batch = max_batch
+        self._bufs = [arena.alloc_f32(n_total * max_batch) for _ in range(2)]
+        self._turn = 0
+
+    def forward(self, x: Tensor) -> Tensor:
+        batch = x.dim().shape[1]
+        if batch > self.max_batch:
+            raise GError(f"batch {batch} > max_batch {self.max_batch}")
+        off, flat = self._bufs[self._turn]
+        self._turn ^= 1
+        dev = x.device.gpu
+        full = Tensor(GGmlType.F32, Dim.ggml((self.n_total, batch), GGmlType.F32), flat, x.device)
+        peers = self.arena.peers(off)
+        epoch = self.arena.next_epoch(off)
+        wd, xd, dd = self.w_local.dim().c_struct(), x.dim().c_struct(), full.dim().c_struct()
+        rc = lib.galois_b200_mul_mat_q4_0_f32_gather(dev.ctx, C.c_void_p(self.w_local.data_ptr()), C.byref(wd), C.c_void_p(x.data_ptr()),
+                                                     C.byref(xd), C.byref(peers), C.byref(dd), self.r0, epoch)
+        _check(dev.ctx, rc, "mul_mat_q4_0_f32_gather")
+        return full
 
 
 class RowShardedMatMul:

@@ -226,6 +226,44 @@ int galois_b200_cpy_f32_f16(galois_b200_ctx* ctx, const float* x, const galois_d
  * independent (src/op.rs:1540-1543).  Boundaries are multiples of 32 rows. */
 int galois_b200_shard_rows(int64_t n, int world, int rank, int64_t* row0, int64_t* nrows);
 
+/* Peer memory for the sharded mat-mul (no reference counterpart).  One process per
+ * GPU: each rank allocates a buffer with galois_b200_alloc, exports it, passes the
+ * 64 opaque bytes to its peers by any host channel, and imports theirs; the
+ * imported address is valid on the importing context's device (peer access over
+ * NVLink is enabled on first use). */
+#define GALOIS_B200_IPC_HANDLE_BYTES 64
+int galois_b200_ipc_export(galois_b200_ctx* ctx, const void* dev, unsigned char handle[GALOIS_B200_IPC_HANDLE_BYTES]);
+int galois_b200_ipc_import(galois_b200_ctx* ctx, const unsigned char handle[GALOIS_B200_IPC_HANDLE_BYTES], void** out_dev);
+int galois_b200_ipc_close(galois_b200_ctx* ctx, void* imported_dev);
+
+#define GALOIS_B200_MAX_RANKS 8
+typedef struct galois_b200_peers {
+    int32_t rank, nranks;               /* this rank, ranks in the group (2..8) */
+    float* dst[GALOIS_B200_MAX_RANKS];  /* dst[p]: rank p's copy of the full [B][N] result, as an
+                                           address valid on THIS device; dst[rank] is local */
+    uint32_t* flags[GALOIS_B200_MAX_RANKS]; /* flags[p]: rank p's arrival words (>= nranks uint32,
+                                           zero before the first call); flags[rank] is local */
+} galois_b200_peers;
+
+/* Sharded MatMul::f_q_f32_f32 with the exchange fused in: computes rows
+ * [row0, row0 + wd->ne[1]) of the full result from this rank's band `w_band`,
+ * stores them into EVERY rank's result buffer at their final place (plain peer
+ * stores over NVLink; no NCCL call, no staging copy), then publishes `epoch` in
+ * every peer's arrival word for this rank and waits, on the device and for at
+ * most about two seconds, until all peers have published `epoch` here.  When the
+ * work enqueued by this call has completed on this rank's stream, dst[rank]
+ * holds all N rows.  `dd_full` describes the full result (ne = [N, B], dense
+ * rows: nb[1] >= N).  Every rank of the group makes the same sequence of calls
+ * with the same `epoch`, which must grow by one from call to call on a given
+ * flags array (start at 1).  A result buffer may be the target of call e + 1 only
+ * if it was not the target of call e (alternate two buffers): a peer publishes
+ * e + 1 only after the kernels that read its copy of the call e result have run.
+ * A wait that runs out reports GALOIS_B200_E_TIMEOUT from the next
+ * galois_b200_synchronize; the context stays usable. */
+int galois_b200_mul_mat_q4_0_f32_gather(galois_b200_ctx* ctx, const void* w_band, const galois_dim* wd, const float* x,
+                                        const galois_dim* xd, const galois_b200_peers* peers, const galois_dim* dd_full,
+                                        int64_t row0, uint32_t epoch);
+
 #ifdef __cplusplus
 }
 #endif
