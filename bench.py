@@ -243,11 +243,23 @@ def run_ours(args):
     xs = {k: torch.randn(B, k, generator=g, device=device, dtype=torch.float32) for k in (HIDDEN, FFN)}
     xdims = {k: gb.Dim.ggml((k, B), gb.GGmlType.F32).c_struct() for k in (HIDDEN, FFN)}
     outs, odims, fulls = {}, {}, {}
+    peer_exchange = world > 1 and args.exchange == "peer"
+    arena, inbox, full_dims = None, None, {}
+    if peer_exchange:
+        # the mat-mul kernel stores its results into every peer's inbox (IPC-mapped arena) and collects the peers' bands
+        from galois_b200.shard import PeerArena, PeerInbox, band_slots, inbox_bytes
+
+        slots = max(band_slots(n, world, B) for _, n, _ in shapes)
+        arena = PeerArena(dev, inbox_bytes(world, slots) + 4096)
+        inbox = PeerInbox(arena, slots)
     for name, n, k in shapes:
         nr = bands[name][1]
         outs[name] = torch.zeros(B, nr, device=device, dtype=torch.float32)
         odims[name] = gb.Dim.ggml((nr, B), gb.GGmlType.F32).c_struct()
-        if world > 1:
+        if peer_exchange:
+            fulls[name] = torch.zeros(B, n, device=device, dtype=torch.float32)
+            full_dims[name] = gb.Dim.ggml((n, B), gb.GGmlType.F32).c_struct()
+        elif world > 1:
             fulls[name] = torch.zeros(world, B, nr, device=device, dtype=torch.float32)
     weight_bytes = sum(w[0].numel() for ws in weights for w in ws)
     bytes_step = nsets * sum(algorithmic_bytes(n, k, B) for _, n, k in shapes)  # whole job, all ranks
@@ -259,11 +271,21 @@ def run_ours(args):
         if rc != 0:
             raise RuntimeError(f"mul_mat_q4_0 failed: {lib.galois_b200_last_error(ctx)} ({rc})")
 
+    def mul_mat_gather(wbuf, wdim, k, name):
+        rc = lib.galois_b200_mul_mat_q4_0_f32_gather(ctx, C.c_void_p(wbuf.data_ptr()), C.byref(wdim), C.c_void_p(xs[k].data_ptr()),
+                                                     C.byref(xdims[k]), C.c_void_p(fulls[name].data_ptr()), C.byref(full_dims[name]),
+                                                     bands[name][0], C.byref(inbox.peers), inbox.next_epoch())
+        if rc != 0:
+            raise RuntimeError(f"mul_mat_q4_0 gather failed: {lib.galois_b200_last_error(ctx)} ({rc})")
+
     def step():
         for ws in weights:
             for (name, n, k), (wbuf, wdim) in zip(shapes, ws):
+                if peer_exchange:  # the exchange step is inside the mat-mul kernel: peer stores + arrival words
+                    mul_mat_gather(wbuf, wdim, k, name)
+                    continue
                 mul_mat(wbuf, wdim, k, name)
-                if world > 1:  # the exchange step: all-gather of the f32 output bands
+                if world > 1:  # the exchange step as an NCCL all-gather of the f32 output bands
                     dist.all_gather_into_tensor(fulls[name], outs[name])
 
     def sync_all():
@@ -466,7 +488,8 @@ def run_ours(args):
                        "weight_bytes_resident_per_gpu": weight_bytes,
                        "l2": f"inputs larger than L2: {weight_bytes / L2_BYTES:.1f}x the 126 MB L2 streamed between reuses",
                        "launch": "cuda_graph" if use_graph else "stream",
-                       "parallelism": f"rows/{world} + nccl all_gather" if world > 1 else "single gpu"},
+                       "parallelism": (f"rows/{world} + " + ("packet exchange over NVLink peer memory fused into the mat-mul kernel" if peer_exchange else "nccl all_gather"))
+                       if world > 1 else "single gpu"},
             "roofline": {"bound": "hbm", "kernel": "gemv_q4_0_kernel" if B <= 4 else ("mmv_q4_0_bulk_kernel" if B <= 8 else "mm_q4_0_tc_kernel"), "achieved": achieved, "peak": peak, "unit": UNIT,
                          "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
                          "kernel_us": kernel_ms * 1e3, "algorithmic_bytes_per_launch": local_bytes_call,
@@ -482,6 +505,9 @@ def run_ours(args):
         if extra is not None:
             line["extra"] = extra
         print(json.dumps(line), flush=True)
+    if arena is not None:
+        dev.synchronize()  # surfaces a device-side wait that ran out
+        arena.close()
     if world > 1:
         dist.destroy_process_group()
     dev.close()
@@ -495,6 +521,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--sets", type=int, default=16, help="distinct FFN weight sets per step (16 -> 1.2 GB of Q4_0)")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="N > 1: how output bands travel (peer = stores over NVLink from the mat-mul kernel; nccl = all-gather)")
     ap.add_argument("--no-graph", action="store_true", help="plain stream launches instead of one CUDA graph per step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the decode-layer / prefill / batch 4-8 side measurements")

@@ -23,10 +23,10 @@ IPC_HANDLE_BYTES = 64
 
 
 class GaloisPeers(C.Structure):
-    """``galois_b200_peers``: every rank's copy of a gathered result and its arrival words, as
-    addresses valid on this rank's device."""
+    """``galois_b200_peers``: every rank's inbox of the fused exchange, as addresses valid on this
+    rank's device."""
 
-    _fields_ = [("rank", C.c_int32), ("nranks", C.c_int32), ("dst", C.c_void_p * MAX_RANKS), ("flags", C.c_void_p * MAX_RANKS)]
+    _fields_ = [("rank", C.c_int32), ("nranks", C.c_int32), ("slots", C.c_int64), ("inbox", C.c_void_p * MAX_RANKS)]
 
 
 _P, _F, _I, _I64, _SZ = C.c_void_p, C.c_float, C.c_int, C.c_int64, C.c_size_t
@@ -68,7 +68,7 @@ SIGNATURES = {
     "galois_b200_ipc_export": ([_P, _P, C.c_char_p], _I),
     "galois_b200_ipc_import": ([_P, C.c_char_p, C.POINTER(_P)], _I),
     "galois_b200_ipc_close": ([_P, _P], _I),
-    "galois_b200_mul_mat_q4_0_f32_gather": ([_P, _P, _DP, _P, _DP, C.POINTER(GaloisPeers), _DP, _I64, C.c_uint32], _I),
+    "galois_b200_mul_mat_q4_0_f32_gather": ([_P, _P, _DP, _P, _DP, _P, _DP, _I64, C.POINTER(GaloisPeers), C.c_uint32], _I),
 }
 
 

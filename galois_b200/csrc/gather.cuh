@@ -1,50 +1,74 @@
 // Internal interface of the peer-memory exchange step of the row-sharded mat-mul (gather.cu).
+//
+// Protocol: a result travels as one 8-byte packet {f32 bits, epoch} written with a single 64-bit
+// store into the receiver's inbox, so a packet is its own arrival flag and the sender needs no
+// fence.  A receiver's inbox has two halves used by even and odd epochs; each half has one area
+// of `slots` packets per sender, indexed b * rows_of_the_sender's_band + r.
 #pragma once
 #include "common.cuh"
 
-// Word index, inside the context's 256-byte status block, of the counter that finds the last CTA
-// of a kernel that publishes a band (word 0 is the bounded-wait status).
-constexpr int GB_STATUS_GATHER_COUNTER = 16;
+struct gb_gather_args {
+    galois_b200_peers P;   // P.nranks == 0: the call is not sharded
+    uint32_t epoch;
+    int B;                 // activation rows
+    long long nb1;         // row stride of the full result, in floats
+    float* dst_full;       // this rank's full [B][N] result
+    int band_row0[GALOIS_B200_MAX_RANKS];
+    int band_rows[GALOIS_B200_MAX_RANKS];
+};
 
-// Copies rows [row0, row0 + n_r) of the local result to every peer and runs the arrival protocol
-// (one launch, dependent on the kernel in front of it).
-int gb_gather_push(galois_b200_ctx* ctx, const galois_b200_peers* peers, const galois_dim* dd_full, int64_t row0, int64_t n_r,
-                   uint32_t epoch);
+// Fills `out` for rank peers->rank of a result with N rows (bands of galois_b200_shard_rows).
+int gb_gather_args_fill(galois_b200_ctx* ctx, const galois_b200_peers* peers, float* dst_full, const galois_dim* dd_full,
+                        uint32_t epoch, gb_gather_args* out);
+// One launch, dependent on the kernel in front of it: sends rows [row0, row0 + n_r) of the local
+// result to every peer, then receives the peers' bands.
+int gb_gather_exchange(galois_b200_ctx* ctx, const gb_gather_args& args);
 
 #ifdef __CUDACC__
-__device__ __forceinline__ void gb_st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t gb_ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
+constexpr unsigned long long GB_GATHER_WAIT_NS = 2000000000ull;  // two seconds
+
 __device__ __forceinline__ unsigned long long gb_globaltimer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
 
-// Called by ONE thread of the last CTA of a kernel, after every CTA has fenced its peer stores at
-// system scope: publishes `epoch` in this rank's word on every peer, then waits until every peer's
-// word here has reached `epoch`.  The wait gives up after `limit_ns` and records
-// GALOIS_B200_E_TIMEOUT in *status.
-__device__ __forceinline__ void gb_gather_signal_and_wait(const galois_b200_peers& P, uint32_t epoch, unsigned long long limit_ns,
-                                                          int* status) {
-    __threadfence_system();
-    for (int p = 0; p < P.nranks; p++)
-        if (p != P.rank) gb_st_release_sys(P.flags[p] + P.rank, epoch);
-    const unsigned long long t0 = gb_globaltimer_ns();
-    for (int p = 0; p < P.nranks; p++) {
-        if (p == P.rank) continue;
-        const uint32_t* word = P.flags[P.rank] + p;
-        unsigned spins = 0;
-        while ((int32_t)(gb_ld_acquire_sys(word) - epoch) < 0) {
-            if ((++spins & 63u) == 0 && gb_globaltimer_ns() - t0 > limit_ns) {
-                atomicExch(status, GALOIS_B200_E_TIMEOUT);
-                return;
+// Result `v` of activation row b, row r of this rank's band, to every peer.
+__device__ __forceinline__ void gb_gather_send(const gb_gather_args& G, int b, int r, float v) {
+    const unsigned long long pkt = ((unsigned long long)G.epoch << 32) | (unsigned long long)__float_as_uint(v);
+    const long long slot =
+        ((long long)(G.epoch & 1u) * G.P.nranks + G.P.rank) * G.P.slots + (long long)b * G.band_rows[G.P.rank] + r;
+    for (int q = 0; q < G.P.nranks; q++)
+        if (q != G.P.rank) asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(G.P.inbox[q] + slot), "l"(pkt) : "memory");
+}
+
+// Thread `tid` of `nthreads` moves its share of the peers' packets of this epoch from the local
+// inbox into the full result.  Polls are bounded by the global timer; on time-out the thread
+// records GALOIS_B200_E_TIMEOUT in *status and stops.
+__device__ __forceinline__ void gb_gather_receive(const gb_gather_args& G, long long tid, long long nthreads, int* status) {
+    unsigned long long t0 = 0;
+    for (int p = 0; p < G.P.nranks; p++) {
+        if (p == G.P.rank) continue;
+        const uint64_t* area = G.P.inbox[G.P.rank] + ((long long)(G.epoch & 1u) * G.P.nranks + p) * G.P.slots;
+        const int n_p = G.band_rows[p];
+        const long long total = (long long)G.B * n_p;
+        for (long long i = tid; i < total; i += nthreads) {
+            unsigned long long pkt;
+            unsigned spins = 0;
+            for (;;) {
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(pkt) : "l"(area + i) : "memory");
+                if ((uint32_t)(pkt >> 32) == G.epoch) break;
+                if ((++spins & 255u) == 0) {
+                    const unsigned long long now = gb_globaltimer_ns();
+                    if (t0 == 0) t0 = now;
+                    if (now - t0 > GB_GATHER_WAIT_NS) {
+                        atomicExch(status, GALOIS_B200_E_TIMEOUT);
+                        return;
+                    }
+                }
             }
+            const long long b = i / n_p, r = i - b * n_p;
+            G.dst_full[b * G.nb1 + G.band_row0[p] + r] = __uint_as_float((uint32_t)pkt);
         }
     }
 }

@@ -176,7 +176,7 @@ __device__ __forceinline__ void quantize_rows_cluster(const float* __restrict__ 
 template <int NB, int SEG, bool SPLIT, int NPASS>
 __global__ void __launch_bounds__(GEMV_THREADS)
     gemv_q4_0_kernel(const uint8_t* __restrict__ w, const float* __restrict__ x, int x_stride, float* __restrict__ dst, int nb1, int K, int N, int nbatch, int stages,
-                     int* __restrict__ status, int dbg, const galois_b200_peers P, uint32_t epoch, unsigned* __restrict__ counter) {
+                     int* __restrict__ status, int dbg, const gb_gather_args G) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
 
@@ -299,8 +299,7 @@ __global__ void __launch_bounds__(GEMV_THREADS)
                 for (int o = nsegk >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
                 if ((lane & (nsegk - 1)) == 0 && row0 + r < N && b < nbatch) {
                     dst[b * nb1 + row0 + r] = v;
-                    for (int q = 0; q < P.nranks; q++)
-                        if (q != P.rank) P.dst[q][b * nb1 + row0 + r] = v;
+                    if (G.P.nranks) gb_gather_send(G, b, row0 + r, v);
                 }
             }
         } else {
@@ -309,25 +308,15 @@ __global__ void __launch_bounds__(GEMV_THREADS)
                 const float v = gb_warp_sum(acc[b]);
                 if (lane == 0 && b < nbatch) {
                     dst[b * nb1 + row0] = v;
-                    for (int q = 0; q < P.nranks; q++)
-                        if (q != P.rank) P.dst[q][b * nb1 + row0] = v;
+                    if (G.P.nranks) gb_gather_send(G, b, row0, v);
                 }
             }
         }
     }
     if (!ok && lane == 0) atomicExch(status, GALOIS_B200_E_TIMEOUT);
-    if (P.nranks > 0) {
-        // sharded call: this rank's rows went to every peer as well; the last CTA to finish
-        // publishes the band and waits for the peers' bands
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            __threadfence_system();
-            if (atomicAdd(counter, 1u) == gridDim.x - 1) {
-                *counter = 0;
-                gb_gather_signal_and_wait(P, epoch, 2000000000ull, status);
-            }
-        }
-    }
+    // sharded call: every result went to the peers' inboxes as well; now collect the peers' bands
+    if (G.P.nranks > 0)
+        gb_gather_receive(G, (long long)blockIdx.x * GEMV_THREADS + threadIdx.x, (long long)gridDim.x * GEMV_THREADS, status);
 }
 
 struct gemv_plan {
@@ -409,7 +398,7 @@ cudaError_t gemv_attr() {
 
 template <int NB, int SEG, bool SPLIT, int NPASS>
 int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, const float* x, int x_stride, float* dst, int nb1,
-                int K, int N, int B, const galois_b200_peers& peers, uint32_t epoch) {
+                int K, int N, int B, const gb_gather_args& gather) {
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute at[2];
     int na = 0;
@@ -430,8 +419,7 @@ int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, cons
     cfg.blockDim = dim3(GEMV_THREADS);
     cfg.dynamicSmemBytes = p.smem;
     GB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_0_kernel<NB, SEG, SPLIT, NPASS>, w, x, x_stride, dst, nb1, K, N, B, p.stages,
-                                    ctx->dev_status, ctx->tune_dbg, peers, epoch,
-                                    reinterpret_cast<unsigned*>(ctx->dev_status) + GB_STATUS_GATHER_COUNTER));
+                                    ctx->dev_status, ctx->tune_dbg, gather));
     ctx->launches++;
     return 0;
 }
@@ -460,12 +448,12 @@ bool gb_gemv_supported(const galois_b200_ctx* ctx, const void* w, const galois_d
 
 int gb_gemv_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
                  const galois_dim* dd) {
-    galois_b200_peers none = {};
-    return gb_gemv_q4_0_gather(ctx, w, wd, x, xd, dst, dd, &none, 0);
+    gb_gather_args none = {};
+    return gb_gemv_q4_0_gather(ctx, w, wd, x, xd, dst, dd, &none);
 }
 
 int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
-                        const galois_dim* dd, const galois_b200_peers* peers, uint32_t epoch) {
+                        const galois_dim* dd, const gb_gather_args* gather) {
     const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
     const gemv_plan p = plan_gemv(ctx, K, N, B);
     if (!p.ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: shape not supported by the streaming GEMV");
@@ -473,7 +461,7 @@ int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* w
     const int nb1 = (int)dd->nb[1], xs = (int)xd->nb[1];
 #define X(NB_, SEG_, SPLIT_, NP_)                                                   \
     if (p.nbt == NB_ && p.seg == SEG_ && p.split == SPLIT_ && p.npass == NP_)       \
-        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, x, xs, dst, nb1, K, N, B, *peers, epoch);
+        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, x, xs, dst, nb1, K, N, B, *gather);
     GB_GEMV_INSTANCES(X)
 #undef X
     return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: no streaming-GEMV instance for this shape");

@@ -1,6 +1,7 @@
 // Internal interface of the streaming decode GEMV (gemv_q4_0.cu).
 #pragma once
 #include "common.cuh"
+#include "gather.cuh"
 
 // Sets the shared-memory limit of every kernel instance on the current device.
 int gb_gemv_init(galois_b200_ctx* ctx);
@@ -12,8 +13,8 @@ bool gb_gemv_supported(const galois_b200_ctx* ctx, const void* w, const galois_d
 // dependent launch when the context allows it).  Needs no scratch memory.
 int gb_gemv_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
                  const galois_dim* dd);
-// The same launch for one band of a row-sharded mat-mul: `dst` and every peers->dst[q] point at
-// the band's first row inside rank q's copy of the full result (peers->nranks == 0: not sharded).
-// Each result goes to all ranks and the kernel's last CTA runs the arrival protocol of gather.cu.
+// The same launch for one band of a row-sharded mat-mul: `dst` points at the band's first row
+// inside this rank's full result (gather->P.nranks == 0: not sharded).  Each result also goes to
+// every peer's inbox and the kernel's tail receives the peers' bands (protocol of gather.cuh).
 int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
-                        const galois_dim* dd, const galois_b200_peers* peers, uint32_t epoch);
+                        const galois_dim* dd, const gb_gather_args* gather);

@@ -9,9 +9,9 @@ outputs are all-gathered into ``[B][N]`` on every rank.  One process per GPU,
 host logic).
 
 Two exchange steps exist.  ``PeerArena`` + ``PeerShardedMatMul``: the mat-mul
-kernel itself stores its band into every rank's result buffer over NVLink peer
-memory and a device-side arrival protocol replaces the collective (one kernel
-per mat-mul at decode batches).  ``RowShardedMatMul``: NCCL all-gather, kept as
+kernel itself stores its results into every rank's inbox over NVLink peer
+memory as self-flagging packets and its tail collects the peers' bands (one
+kernel per mat-mul at decode batches).  ``RowShardedMatMul``: NCCL all-gather, kept as
 the baseline and for process groups whose ranks cannot map each other's memory.
 """
 from __future__ import annotations
@@ -50,12 +50,9 @@ class _RawDeviceBytes:
 
 class PeerArena:
     """One device buffer per rank, mapped into every other rank of `group` (CUDA IPC over
-    NVLink).  The first 256 bytes hold the arrival words of the exchange protocol; result buffers
-    are carved out behind them at the same offset on every rank, so a buffer's address on any
+    NVLink).  Pieces are carved out at the same offset on every rank, so a piece's address on any
     peer is that peer's base plus the offset.  Every rank must make the same sequence of
-    ``alloc_f32`` calls."""
-
-    HEADER = 256
+    ``alloc`` calls.  The buffer starts zeroed."""
 
     def __init__(self, dev, nbytes: int, group=None):
         import torch
@@ -65,7 +62,7 @@ class PeerArena:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if not 2 <= self.world <= MAX_RANKS:
             raise GError(f"PeerArena: {self.world} ranks (2..{MAX_RANKS})")
-        self.nbytes = (int(nbytes) + self.HEADER + 255) // 256 * 256
+        self.nbytes = (int(nbytes) + 255) // 256 * 256
         base = C.c_void_p()
         _check(dev.ctx, lib.galois_b200_alloc(dev.ctx, self.nbytes, C.byref(base)), "PeerArena alloc")
         self.base = base.value
@@ -84,38 +81,17 @@ class PeerArena:
             ptr = C.c_void_p()
             _check(dev.ctx, lib.galois_b200_ipc_import(dev.ctx, h, C.byref(ptr)), f"ipc_import (rank {r})")
             self.bases.append(ptr.value)
-        dist.barrier(group=group)  # every rank has zeroed its words and mapped its peers
-        self._top = self.HEADER
-        self.epoch = 0
-        self._last_target = None
+        dist.barrier(group=group)  # every rank has zeroed its buffer and mapped its peers
+        self._top = 0
 
-    def alloc_f32(self, n: int):
-        """(offset in bytes, flat torch f32 tensor over the local copy) of a buffer of n floats."""
-        import torch
-
+    def alloc(self, nbytes: int) -> int:
+        """Offset in bytes of a new 256-byte aligned piece."""
         off = self._top
-        size = (4 * int(n) + 255) // 256 * 256
+        size = (int(nbytes) + 255) // 256 * 256
         if off + size > self.nbytes:
             raise GError(f"PeerArena: out of space ({off + size} > {self.nbytes} bytes)")
         self._top = off + size
-        return off, self.bytes[off : off + 4 * int(n)].view(torch.float32)
-
-    def peers(self, offset: int) -> GaloisPeers:
-        p = GaloisPeers()
-        p.rank, p.nranks = self.rank, self.world
-        for r in range(self.world):
-            p.dst[r] = self.bases[r] + offset
-            p.flags[r] = self.bases[r]
-        return p
-
-    def next_epoch(self, offset: int) -> int:
-        """Epoch of the next exchange into the buffer at `offset`; two exchanges in a row must not
-        target the same buffer (a peer could still be reading the earlier result)."""
-        if offset == self._last_target:
-            raise GError("PeerArena: two exchanges in a row into the same buffer; alternate two buffers")
-        self._last_target = offset
-        self.epoch += 1
-        return self.epoch
+        return off
 
     def close(self):
         if getattr(self, "base", None):
@@ -130,11 +106,39 @@ class PeerArena:
             self.base = None
 
 
+class PeerInbox:
+    """The receive areas of one fused exchange: on every rank 2 halves x `world` senders x `slots`
+    8-byte packets, plus the epoch counter of the calls made on them."""
+
+    def __init__(self, arena: PeerArena, slots: int):
+        self.arena, self.slots = arena, int(slots)
+        off = arena.alloc(inbox_bytes(arena.world, slots))
+        self.peers = GaloisPeers()
+        self.peers.rank, self.peers.nranks, self.peers.slots = arena.rank, arena.world, self.slots
+        for r in range(arena.world):
+            self.peers.inbox[r] = arena.bases[r] + off
+        self.epoch = 0
+
+    def next_epoch(self) -> int:
+        self.epoch = (self.epoch % 0xFFFFFFFF) + 1  # 1 .. 2^32 - 1, never 0
+        return self.epoch
+
+
+def inbox_bytes(world: int, slots: int) -> int:
+    return 2 * world * int(slots) * 8
+
+
+def band_slots(n_total: int, world: int, batch: int) -> int:
+    """Packets the largest band of an N-row result sends per call."""
+    return batch * max(shard_rows(n_total, world, r)[1] for r in range(world))
+
+
 class PeerShardedMatMul:
     """`W` [N][K] Q4_0 sharded by rows over the ranks of the arena's group; ``forward(x)``
     returns the full ``[B][N]`` f32 result on every rank.  The exchange is part of the mat-mul
-    call (``galois_b200_mul_mat_q4_0_f32_gather``): peer stores over NVLink and a device-side
-    arrival protocol, no collective library call.  Results alternate between two buffers."""
+    call (``galois_b200_mul_mat_q4_0_f32_gather``): packets stored into the peers' inboxes over
+    NVLink by the kernel that computes them and collected by its tail; no collective library
+    call."""
 
     def __init__(self, w_local: Tensor, n_total: int, arena: PeerArena, max_batch: int = 1):
         self.arena = arena
@@ -145,22 +149,21 @@ class PeerShardedMatMul:
             raise GError(f"rank {arena.rank} holds {w_local.dim().shape[1]} rows, expected {self.nr}")
         self.w_local = w_local
         self.max_batch = max_batch
-        self._bufs = [arena.alloc_f32(n_total * max_batch) for _ in range(2)]
-        self._turn = 0
+        self.inbox = PeerInbox(arena, band_slots(n_total, arena.world, max_batch))
+        self._full = {}
 
     def forward(self, x: Tensor) -> Tensor:
         batch = x.dim().shape[1]
         if batch > self.max_batch:
             raise GError(f"batch {batch} > max_batch {self.max_batch}")
-        off, flat = self._bufs[self._turn]
-        self._turn ^= 1
+        if batch not in self._full:
+            self._full[batch] = Tensor.zeros((self.n_total, batch), GGmlType.F32, x.device)
+        full = self._full[batch]
         dev = x.device.gpu
-        full = Tensor(GGmlType.F32, Dim.ggml((self.n_total, batch), GGmlType.F32), flat, x.device)
-        peers = self.arena.peers(off)
-        epoch = self.arena.next_epoch(off)
         wd, xd, dd = self.w_local.dim().c_struct(), x.dim().c_struct(), full.dim().c_struct()
         rc = lib.galois_b200_mul_mat_q4_0_f32_gather(dev.ctx, C.c_void_p(self.w_local.data_ptr()), C.byref(wd), C.c_void_p(x.data_ptr()),
-                                                     C.byref(xd), C.byref(peers), C.byref(dd), self.r0, epoch)
+                                                     C.byref(xd), C.c_void_p(full.data_ptr()), C.byref(dd), self.r0,
+                                                     C.byref(self.inbox.peers), self.inbox.next_epoch())
         _check(dev.ctx, rc, "mul_mat_q4_0_f32_gather")
         return full
 

@@ -238,31 +238,29 @@ int galois_b200_ipc_close(galois_b200_ctx* ctx, void* imported_dev);
 
 #define GALOIS_B200_MAX_RANKS 8
 typedef struct galois_b200_peers {
-    int32_t rank, nranks;               /* this rank, ranks in the group (2..8) */
-    float* dst[GALOIS_B200_MAX_RANKS];  /* dst[p]: rank p's copy of the full [B][N] result, as an
-                                           address valid on THIS device; dst[rank] is local */
-    uint32_t* flags[GALOIS_B200_MAX_RANKS]; /* flags[p]: rank p's arrival words (>= nranks uint32,
-                                           zero before the first call); flags[rank] is local */
+    int32_t rank, nranks; /* this rank, ranks in the group (2..8) */
+    int64_t slots;        /* capacity of one sender's area, in 8-byte packets (>= B * rows of the largest band) */
+    uint64_t* inbox[GALOIS_B200_MAX_RANKS]; /* inbox[p]: rank p's receive area, 2 * nranks * slots packets, zero
+                                               before the first call, as an address valid on THIS device;
+                                               inbox[rank] is local */
 } galois_b200_peers;
 
-/* Sharded MatMul::f_q_f32_f32 with the exchange fused in: computes rows
- * [row0, row0 + wd->ne[1]) of the full result from this rank's band `w_band`,
- * stores them into EVERY rank's result buffer at their final place (plain peer
- * stores over NVLink; no NCCL call, no staging copy), then publishes `epoch` in
- * every peer's arrival word for this rank and waits, on the device and for at
- * most about two seconds, until all peers have published `epoch` here.  When the
- * work enqueued by this call has completed on this rank's stream, dst[rank]
- * holds all N rows.  `dd_full` describes the full result (ne = [N, B], dense
- * rows: nb[1] >= N).  Every rank of the group makes the same sequence of calls
- * with the same `epoch`, which must grow by one from call to call on a given
- * flags array (start at 1).  A result buffer may be the target of call e + 1 only
- * if it was not the target of call e (alternate two buffers): a peer publishes
- * e + 1 only after the kernels that read its copy of the call e result have run.
- * A wait that runs out reports GALOIS_B200_E_TIMEOUT from the next
- * galois_b200_synchronize; the context stays usable. */
+/* Sharded MatMul::f_q_f32_f32 with the exchange fused in (no reference counterpart).  The N rows are
+ * cut into the bands of galois_b200_shard_rows(N, nranks, .); this rank computes its band
+ * [row0, row0 + wd->ne[1]) from `w_band` into `dst_full` and, from the same kernel, stores every
+ * result as an 8-byte packet {f32 bits, epoch} into each peer's inbox over NVLink (plain peer stores;
+ * no NCCL call, no fence, no staging copy).  The tail of the kernel polls this rank's inbox and moves
+ * the peers' packets of this `epoch` into their rows of `dst_full`.  When the work enqueued by this
+ * call has completed on this rank's stream, `dst_full` ([N][B] f32, dense rows: nb[1] >= N; local
+ * memory, not shared) holds all N rows.  Every rank of the group makes the same sequence of calls with
+ * the same shapes and the same `epoch`, which starts at 1 and grows by one per call on a given set of
+ * inboxes (the two halves of an inbox alternate by epoch parity, which is what lets a fast rank run at
+ * most one call ahead of a slow one without overwriting unread packets).  The poll is bounded (about
+ * two seconds); when it runs out the next galois_b200_synchronize returns GALOIS_B200_E_TIMEOUT and
+ * the context stays usable. */
 int galois_b200_mul_mat_q4_0_f32_gather(galois_b200_ctx* ctx, const void* w_band, const galois_dim* wd, const float* x,
-                                        const galois_dim* xd, const galois_b200_peers* peers, const galois_dim* dd_full,
-                                        int64_t row0, uint32_t epoch);
+                                        const galois_dim* xd, float* dst_full, const galois_dim* dd_full, int64_t row0,
+                                        const galois_b200_peers* peers, uint32_t epoch);
 
 #ifdef __cplusplus
 }

@@ -1,8 +1,8 @@
 """The exchange step of the row-sharded mat-mul over peer memory
 (galois_b200_mul_mat_q4_0_f32_gather; the reference has no multi-GPU path).
 
-On one GPU the peers are stand-ins: ordinary buffers on the same device whose arrival words the
-test writes itself, so no kernel ever waits for another kernel.  With two or more GPUs the real
+On one GPU the peers are stand-ins: ordinary buffers on the same device, with the packets a
+peer would have sent written by the test beforehand, so no kernel ever waits for another kernel.  With two or more GPUs the real
 protocol runs as one process per GPU (tests/peer_gather_worker.py)."""
 import ctypes as C
 import os
@@ -22,7 +22,7 @@ def _setup(dev, n, k, b, world, rank, seed):
 
     import galois_b200 as gb
     from galois_b200._lib import GaloisPeers
-    from galois_b200.shard import shard_q4_0_bytes, shard_rows
+    from galois_b200.shard import band_slots, shard_q4_0_bytes, shard_rows
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from peer_gather_worker import random_q4_0
 
@@ -34,85 +34,98 @@ def _setup(dev, n, k, b, world, rank, seed):
     x = gb.Tensor.from_numpy(np.random.default_rng(seed + 1).standard_normal((b, k)).astype(np.float32), gb.GGmlType.F32, G)
     ref = gb.Tensor.zeros((n, b), gb.GGmlType.F32, G)
     gb.galois_matmul(w_full, x, ref)
-    outs = [torch.full((b * n,), -7.0, device=dev.torch_device, dtype=torch.float32) for _ in range(world)]
-    flags = [torch.zeros(64, device=dev.torch_device, dtype=torch.int32) for _ in range(world)]
+    slots = band_slots(n, world, b) + 3
+    inboxes = [torch.zeros(2 * world * slots, device=dev.torch_device, dtype=torch.int64) for _ in range(world)]
     peers = GaloisPeers()
-    peers.rank, peers.nranks = rank, world
+    peers.rank, peers.nranks, peers.slots = rank, world, slots
     for p in range(world):
-        peers.dst[p] = outs[p].data_ptr()
-        peers.flags[p] = flags[p].data_ptr()
+        peers.inbox[p] = inboxes[p].data_ptr()
+    full = torch.full((b * n,), -7.0, device=dev.torch_device, dtype=torch.float32)
     dd = gb.Dim.ggml((n, b), gb.GGmlType.F32).c_struct()
-    return w_band, x, ref, outs, flags, peers, dd, r0, nr
+    return w_band, x, ref, full, inboxes, peers, dd, r0, nr, slots
+
+
+def _packets(values: np.ndarray, epoch: int) -> np.ndarray:
+    """[b][rows] f32 -> int64 packets {f32 bits, epoch} in slot order."""
+    bits = np.ascontiguousarray(values, dtype=np.float32).reshape(-1).view(np.uint32).astype(np.uint64)
+    return ((np.uint64(epoch) << np.uint64(32)) | bits).view(np.int64)
+
+
+def _call(dev, w_band, x, full, dd, r0, peers, epoch):
+    from galois_b200 import lib
+
+    return lib.galois_b200_mul_mat_q4_0_f32_gather(dev.ctx, C.c_void_p(w_band.data_ptr()), C.byref(w_band.dim().c_struct()),
+                                                   C.c_void_p(x.data_ptr()), C.byref(x.dim().c_struct()), C.c_void_p(full.data_ptr()),
+                                                   C.byref(dd), r0, C.byref(peers), epoch)
 
 
 @pytest.mark.parametrize("n,k,b", [(4096, 4096, 1), (11008, 4096, 4), (4096, 11008, 2), (2048, 1024, 8), (4096, 4096, 16), (256, 64, 3)])
-@pytest.mark.parametrize("world,rank", [(2, 1), (4, 2), (8, 0)])
-def test_band_reaches_every_rank(dev, n, k, b, world, rank):
+@pytest.mark.parametrize("world,rank,epoch", [(2, 1, 5), (4, 2, 6), (8, 0, 1)])
+def test_band_goes_out_and_peers_bands_come_in(dev, n, k, b, world, rank, epoch):
     import torch
 
     from galois_b200 import lib
+    from galois_b200.shard import shard_rows
 
-    w_band, x, ref, outs, flags, peers, dd, r0, nr = _setup(dev, n, k, b, world, rank, 31 * n + k + b)
-    epoch = 5
+    w_band, x, ref, full, inboxes, peers, dd, r0, nr, slots = _setup(dev, n, k, b, world, rank, 31 * n + k + b)
+    want = ref.to_numpy()  # [b][n]
+    # the stand-in peers "have sent": their packets of this epoch already sit in the local inbox
+    half = epoch & 1
     for p in range(world):
-        if p != rank:
-            flags[rank][p] = epoch  # the stand-in peers "have arrived"
+        if p == rank:
+            continue
+        p0, pn = shard_rows(n, world, p)
+        pk = torch.from_numpy(_packets(want[:, p0 : p0 + pn], epoch)).to(dev.torch_device)
+        start = (half * world + p) * slots
+        inboxes[rank][start : start + pk.numel()] = pk
     torch.cuda.synchronize()
-    rc = lib.galois_b200_mul_mat_q4_0_f32_gather(dev.ctx, C.c_void_p(w_band.data_ptr()), C.byref(w_band.dim().c_struct()),
-                                                 C.c_void_p(x.data_ptr()), C.byref(x.dim().c_struct()), C.byref(peers), C.byref(dd), r0, epoch)
+    rc = _call(dev, w_band, x, full, dd, r0, peers, epoch)
     assert rc == 0, lib.galois_b200_last_error(dev.ctx)
     dev.synchronize()
-    want = ref.to_numpy()  # [b][n]
+    assert np.array_equal(full.cpu().numpy().reshape(b, n), want), "full result differs"
+    mine = _packets(want[:, r0 : r0 + nr], epoch)
     for p in range(world):
-        got = outs[p].cpu().numpy().reshape(b, n)
-        assert np.array_equal(got[:, r0 : r0 + nr], want[:, r0 : r0 + nr]), f"band differs in rank {p}'s buffer"
-        rest = np.delete(got, np.s_[r0 : r0 + nr], axis=1)
-        assert np.all(rest == -7.0), "rows outside the band were touched"
-        if p != rank:
-            assert int(flags[p][rank].item()) == epoch, "arrival word not published"
-            assert int(flags[p].sum().item()) == epoch, "a foreign arrival word was written"
+        if p == rank:
+            continue
+        got = inboxes[p].cpu().numpy()
+        start = (half * world + rank) * slots
+        assert np.array_equal(got[start : start + mine.size], mine), f"packets in rank {p}'s inbox differ"
+        got[start : start + mine.size] = 0
+        assert not got.any(), "packets outside this rank's area of the inbox"
 
 
 def test_wait_runs_out_and_context_survives(dev):
-    """Nothing sets the peer's arrival word: the bounded device wait gives up, the next
-    synchronize reports the time-out, and the context keeps working."""
+    """Nothing ever fills the inbox: the bounded device wait gives up, the next synchronize
+    reports the time-out, and the context keeps working."""
     import galois_b200 as gb
-    from galois_b200 import lib
 
     n, k, b = 256, 256, 1
-    w_band, x, ref, outs, flags, peers, dd, r0, nr = _setup(dev, n, k, b, 2, 0, 777)
-    rc = lib.galois_b200_mul_mat_q4_0_f32_gather(dev.ctx, C.c_void_p(w_band.data_ptr()), C.byref(w_band.dim().c_struct()),
-                                                 C.c_void_p(x.data_ptr()), C.byref(x.dim().c_struct()), C.byref(peers), C.byref(dd), r0, 1)
-    assert rc == 0
+    w_band, x, ref, full, inboxes, peers, dd, r0, nr, slots = _setup(dev, n, k, b, 2, 0, 777)
+    assert _call(dev, w_band, x, full, dd, r0, peers, 1) == 0
     with pytest.raises(gb.GError) as e:
         dev.synchronize()
     assert e.value.code == -9  # GALOIS_B200_E_TIMEOUT
-    # the band itself was computed and pushed, and later calls are unaffected
+    # this rank's own band was computed all the same, and later calls are unaffected
     want = ref.to_numpy()
-    assert np.array_equal(outs[1].cpu().numpy().reshape(b, n)[:, r0 : r0 + nr], want[:, r0 : r0 + nr])
-    out = gb.Tensor.zeros((n, b), gb.GGmlType.F32, x.device)
-    w_full = w_band  # rank 0 of 2 holds rows [0, n/2)
-    out2 = gb.Tensor.zeros((nr, b), gb.GGmlType.F32, x.device)
-    gb.galois_matmul(w_full, x, out2)
+    assert np.array_equal(full.cpu().numpy().reshape(b, n)[:, r0 : r0 + nr], want[:, r0 : r0 + nr])
+    out = gb.Tensor.zeros((nr, b), gb.GGmlType.F32, x.device)
+    gb.galois_matmul(w_band, x, out)  # rank 0 of 2 holds rows [0, n/2)
     dev.synchronize()
-    assert np.array_equal(out2.to_numpy(), want[:, :nr])
-    del out
+    assert np.array_equal(out.to_numpy(), want[:, :nr])
 
 
 def test_argument_errors(dev):
-    from galois_b200 import lib
-
-    w_band, x, ref, outs, flags, peers, dd, r0, nr = _setup(dev, 256, 256, 1, 2, 0, 3)
-    args = lambda pe, row0, ep: lib.galois_b200_mul_mat_q4_0_f32_gather(  # noqa: E731
-        dev.ctx, C.c_void_p(w_band.data_ptr()), C.byref(w_band.dim().c_struct()), C.c_void_p(x.data_ptr()), C.byref(x.dim().c_struct()),
-        C.byref(pe), C.byref(dd), row0, ep)
-    assert args(peers, r0, 0) == -1  # epoch 0
-    assert args(peers, 200, 1) == -2  # band outside the result
+    w_band, x, ref, full, inboxes, peers, dd, r0, nr, slots = _setup(dev, 256, 256, 1, 2, 0, 3)
+    assert _call(dev, w_band, x, full, dd, r0, peers, 0) == -1  # epoch 0
+    assert _call(dev, w_band, x, full, dd, 32, peers, 1) == -2  # not this rank's band
+    peers.slots = 5
+    assert _call(dev, w_band, x, full, dd, r0, peers, 1) == -2  # inbox too small
+    peers.slots = slots
     peers.nranks = 9
-    assert args(peers, r0, 1) == -1
+    assert _call(dev, w_band, x, full, dd, r0, peers, 1) == -1
     peers.nranks = 2
-    peers.dst[1] = None
-    assert args(peers, r0, 1) == -1
+    peers.inbox[1] = None
+    assert _call(dev, w_band, x, full, dd, r0, peers, 1) == -1
 
 
 def test_two_or_more_gpus_real_exchange():
