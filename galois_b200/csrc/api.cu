@@ -8,6 +8,7 @@
 #include "gemv_q4_0.cuh"
 #include "mul_mat_q4_0.cuh"
 #include "mul_mat_q4_0_tc.cuh"
+#include "mmq_skinny.cuh"
 #include "quantize.cuh"
 
 static char g_init_err[512] = "";
@@ -159,6 +160,7 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
         rc = gb_scratch(ctx, (size_t)16 << 20, &p);
         if (rc == 0) rc = gb_mmv_bulk_init(ctx);
         if (rc == 0) rc = gb_gemv_init(ctx);
+        if (rc == 0) rc = gb_mmq_skinny_init(ctx);
         if (rc == 0) rc = gb_mm_tc_init(ctx);
         if (rc != 0) snprintf(g_init_err, sizeof(g_init_err), "%s", ctx->err);
     }
@@ -201,7 +203,7 @@ extern "C" int64_t galois_b200_launch_count(galois_b200_ctx* ctx) { return ctx ?
 
 extern "C" int galois_b200_set_mul_mat_variant(galois_b200_ctx* ctx, int variant) {
     GB_CHECK_CTX(ctx);
-    if (variant < 0 || variant > 3) return gb_fail(ctx, GALOIS_B200_E_BADARG, "set_mul_mat_variant: %d not in 0..3", variant);
+    if (variant < 0 || variant > 4) return gb_fail(ctx, GALOIS_B200_E_BADARG, "set_mul_mat_variant: %d not in 0..4", variant);
     ctx->variant = variant;
     return 0;
 }
@@ -296,8 +298,16 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
     const bool tc_ok = gb_mm_tc_supported(ctx, w, wd, x, xd, dd);
     const bool gemv_ok = gb_gemv_supported(ctx, w, wd, x, xd, dd);
     const bool bulk_ok = gb_mmv_bulk_supported(ctx, w, wd, xd, dd);
+    const bool skinny_ok = gb_mmq_skinny_supported(ctx, w, wd, x, xd, dd);
     int variant = ctx->variant;
-    if (variant == 0) variant = (tc_ok && xd->ne[1] >= GB_TC_MIN_BATCH) ? 3 : ((gemv_ok || bulk_ok) ? 2 : 1);
+    if (variant == 0) {
+        // one activation row: dp4a GEMV; 2..96 rows: mma.sync skinny kernel; more: tcgen05 GEMM
+        if (gemv_ok && xd->ne[1] < GB_SKINNY_MIN_BATCH) variant = 2;
+        else if (skinny_ok) variant = 4;
+        else if (tc_ok && xd->ne[1] >= GB_TC_MIN_BATCH) variant = 3;
+        else variant = (gemv_ok || bulk_ok) ? 2 : 1;
+    }
+    if (variant == 4 && !skinny_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: skinny variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned operands, batch <= 96");
     if (variant == 2 && !(gemv_ok || bulk_ok)) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: streaming variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned base, batch <= 8");
     if (variant == 3 && !tc_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: tensor-core variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned operands");
 
@@ -306,6 +316,9 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
     void* scratch = nullptr;
     if (variant == 3) {
         rc = gb_scratch(ctx, gb_mm_tc_scratch_bytes(wd, xd), &scratch);
+        if (rc) return rc;
+    } else if (variant == 4) {
+        rc = gb_scratch(ctx, gb_mmq_skinny_scratch_bytes(wd, xd), &scratch);
         if (rc) return rc;
     } else if (!gemv) {
         rc = gb_scratch(ctx, gb_q8_soa_bytes(K, nrows), &scratch);
@@ -317,6 +330,8 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
     if (prof) GB_CUDA(ctx, cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream));
     if (variant == 3)
         rc = gb_mm_q4_0_tc(ctx, w, wd, x, xd, dst, dd, scratch);
+    else if (variant == 4)
+        rc = gb_mmq_skinny(ctx, w, wd, x, xd, dst, dd, scratch);
     else if (gemv)
         rc = gb_gemv_q4_0(ctx, w, wd, x, xd, dst, dd);
     else if (variant == 2)

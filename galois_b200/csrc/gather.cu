@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "gather.cuh"
 #include "gemv_q4_0.cuh"
+#include "mmq_skinny.cuh"
 
 namespace {
 
@@ -132,7 +133,8 @@ extern "C" int galois_b200_mul_mat_q4_0_f32_gather(galois_b200_ctx* ctx, const v
         float* local = dst_full + row0;
         rc = gb_validate_mul_mat(ctx, w_band, wd, x, xd, local, &band);
         if (rc != 0) return rc;
-        if (ctx->variant == 0 && wd->ne[0] > 0 && gb_gemv_supported(ctx, w_band, wd, x, xd, &band))
+        // the same kernel choice as the unsharded entry point, so that sharded and unsharded results agree bit for bit
+        if (ctx->variant == 0 && wd->ne[0] > 0 && xd->ne[1] < GB_SKINNY_MIN_BATCH && gb_gemv_supported(ctx, w_band, wd, x, xd, &band))
             return gb_gemv_q4_0_gather(ctx, w_band, wd, x, xd, local, &band, &args);  // one kernel in all
         rc = galois_b200_mul_mat_q4_0_f32(ctx, w_band, wd, x, xd, local, &band);
         if (rc != 0) return rc;

@@ -1,0 +1,316 @@
+// Skinny Q4_0 x Q8_0 mat-mul for 2..16 activation rows: the weights stream once from HBM and the
+// per-block integer dot products run on the warp-level int8 tensor-core instruction
+// (mma.sync m16n8k32, u8 x s8 -> s32), 16 weight rows x 8 activation rows x one 32-element block
+// per instruction.  The mat-mul stays HBM-bound work; the MMA only replaces the dp4a sequence
+// whose shared-memory reads of the activations grow with the batch.
+//
+//   * A operand = weights.  The nibbles of a block are used as unsigned values 0..15 (low nibbles
+//     are k = 0..15, high nibbles k = 16..31, exactly the fragment split of the instruction), so
+//     unpacking a fragment is one AND and one shift+AND; the "- 8" of Q4_0 is folded into a
+//     per-(activation row, block) term -8 * sum(q8), precomputed by the quantiser.
+//   * B operand = Q8_0 activations, written by the quantiser in fragment order (one coalesced
+//     8-byte load per lane per block), read through L1.
+//   * the 18-byte blocks travel HBM -> shared memory in per-warp rings of 1-D bulk copies
+//     (cp.async.bulk, one copy per weight row and stage, completing on an mbarrier; no multicast);
+//     a row segment sits at a 304-byte pitch so that the 32 fragment loads of a warp hit 32 banks.
+//   * scales: acc += (d_w * d_x) * float(isum) per block, in f32, as in BlockQ4_0::vec_dot_q8_0
+//     (src/ggml_quants.rs:156-172 of galois); only the order of the additions differs.
+//   * programmatic dependent launch: weight prefetch starts before the quantiser in front of
+//     this kernel has finished.
+//
+// Quantisation is bit-exact with <BlockQ8_0 as QuantType>::from_f32 (src/ggml_quants.rs:736-764).
+#include "common.cuh"
+#include "mmq_skinny.cuh"
+#include "ptx.cuh"
+
+namespace {
+
+#ifndef GB_SK_KC
+#define GB_SK_KC 16
+#endif
+constexpr int SK_WARPS = 8;
+constexpr int SK_THREADS = SK_WARPS * 32;
+constexpr int SK_ROWS = 16;                        // weight rows per CTA tile (the M of the MMA)
+constexpr int SK_KC = GB_SK_KC;                    // blocks per row and stage (8 or 16)
+// row pitch in a stage: an odd multiple of 16 bytes, so the 32 fragment loads of a warp hit 32 banks
+constexpr int SK_PITCH = SK_KC == 8 ? 144 : 304;
+constexpr int SK_STAGE_BYTES = SK_ROWS * SK_PITCH;
+constexpr int SK_MAX_STAGES = 8;
+constexpr int SK_BAR_BYTES = SK_WARPS * SK_MAX_STAGES * 8;  // 512
+constexpr int SK_MAGIC_INT = 0x4B400000;           // bits of 12582912.0f = 1.5 * 2^23
+constexpr float SK_MAGIC = 12582912.0f;
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// Q8_0 quantiser into MMA fragment order.  Eight threads own one (activation row, block).
+//   qfrag: [nblk][NT][32 lanes][2] u32 -- lane (g = lane / 4, t = lane % 4) of n-tile nt holds
+//          word j = quants k = 16 j + 4 t .. + 3 of activation row 8 nt + g;
+//   ds   : [nblk][8 NT] {d, bits(MAGIC_INT - 8 * sum q)} per activation row.
+// Rows >= nbatch (padding up to 8 NT) are written as zeros.
+__global__ void __launch_bounds__(256) quantize_q8_frag_kernel(const float* __restrict__ x, long long x_stride, int K, int nbatch, int NT,
+                                                               uint32_t* __restrict__ qfrag, float2* __restrict__ ds) {
+    gb_pdl_entry();
+    const int nblk = K >> 5;
+    const int bpad = 8 * NT;
+    const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;  // (blk, b), b fastest
+    const int sub = threadIdx.x & 7;
+    if (item >= (long long)nblk * bpad) return;  // whole groups of eight leave together
+    const int blk = (int)(item / bpad), b = (int)(item - (long long)blk * bpad);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (b < nbatch) v = __ldg(reinterpret_cast<const float4*>(x + (long long)b * x_stride + blk * 32) + sub);
+    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+    // `as i8` in Rust saturates and maps NaN to 0; so does (int) followed by the clamp
+    const int q0 = max(-128, min(127, (int)roundf(__fmul_rn(v.x, id))));
+    const int q1 = max(-128, min(127, (int)roundf(__fmul_rn(v.y, id))));
+    const int q2 = max(-128, min(127, (int)roundf(__fmul_rn(v.z, id))));
+    const int q3 = max(-128, min(127, (int)roundf(__fmul_rn(v.w, id))));
+    int s = q0 + q1 + q2 + q3;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const uint32_t packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+    const int nt = b >> 3, g = b & 7, t = sub & 3, j = sub >> 2;
+    qfrag[(((long long)blk * NT + nt) * 32 + g * 4 + t) * 2 + j] = packed;
+    if (sub == 0) {
+        const float dr = __half2float(__float2half_rn(d));  // the f16 scale the Q8_0 block stores
+        ds[(long long)blk * bpad + b] = make_float2(dr, __int_as_float(SK_MAGIC_INT - 8 * s));
+    }
+}
+
+// One block of 16 weight rows (fragment words qa for row g, qb for row g + 8; scales dwa, dwb)
+// against NT n-tiles of activations.
+template <int NT>
+__device__ __forceinline__ void block_mma(uint32_t qa, uint32_t qb, float dwa, float dwb, const uint2* __restrict__ qfrag,
+                                          const float4* __restrict__ ds4, int blk, int lane, float (&acc)[NT][4]) {
+    const uint32_t a0 = qa & 0x0F0F0F0Fu, a2 = (qa >> 4) & 0x0F0F0F0Fu;
+    const uint32_t a1 = qb & 0x0F0F0F0Fu, a3 = (qb >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        const uint2 bf = __ldg(qfrag + ((long long)blk * NT + nt) * 32 + lane);
+        const float4 s = __ldg(ds4 + ((long long)blk * NT + nt) * 4 + (lane & 3));  // {d, m} of rows 2t, 2t + 1
+        int c[4];
+        mma_u8s8(c, a0, a1, a2, a3, bf.x, bf.y);
+        // float(isum) = float(c - 8 * sum q) through the 1.5 * 2^23 trick: exact for |isum| < 2^22
+        const float f0 = __int_as_float(c[0] + __float_as_int(s.y)) - SK_MAGIC;
+        const float f1 = __int_as_float(c[1] + __float_as_int(s.w)) - SK_MAGIC;
+        const float f2 = __int_as_float(c[2] + __float_as_int(s.y)) - SK_MAGIC;
+        const float f3 = __int_as_float(c[3] + __float_as_int(s.w)) - SK_MAGIC;
+        acc[nt][0] = fmaf(dwa * s.x, f0, acc[nt][0]);
+        acc[nt][1] = fmaf(dwa * s.z, f1, acc[nt][1]);
+        acc[nt][2] = fmaf(dwb * s.x, f2, acc[nt][2]);
+        acc[nt][3] = fmaf(dwb * s.z, f3, acc[nt][3]);
+    }
+}
+
+// NP block pairs of one stage: rows g and g + 8 of the tile (ra, rb) against the activations of
+// blocks blk0 .. blk0 + 2 NP - 1.  Fully unrolled so that the loads of later pairs overlap the
+// MMAs and scale arithmetic of earlier ones.
+template <int NT, int NP>
+__device__ __forceinline__ void stage_mma(const uint8_t* ra, const uint8_t* rb, const uint2* __restrict__ qfrag,
+                                          const float4* __restrict__ ds4, int blk0, int lane, float (&acc)[NT][4]) {
+    const int t = lane & 3;
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+        // a block pair is nine aligned words: {d0 | qs0[0:2]}, qs0[2:14], {qs0[14:16] | d1}, qs1[0:16]
+        const uint32_t* ta = reinterpret_cast<const uint32_t*>(ra + p * 36);
+        const uint32_t* tb = reinterpret_cast<const uint32_t*>(rb + p * 36);
+        const uint32_t a_lo = ta[t], a_hi = ta[t + 1], a_1 = ta[5 + t];
+        const uint32_t b_lo = tb[t], b_hi = tb[t + 1], b_1 = tb[5 + t];
+        const float dwa0 = __half2float(*reinterpret_cast<const __half*>(ra + p * 36));
+        const float dwa1 = __half2float(*reinterpret_cast<const __half*>(ra + p * 36 + 18));
+        const float dwb0 = __half2float(*reinterpret_cast<const __half*>(rb + p * 36));
+        const float dwb1 = __half2float(*reinterpret_cast<const __half*>(rb + p * 36 + 18));
+        block_mma<NT>(__funnelshift_r(a_lo, a_hi, 16), __funnelshift_r(b_lo, b_hi, 16), dwa0, dwb0, qfrag, ds4, blk0 + 2 * p, lane, acc);
+        block_mma<NT>(a_1, b_1, dwa1, dwb1, qfrag, ds4, blk0 + 2 * p + 1, lane, acc);
+    }
+}
+
+// Shared memory: [0, 512) mbarriers | two reduction buffers | SK_WARPS rings of `stages` stages of
+// 16 rows x SK_PITCH bytes.
+// A CTA owns tiles of 16 consecutive weight rows, dealt round-robin over the grid.  The K dimension
+// of a tile is walked in steps of SK_KC blocks; step s belongs to warp s % SK_WARPS, so the eight
+// warps of the CTA work on one tile at the same time and their partial sums meet in shared memory.
+// A warp's (tile, step) pairs form one sequence that its ring runs through without draining
+// between tiles.
+template <int NT>
+__global__ void __launch_bounds__(SK_THREADS) mmq_skinny_kernel(const uint8_t* __restrict__ w, const uint2* __restrict__ qfrag,
+                                                                const float4* __restrict__ ds4, float* __restrict__ dst, long long nb1,
+                                                                int K, int N, int nbatch, int stages, int* __restrict__ status) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2;
+    const int nblk = K >> 5;
+    const int nsteps = (nblk + SK_KC - 1) / SK_KC;
+    const long long row_bytes = (long long)nblk * GB_Q4_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem) + warp * SK_MAX_STAGES;
+    float* red = reinterpret_cast<float*>(smem + SK_BAR_BYTES);  // [2][SK_WARPS][NT * 128]
+    constexpr int RED_FLOATS = SK_WARPS * NT * 128;
+    uint8_t* ring = smem + SK_BAR_BYTES + 2 * RED_FLOATS * sizeof(float) + (size_t)warp * stages * SK_STAGE_BYTES;
+
+    const int ntiles = (N + SK_ROWS - 1) / SK_ROWS;
+    const int my_tiles = (int)blockIdx.x < ntiles ? (ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int my_steps = warp < nsteps ? (nsteps - warp + SK_WARPS - 1) / SK_WARPS : 0;  // steps of a tile this warp owns
+    const int total = my_tiles * my_steps;
+
+    auto issue = [&](int idx, int s) {
+        const int j = idx / my_steps;
+        const int tile = (int)blockIdx.x + j * (int)gridDim.x, step = warp + (idx - j * my_steps) * SK_WARPS;
+        const int blocks = min(SK_KC, nblk - step * SK_KC);
+        const int rows = min(SK_ROWS, N - tile * SK_ROWS);
+        const uint32_t bytes = (uint32_t)blocks * GB_Q4_BYTES;
+        if (lane == 0) mbar_expect_tx(&bars[s], bytes * rows);
+        __syncwarp();
+        if (lane < rows)
+            bulk_g2s(ring + (size_t)s * SK_STAGE_BYTES + lane * SK_PITCH,
+                     w + ((long long)tile * SK_ROWS + lane) * row_bytes + (long long)step * (SK_KC * GB_Q4_BYTES), bytes, &bars[s]);
+    };
+
+    if (lane == 0) {
+        for (int s = 0; s < stages; s++) mbar_init(&bars[s], 1);
+        fence_proxy_async();
+    }
+    __syncwarp();
+    // weights are not produced by the kernel in front of this one: prefetch before the dependency wait
+    for (int s = 0; s < stages && s < total; s++) issue(s, s);
+    pdl_wait();  // the quantised activations come from the preceding launch
+
+    bool ok = true;
+    int idx = 0;
+    for (int j = 0; j < my_tiles; j++) {
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
+
+        for (int q = 0; q < my_steps && ok; q++, idx++) {
+            const int s = idx % stages;
+            ok = mbar_wait_bounded(&bars[s], (uint32_t)(idx / stages) & 1u);
+            if (!ok) break;
+            const int step = warp + q * SK_WARPS;
+            const int blocks = min(SK_KC, nblk - step * SK_KC);
+            const uint8_t* ra = ring + (size_t)s * SK_STAGE_BYTES + g * SK_PITCH;
+            const uint8_t* rb = ra + 8 * SK_PITCH;
+            if (blocks == SK_KC)
+                stage_mma<NT, SK_KC / 2>(ra, rb, qfrag, ds4, step * SK_KC, lane, acc);
+            else  // K % 256 == 0: the ragged last step of a row is a whole number of 8 blocks
+                for (int p8 = 0; p8 < blocks / 8; p8++) stage_mma<NT, 4>(ra + p8 * 144, rb + p8 * 144, qfrag, ds4, step * SK_KC + 8 * p8, lane, acc);
+            __syncwarp();  // every lane has consumed the stage: refill it
+            if (idx + stages < total) issue(idx + stages, s);
+        }
+
+        // partial sums of the eight warps meet here; buffers alternate so one barrier per tile is enough
+        float* mine = red + (j & 1) * RED_FLOATS + warp * (NT * 128);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) mine[(nt * 4 + i) * 32 + lane] = acc[nt][i];
+        __syncthreads();
+        const int tile = (int)blockIdx.x + j * (int)gridDim.x;
+        for (int o = threadIdx.x; o < NT * 128; o += SK_THREADS) {
+            // output o = (activation row b, row r of the tile), r fastest; lane (g, t) held rows g, g + 8
+            // for activation rows 8 nt + 2 t and + 1 as acc[nt][2 * (r / 8) + (b & 1)]
+            const int b = o >> 4, r = o & 15;
+            const int nt = b >> 3, tt = (b & 7) >> 1, src_lane = (r & 7) * 4 + tt, i = 2 * (r >> 3) + (b & 1);
+            const float* col = red + (j & 1) * RED_FLOATS + (nt * 4 + i) * 32 + src_lane;
+            float v = 0.0f;
+#pragma unroll
+            for (int ww = 0; ww < SK_WARPS; ww++) v += col[ww * (NT * 128)];
+            const int row = tile * SK_ROWS + r;
+            if (b < nbatch && row < N) dst[b * nb1 + row] = v;
+        }
+    }
+    if (!ok && lane == 0) atomicExch(status, GALOIS_B200_E_TIMEOUT);
+}
+
+struct skinny_plan {
+    int nt, stages, grid;
+    size_t smem;
+};
+
+skinny_plan plan_skinny(const galois_b200_ctx* ctx, int64_t N, int64_t B) {
+    skinny_plan p;
+    p.nt = B <= 8 ? 1 : 2;
+    const size_t fixed = SK_BAR_BYTES + 2 * (size_t)SK_WARPS * p.nt * 128 * sizeof(float);
+    // two CTAs of one launch per SM and room in L1 for the activation fragments
+    const size_t budget = (size_t)(ctx->tune_smem_kb > 0 ? ctx->tune_smem_kb : 88) * 1024;
+    int stages = (int)((budget - fixed) / ((size_t)SK_WARPS * SK_STAGE_BYTES));
+    if (stages > SK_MAX_STAGES) stages = SK_MAX_STAGES;
+    if (stages < 2) stages = 2;
+    if (ctx->tune_stages >= 2 && ctx->tune_stages <= SK_MAX_STAGES) stages = ctx->tune_stages;
+    p.stages = stages;
+    p.smem = fixed + (size_t)SK_WARPS * stages * SK_STAGE_BYTES;
+    const int64_t ntiles = (N + SK_ROWS - 1) / SK_ROWS;
+    const int cps = ctx->tune_ctas_per_sm > 0 ? ctx->tune_ctas_per_sm : 2;
+    int64_t grid = (int64_t)ctx->sm_count * cps;
+    if (grid > ntiles) grid = ntiles;
+    p.grid = (int)(grid < 1 ? 1 : grid);
+    return p;
+}
+
+}  // namespace
+
+int gb_mmq_skinny_init(galois_b200_ctx* ctx) {
+    GB_CUDA(ctx, cudaFuncSetAttribute(mmq_skinny_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    GB_CUDA(ctx, cudaFuncSetAttribute(mmq_skinny_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    return 0;
+}
+
+bool gb_mmq_skinny_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
+                             const galois_dim* dd) {
+    (void)ctx;
+    const int64_t K = wd->ne[0], N = wd->ne[1];
+    if (K % 256 != 0 || K > (1 << 20) || N < 1 || N > (1 << 30)) return false;  // rows are whole multiples of 144 bytes
+    if ((uintptr_t)w % 16 != 0) return false;  // bulk copies start on 16-byte boundaries
+    if (wd->ne[2] != 1 || wd->ne[3] != 1 || xd->ne[2] != 1 || xd->ne[3] != 1) return false;
+    if (wd->nb[1] != K / GB_QK) return false;
+    if (xd->ne[1] < 1 || xd->ne[1] > GB_SKINNY_MAX_BATCH) return false;
+    if ((uintptr_t)x % 16 != 0 || xd->nb[1] % 4 != 0) return false;  // float4 loads in the quantiser
+    (void)dd;
+    return true;
+}
+
+// scratch of one pass of up to 16 activation rows: fragments, then {d, m} pairs
+static size_t pass_scratch_bytes(size_t nblk) { return ((nblk * 2 * 256 + 255) & ~(size_t)255) + nblk * 2 * 64 + 256; }
+
+size_t gb_mmq_skinny_scratch_bytes(const galois_dim* wd, const galois_dim* xd) {
+    const size_t passes = (size_t)((xd->ne[1] + 15) / 16);
+    return passes * pass_scratch_bytes((size_t)(wd->ne[0] / GB_QK));
+}
+
+int gb_mmq_skinny(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
+                  const galois_dim* dd, void* scratch) {
+    const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
+    const int nblk = K / GB_QK;
+    const uint8_t* wb = (const uint8_t*)w;
+    // more than 16 activation rows: one pass over the weights per 16 rows (the weights of the
+    // shapes this path takes stay in L2 between passes)
+    for (int b0 = 0; b0 < B; b0 += 16) {
+        const int bc = B - b0 < 16 ? B - b0 : 16;
+        const skinny_plan p = plan_skinny(ctx, N, bc);
+        uint8_t* base = reinterpret_cast<uint8_t*>(scratch) + (size_t)(b0 / 16) * pass_scratch_bytes((size_t)nblk);
+        uint32_t* qfrag = reinterpret_cast<uint32_t*>(base);
+        float2* ds = reinterpret_cast<float2*>(base + (((size_t)nblk * p.nt * 256 + 255) & ~(size_t)255));
+        const float* xp = x + (long long)b0 * xd->nb[1];
+        float* dp = dst + (long long)b0 * dd->nb[1];
+        const long long items = (long long)nblk * 8 * p.nt * 8;  // eight threads per (block, padded activation row)
+        gb_launch(ctx, quantize_q8_frag_kernel, dim3((unsigned)((items + 255) / 256)), dim3(256), 0, xp, (long long)xd->nb[1], K, bc, p.nt, qfrag, ds);
+        GB_LAUNCHED(ctx, "quantize_q8_frag");
+        if (p.nt == 1)
+            gb_launch(ctx, mmq_skinny_kernel<1>, dim3((unsigned)p.grid), dim3(SK_THREADS), p.smem, wb, reinterpret_cast<const uint2*>(qfrag),
+                      reinterpret_cast<const float4*>(ds), dp, (long long)dd->nb[1], K, N, bc, p.stages, ctx->dev_status);
+        else
+            gb_launch(ctx, mmq_skinny_kernel<2>, dim3((unsigned)p.grid), dim3(SK_THREADS), p.smem, wb, reinterpret_cast<const uint2*>(qfrag),
+                      reinterpret_cast<const float4*>(ds), dp, (long long)dd->nb[1], K, N, bc, p.stages, ctx->dev_status);
+        GB_LAUNCHED(ctx, "mmq_skinny");
+    }
+    return 0;
+}

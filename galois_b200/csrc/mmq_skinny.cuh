@@ -1,0 +1,20 @@
+// Internal interface of the skinny (2..96 activation rows) Q4_0 mat-mul on mma.sync (mmq_skinny.cu).
+#pragma once
+#include "common.cuh"
+
+// 16 activation rows per pass over the weights; up to 6 passes before the tcgen05 GEMM takes over.
+constexpr int GB_SKINNY_MAX_BATCH = 96;
+// The automatic choice uses this kernel from this many activation rows on (below it: the dp4a GEMV).
+constexpr int GB_SKINNY_MIN_BATCH = 2;
+
+// Sets the shared-memory limit of the kernel instances on the current device.
+int gb_mmq_skinny_init(galois_b200_ctx* ctx);
+// True for 2-D contiguous weights with K % 256 == 0 and a 16-byte aligned base, batch <= 96,
+// 16-byte aligned f32 activations.
+bool gb_mmq_skinny_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
+                             const galois_dim* dd);
+// Bytes of scratch the two launches share (the quantised activations in fragment order).
+size_t gb_mmq_skinny_scratch_bytes(const galois_dim* wd, const galois_dim* xd);
+// Two launches per 16 activation rows: the fragment-order Q8_0 quantiser, then the mat-mul.
+int gb_mmq_skinny(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
+                  const galois_dim* dd, void* scratch);
