@@ -372,6 +372,35 @@ def run_ours(args):
         e2e = {"value": bytes_step / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
                "h2d_bytes_per_step": nsets * sum(B * k * 4 for _, n, k in shapes),
                "d2h_bytes_per_step": nsets * sum(B * n * 4 for _, n, k in shapes), "ms_per_step": e2e_ms}
+    elif peer_exchange:
+        # N > 1: per mat-mul, activations from pinned host memory -> device, the sharded mat-mul with its fused
+        # exchange, the full [B][N] result back to pinned host memory, stream synchronised (as the host entry does)
+        xh = {k: torch.randn(B, k, dtype=torch.float32).pin_memory() for k in (HIDDEN, FFN)}
+        oh = {name: torch.zeros(B, n, dtype=torch.float32).pin_memory() for name, n, k in shapes}
+
+        def e2e_step():
+            for ws in weights:
+                for (name, n, k), (wbuf, wdim) in zip(shapes, ws):
+                    xs[k].copy_(xh[k], non_blocking=True)
+                    mul_mat_gather(wbuf, wdim, k, name)
+                    oh[name].copy_(fulls[name], non_blocking=True)
+                    stream.synchronize()
+
+        for _ in range(3):
+            e2e_step()
+        sync_all()
+        e0.record(stream)
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record(stream)
+        sync_all()
+        t = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item()) / args.steps
+        e2e = {"value": bytes_step / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+               "h2d_bytes_per_step": nsets * sum(B * k * 4 for _, n, k in shapes),
+               "d2h_bytes_per_step": nsets * sum(B * n * 4 for _, n, k in shapes), "ms_per_step": e2e_ms,
+               "note": "bytes per rank; every rank uploads the activations and reads back the full result"}
     sampler.stop()
 
     # ---- other BASELINE configs measured beside the headline (N = 1 only; reported under "extra")
@@ -462,6 +491,8 @@ def run_ours(args):
             extra[f"config2_batch{bb}"] = {"us_gate_up": us_g, "us_down": us_d, "hbm_gbs": 3 * ab / (2 * us_g + us_d) / 1e3}
         us_h = time_mm(32000, 4096, 16, 8)
         extra["config5_head_batch16"] = {"us": us_h, "hbm_gbs": algorithmic_bytes(32000, 4096, 16) / us_h / 1e3}
+        us_f = time_mm(28672, 8192, 16, 4)
+        extra["config5_ffn70b_batch16"] = {"us": us_f, "hbm_gbs": algorithmic_bytes(28672, 8192, 16) / us_f / 1e3}
 
     # ---- CPU baseline (rank 0, N = 1): the oracle's restatement of the reference CPU path, 4 tasks
     cpu = None
