@@ -410,47 +410,51 @@ def run_ours(args):
         # config 4: one decode step of a LLaMA-7B-shaped layer built from galois ops, 4 distinct layers in rotation
         from galois_b200.decode import DecodeLayer, LayerShape, weight_shapes
         shp = LayerShape()
-        layers = []
-        for li in range(4):
-            wq4 = {name: make_q4_0(n, k, 31000 + 100 * li + i, device).cpu().numpy()
-                   for i, (name, (n, k)) in enumerate(weight_shapes(shp).items())}
-            gk = torch.Generator(device=device)
-            gk.manual_seed(32000 + li)
-            kc = torch.randn(shp.heads, shp.ctx, shp.head_dim, generator=gk, device=device).to(torch.float16).cpu().numpy()
-            vc = torch.randn(shp.heads, shp.head_dim, shp.ctx, generator=gk, device=device).to(torch.float16).cpu().numpy()
-            layers.append(DecodeLayer(dev, shp, wq4, np.ones(shp.hidden, np.float32), np.ones(shp.hidden, np.float32), kc, vc))
-        G = gb.Device.Gpu(dev)
-        xin = gb.Tensor.from_numpy(xs[HIDDEN][:1].cpu().numpy(), gb.GGmlType.F32, G)
-        post = gb.Tensor.from_numpy(np.array([shp.ctx - 1], np.int32), gb.GGmlType.I32, G)
+        def measure_layer(fused_layer):
+            layers = []
+            for li in range(4):
+                wq4 = {name: make_q4_0(n, k, 31000 + 100 * li + i, device).cpu().numpy()
+                       for i, (name, (n, k)) in enumerate(weight_shapes(shp).items())}
+                gk = torch.Generator(device=device)
+                gk.manual_seed(32000 + li)
+                kc = torch.randn(shp.heads, shp.ctx, shp.head_dim, generator=gk, device=device).to(torch.float16).cpu().numpy()
+                vc = torch.randn(shp.heads, shp.head_dim, shp.ctx, generator=gk, device=device).to(torch.float16).cpu().numpy()
+                layers.append(DecodeLayer(dev, shp, wq4, np.ones(shp.hidden, np.float32), np.ones(shp.hidden, np.float32), kc, vc,
+                                          fused=fused_layer))
+            G = gb.Device.Gpu(dev)
+            xin = gb.Tensor.from_numpy(xs[HIDDEN][:1].cpu().numpy(), gb.GGmlType.F32, G)
+            post = gb.Tensor.from_numpy(np.array([shp.ctx - 1], np.int32), gb.GGmlType.I32, G)
 
-        def layer_pass():
-            for L in layers:
-                L.step(xin, post, shp.ctx - 1)
+            def layer_pass():
+                for L in layers:
+                    L.step(xin, post, shp.ctx - 1)
 
-        for _ in range(3):
-            layer_pass()
-        torch.cuda.synchronize()
-        l0 = dev.launch_count()
-        lg = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(lg, stream=stream):
-            layer_pass()
-        layer_launches = (dev.launch_count() - l0) // len(layers)
-        for _ in range(3):
-            lg.replay()
-        torch.cuda.synchronize()
-        reps = max(10, args.steps // 4)
-        e0.record(stream)
-        for _ in range(reps):
-            lg.replay()
-        e1.record(stream)
-        torch.cuda.synchronize()
-        us_layer = e0.elapsed_time(e1) * 1e3 / (reps * len(layers))
-        lbytes = layers[0].algorithmic_bytes()
-        extra["decode_layer"] = {"config": "config4: hidden 4096, 32 heads x 128, FFN 11008, f16 KV cache 2048, batch 1, position 2047",
-                                 "layer_steps_per_s": 1e6 / us_layer, "us_per_layer": us_layer, "kernels_per_layer": layer_launches,
-                                 "algorithmic_bytes": lbytes, "hbm_gbs": lbytes / us_layer / 1e3,
-                                 "frac_of_measured_hbm": lbytes / us_layer / 1e3 / peak}
-        del layers, lg
+            for _ in range(3):
+                layer_pass()
+            torch.cuda.synchronize()
+            l0 = dev.launch_count()
+            lg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(lg, stream=stream):
+                layer_pass()
+            layer_launches = (dev.launch_count() - l0) // len(layers)
+            for _ in range(3):
+                lg.replay()
+            torch.cuda.synchronize()
+            reps = max(10, args.steps // 4)
+            e0.record(stream)
+            for _ in range(reps):
+                lg.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            us_layer = e0.elapsed_time(e1) * 1e3 / (reps * len(layers))
+            lbytes = layers[0].algorithmic_bytes()
+            return {"config": "config4: hidden 4096, 32 heads x 128, FFN 11008, f16 KV cache 2048, batch 1, position 2047",
+                                     "layer_steps_per_s": 1e6 / us_layer, "us_per_layer": us_layer, "kernels_per_layer": layer_launches,
+                                     "algorithmic_bytes": lbytes, "hbm_gbs": lbytes / us_layer / 1e3,
+                                     "frac_of_measured_hbm": lbytes / us_layer / 1e3 / peak}
+
+        extra["decode_layer"] = measure_layer(False)       # the op-by-op sequence a galois caller writes
+        extra["decode_layer_fused"] = measure_layer(True)  # stacked QKV / gate-up weights + two-op fusions, same numbers
         # config 3: prefill 4096 x 4096 x 512 tokens on the tcgen05 int8 path; config 2 at batch 4 and 8
         def time_mm(n, k, b, copies):
             ws = [make_q4_0(n, k, 33000 + c, device) for c in range(copies)]

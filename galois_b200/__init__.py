@@ -13,8 +13,10 @@ from .op import (  # noqa: F401
     galois_matmul,
     galois_mul,
     galois_rms_norm,
+    galois_rms_norm_mul,
     galois_rope_custom,
     galois_scale,
+    galois_silu_mul,
     galois_soft_max,
     galois_soft_max_ext,
     galois_unary,

@@ -55,6 +55,8 @@ SIGNATURES = {
     "galois_b200_mul_mat_q4_0_f32_static": ([_P, _P, _DP, _P, _DP, _P, _DP, C.c_char_p, _SZ], _I),
     "galois_b200_mul_mat_f16_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_rms_norm_f32": ([_P, _P, _DP, _P, _DP, _F], _I),
+    "galois_b200_rms_norm_mul_f32": ([_P, _P, _DP, _P, _DP, _P, _DP, _F], _I),
+    "galois_b200_silu_mul_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_rope_f32": ([_P, _P, _DP, _P, _DP, _P, _DP, _I, _I, _I, _F, _F, _F, _I], _I),
     "galois_b200_soft_max_f32": ([_P, _P, _DP, _P, _DP], _I),
     "galois_b200_soft_max_ext_f32": ([_P, _P, _DP, _P, _DP, _F, _P], _I),

@@ -40,8 +40,13 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // ---------------------------------------------------------------- rms_norm
 // f32::rms_norm (src/lib.rs:594-604): sum of squares over the first K & !31
 // elements only, mean = sum / K, scale = 1 / sqrt(mean + eps), y = x * scale.
+// With a gain tensor `w` (Mul::f broadcast: row (i1 % we1, i2 % we2, i3 % we3)) the product of the
+// two ops is formed in the same launch, y = (x * scale) * w, both multiplies rounded separately as
+// the two-op sequence rounds them.
 __global__ void rms_norm_kernel(const float* __restrict__ x, int64_t xb1, int64_t xb2, int64_t xb3, float* __restrict__ y,
-                                int64_t yb1, int64_t yb2, int64_t yb3, int64_t K, int64_t ne1, int64_t ne2, float eps) {
+                                int64_t yb1, int64_t yb2, int64_t yb3, int64_t K, int64_t ne1, int64_t ne2, float eps,
+                                const float* __restrict__ w, int64_t wb1, int64_t wb2, int64_t wb3, int64_t we1, int64_t we2,
+                                int64_t we3) {
     gb_pdl_entry();
     __shared__ float red[33];
     const int64_t r = blockIdx.x;
@@ -57,7 +62,12 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, int64_t xb1, int64_
     s = block_sum(s, red);
     const float mean = __fdiv_rn(s, (float)K);
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
-    for (int64_t i = threadIdx.x; i < K; i += blockDim.x) yr[i] = __fmul_rn(xr[i], scale);
+    if (w == nullptr) {
+        for (int64_t i = threadIdx.x; i < K; i += blockDim.x) yr[i] = __fmul_rn(xr[i], scale);
+    } else {
+        const float* wr = w + (i1 % we1) * wb1 + (i2 % we2) * wb2 + (i3 % we3) * wb3;
+        for (int64_t i = threadIdx.x; i < K; i += blockDim.x) yr[i] = __fmul_rn(__fmul_rn(xr[i], scale), wr[i]);
+    }
 }
 
 // ---------------------------------------------------------------- rope
@@ -138,14 +148,16 @@ __global__ void soft_max_kernel(const float* __restrict__ x, int64_t xb1, int64_
 
 // ---------------------------------------------------------------- silu
 // f32::vec_silu (src/lib.rs:543-549): y = f32(SILU_LUT[bits(f16(x))]).
+// With `u` (same shape as x) the SwiGLU product y = silu(x) * u is formed in the same launch.
 __global__ void silu_kernel(const float* __restrict__ x, int64_t xb1, float* __restrict__ y, int64_t yb1, int64_t nc,
-                            int64_t nr, const uint16_t* __restrict__ lut) {
+                            int64_t nr, const uint16_t* __restrict__ lut, const float* __restrict__ u, int64_t ub1) {
     gb_pdl_entry();
     const int64_t total = nc * nr;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / nc, c = i - r * nc;
         const unsigned short h = __half_as_ushort(__float2half_rn(x[r * xb1 + c]));
-        y[r * yb1 + c] = __half2float(__ushort_as_half(__ldg(lut + h)));
+        const float v = __half2float(__ushort_as_half(__ldg(lut + h)));
+        y[r * yb1 + c] = u ? __fmul_rn(v, u[r * ub1 + c]) : v;
     }
 }
 
@@ -240,8 +252,25 @@ extern "C" int galois_b200_rms_norm_f32(galois_b200_ctx* ctx, const float* x, co
     const int64_t K = xd->ne[0], nr = xd->ne[1] * xd->ne[2] * xd->ne[3];
     if (K == 0 || nr == 0) return 0;
     gb_launch(ctx, rms_norm_kernel, dim3((unsigned)nr), dim3(row_threads(K)), 0, x, xd->nb[1], xd->nb[2], xd->nb[3], y, yd->nb[1],
-                                                                      yd->nb[2], yd->nb[3], K, xd->ne[1], xd->ne[2], eps);
+              yd->nb[2], yd->nb[3], K, xd->ne[1], xd->ne[2], eps, (const float*)nullptr, (int64_t)0, (int64_t)0, (int64_t)0, (int64_t)1,
+              (int64_t)1, (int64_t)1);
     GB_LAUNCHED(ctx, "rms_norm");
+    return 0;
+}
+
+extern "C" int galois_b200_rms_norm_mul_f32(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, const float* w,
+                                            const galois_dim* wd, float* y, const galois_dim* yd, float eps) {
+    GB_CHECK_CTX(ctx);
+    if (any_null(x, xd, y, yd) || any_null(w, wd)) return gb_fail(ctx, GALOIS_B200_E_BADARG, "rms_norm_mul: null pointer");
+    if (!gb_same_shape(xd, yd)) return gb_fail(ctx, GALOIS_B200_E_SHAPE, "rms_norm_mul: src and dst shapes differ");
+    if (xd->nb[0] != 1 || yd->nb[0] != 1 || wd->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "rms_norm_mul: rows must be contiguous");
+    if (wd->ne[0] < xd->ne[0] || wd->ne[1] < 1 || wd->ne[2] < 1 || wd->ne[3] < 1)
+        return gb_fail(ctx, GALOIS_B200_E_SHAPE, "rms_norm_mul: gain row shorter than src row");
+    const int64_t K = xd->ne[0], nr = xd->ne[1] * xd->ne[2] * xd->ne[3];
+    if (K == 0 || nr == 0) return 0;
+    gb_launch(ctx, rms_norm_kernel, dim3((unsigned)nr), dim3(row_threads(K)), 0, x, xd->nb[1], xd->nb[2], xd->nb[3], y, yd->nb[1],
+              yd->nb[2], yd->nb[3], K, xd->ne[1], xd->ne[2], eps, w, wd->nb[1], wd->nb[2], wd->nb[3], wd->ne[1], wd->ne[2], wd->ne[3]);
+    GB_LAUNCHED(ctx, "rms_norm_mul");
     return 0;
 }
 
@@ -318,8 +347,23 @@ extern "C" int galois_b200_silu_f32(galois_b200_ctx* ctx, const float* x, const 
     if (xd->nb[0] != 1 || yd->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "silu: rows must be contiguous");
     const int64_t nc = xd->ne[0], nr = xd->ne[1] * xd->ne[2] * xd->ne[3];
     if (nc == 0 || nr == 0) return 0;
-    gb_launch(ctx, silu_kernel, dim3(ew_grid(nc * nr, ctx->sm_count)), dim3(256), 0, x, xd->nb[1], y, yd->nb[1], nc, nr, ctx->silu_lut);
+    gb_launch(ctx, silu_kernel, dim3(ew_grid(nc * nr, ctx->sm_count)), dim3(256), 0, x, xd->nb[1], y, yd->nb[1], nc, nr, ctx->silu_lut,
+              (const float*)nullptr, (int64_t)0);
     GB_LAUNCHED(ctx, "silu");
+    return 0;
+}
+
+extern "C" int galois_b200_silu_mul_f32(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, const float* u,
+                                        const galois_dim* ud, float* y, const galois_dim* yd) {
+    GB_CHECK_CTX(ctx);
+    if (any_null(x, xd, y, yd) || any_null(u, ud)) return gb_fail(ctx, GALOIS_B200_E_BADARG, "silu_mul: null pointer");
+    if (!gb_same_shape(xd, yd) || !gb_same_shape(xd, ud)) return gb_fail(ctx, GALOIS_B200_E_SHAPE, "silu_mul: operand shapes differ");
+    if (xd->nb[0] != 1 || yd->nb[0] != 1 || ud->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "silu_mul: rows must be contiguous");
+    const int64_t nc = xd->ne[0], nr = xd->ne[1] * xd->ne[2] * xd->ne[3];
+    if (nc == 0 || nr == 0) return 0;
+    gb_launch(ctx, silu_kernel, dim3(ew_grid(nc * nr, ctx->sm_count)), dim3(256), 0, x, xd->nb[1], y, yd->nb[1], nc, nr, ctx->silu_lut, u,
+              ud->nb[1]);
+    GB_LAUNCHED(ctx, "silu_mul");
     return 0;
 }
 

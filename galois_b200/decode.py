@@ -18,7 +18,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from .op import (RopeCustomOption, UnaryOp, galois_add, galois_cpy, galois_matmul, galois_mul, galois_rms_norm,
-                 galois_rope_custom, galois_soft_max_ext, galois_unary)
+                 galois_rms_norm_mul, galois_rope_custom, galois_silu_mul, galois_soft_max_ext, galois_unary)
 from .tensor import Device, GGmlType, Tensor
 
 
@@ -44,15 +44,32 @@ def weight_shapes(s: LayerShape):
 
 class DecodeLayer:
     """Weights (Q4_0 bytes, host numpy), norm gains and the two caches live on one GPU; `step`
-    enqueues the ~22 kernels of one token on the device's stream and returns the output tensor."""
+    enqueues the kernels of one token on the device's stream and returns the output tensor.
+
+    ``fused=False``: the op-by-op sequence a galois caller writes, 22 kernels.
+    ``fused=True`` : the same arithmetic in 15 kernels.  The rows of Wq, Wk, Wv (and of W_gate,
+    W_up) are stacked into one Q4_0 weight at upload, so the three (two) projections of the same
+    input are one mat-mul whose result is split by views; rope runs once over the 2 x heads rows of
+    q and k; rms_norm + gain and silu + gate product use the two-op fusions of the library.  Rows
+    of a mat-mul are independent and the fusions round like the op pairs, so both variants give
+    the same numbers bit for bit."""
 
     def __init__(self, dev, shape: LayerShape, weights: dict, attn_norm: np.ndarray, ffn_norm: np.ndarray,
-                 k_cache: np.ndarray, v_cache: np.ndarray):
+                 k_cache: np.ndarray, v_cache: np.ndarray, fused: bool = False):
         s, G = shape, Device.Gpu(dev)
-        self.shape, self.dev = s, dev
+        self.shape, self.dev, self.fused = s, dev, fused
         self.w = {}
         for name, (n, k) in weight_shapes(s).items():
+            if fused and name in ("wq", "wk", "wv", "w_gate", "w_up"):
+                continue
             self.w[name] = Tensor.from_raw(weights[name], (k, n), GGmlType.Q4_0, G)
+        if fused:
+            raw = lambda name: np.ascontiguousarray(weights[name]).view(np.uint8).reshape(-1)
+            self.w["wqkv"] = Tensor.from_raw(np.concatenate([raw("wq"), raw("wk"), raw("wv")]), (s.hidden, 3 * s.hidden), GGmlType.Q4_0, G)
+            self.w["w_gate_up"] = Tensor.from_raw(np.concatenate([raw("w_gate"), raw("w_up")]), (s.hidden, 2 * s.ffn), GGmlType.Q4_0, G)
+            self.qkv = Tensor.zeros((3 * s.hidden, 1), GGmlType.F32, G)
+            self.qkr = Tensor.zeros((s.head_dim, 2 * s.heads, 1), GGmlType.F32, G)
+            self.gu = Tensor.zeros((2 * s.ffn, 1), GGmlType.F32, G)
         self.attn_norm = Tensor.from_numpy(attn_norm.reshape(1, s.hidden), GGmlType.F32, G)
         self.ffn_norm = Tensor.from_numpy(ffn_norm.reshape(1, s.hidden), GGmlType.F32, G)
         # caches arrive as f16 arrays [heads][ctx][head_dim] and [heads][head_dim][ctx]
@@ -72,6 +89,8 @@ class DecodeLayer:
 
     def step(self, x: Tensor, pos: Tensor, position: int) -> Tensor:
         """x: f32 {hidden, 1}; pos: i32 {1} holding `position` (the row of the caches to fill)."""
+        if self.fused:
+            return self._step_fused(x, pos, position)
         s = self.shape
         hd, nh, ctx = s.head_dim, s.heads, s.ctx
         # attention block
@@ -108,6 +127,39 @@ class DecodeLayer:
         galois_matmul(self.w["w_up"], self.h2, self.u)
         galois_unary(self.g, self.a, UnaryOp.Silu)
         galois_mul(self.a, self.u, self.a)
+        galois_matmul(self.w["w_down"], self.a, self.d)
+        galois_add(self.x2, self.d, self.out)
+        return self.out
+
+    def _step_fused(self, x: Tensor, pos: Tensor, position: int) -> Tensor:
+        s = self.shape
+        hd, nh, ctx, H = s.head_dim, s.heads, s.ctx, s.hidden
+        # attention block
+        galois_rms_norm_mul(x, self.attn_norm, self.h, s.eps)
+        galois_matmul(self.w["wqkv"], self.h, self.qkv)  # rows [0, H) = q, [H, 2H) = k, [2H, 3H) = v
+        qk3 = self.qkv.view((hd, 2 * nh, 1), (1, hd, hd * 2 * nh, hd * 2 * nh))
+        galois_rope_custom(self.rope, qk3, pos, self.qkr)  # heads 0..nh-1 of q, then of k
+        k_src = self.qkr.view((hd, 1, nh), (1, hd, hd, hd * nh), offset=H)
+        k_dst = self.k_cache.view((hd, 1, nh), (1, hd, hd * ctx, hd * ctx * nh), offset=position * hd)
+        galois_cpy(k_src, k_dst)
+        v_src = self.qkv.view((1, hd, nh), (1, 1, hd, hd * nh), offset=2 * H)
+        v_dst = self.v_cache.view((1, hd, nh), (1, ctx, hd * ctx, hd * ctx * nh), offset=position)
+        galois_cpy(v_src, v_dst)
+        qh = self.qkr.view((hd, 1, nh), (1, hd, hd, hd * nh))
+        galois_matmul(self.k_cache, qh, self.scores)
+        sc = self.scores.view((ctx, nh, 1), (1, ctx, ctx * nh, ctx * nh))
+        pr = self.probs.view((ctx, nh, 1), (1, ctx, ctx * nh, ctx * nh))
+        galois_soft_max_ext(sc, pr, self.scale, pos)
+        galois_matmul(self.v_cache, self.probs, self.ctxv)
+        ctx_flat = self.ctxv.view((H, 1), (1, H, H, H))
+        galois_matmul(self.w["wo"], ctx_flat, self.o)
+        galois_add(x, self.o, self.x2)
+        # feed-forward block (SwiGLU)
+        galois_rms_norm_mul(self.x2, self.ffn_norm, self.h2, s.eps)
+        galois_matmul(self.w["w_gate_up"], self.h2, self.gu)  # rows [0, ffn) = gate, [ffn, 2 ffn) = up
+        g = self.gu.view((s.ffn, 1), (1, s.ffn, s.ffn, s.ffn))
+        u = self.gu.view((s.ffn, 1), (1, s.ffn, s.ffn, s.ffn), offset=s.ffn)
+        galois_silu_mul(g, u, self.a)
         galois_matmul(self.w["w_down"], self.a, self.d)
         galois_add(self.x2, self.d, self.out)
         return self.out

@@ -92,6 +92,24 @@ def galois_rms_norm(src: Tensor, dst: Tensor, eps: float) -> None:
     _check(ctx, lib.galois_b200_rms_norm_f32(ctx, _p(src), _d(src), _p(dst), _d(dst), eps), "galois_rms_norm")
 
 
+def galois_rms_norm_mul(src: Tensor, gain: Tensor, dst: Tensor, eps: float) -> None:
+    """galois_rms_norm (src/op.rs:3155-3169) followed by galois_mul with `gain` (src/op.rs:3113-3127) in one
+    launch; bit-identical to the two calls.  Not part of the reference API."""
+    ctx = _gpu_ctx(src, gain, dst)
+    for t in (src, gain, dst):
+        _want(t, GGmlType.F32, "galois_rms_norm_mul")
+    _check(ctx, lib.galois_b200_rms_norm_mul_f32(ctx, _p(src), _d(src), _p(gain), _d(gain), _p(dst), _d(dst), eps), "galois_rms_norm_mul")
+
+
+def galois_silu_mul(src: Tensor, other: Tensor, dst: Tensor) -> None:
+    """galois_unary(Silu) (src/op.rs:3232-3256) followed by galois_mul with `other` (src/op.rs:3113-3127) in one
+    launch; bit-identical to the two calls.  Not part of the reference API."""
+    ctx = _gpu_ctx(src, other, dst)
+    for t in (src, other, dst):
+        _want(t, GGmlType.F32, "galois_silu_mul")
+    _check(ctx, lib.galois_b200_silu_mul_f32(ctx, _p(src), _d(src), _p(other), _d(other), _p(dst), _d(dst)), "galois_silu_mul")
+
+
 def galois_rope_custom(op: RopeCustomOption, src0: Tensor, src1: Tensor, dst: Tensor) -> None:
     """src/op.rs:3304-3341; src1 holds the i32 positions."""
     ctx = _gpu_ctx(src0, src1, dst)

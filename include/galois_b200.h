@@ -204,6 +204,19 @@ int galois_b200_mul_f32(galois_b200_ctx* ctx, const float* a, const galois_dim* 
 int galois_b200_add_f32(galois_b200_ctx* ctx, const float* a, const galois_dim* ad, const float* b,
                         const galois_dim* bd, float* dst, const galois_dim* dd);
 
+/* Two-op fusions a caller may use in place of the op pairs they name; results are
+ * bit-identical to running the two ops one after the other (each f32 multiply is
+ * rounded separately).
+ *  - rms_norm_mul: galois_rms_norm followed by galois_mul with a gain tensor
+ *    (src/op.rs:3155-3169 then :3113-3127; w broadcast by modulo over dims 1..3 as
+ *    Mul::f does, src/op.rs:318-611);
+ *  - silu_mul: galois_unary(Silu) followed by galois_mul (the SwiGLU gate;
+ *    src/op.rs:3232-3256 then :3113-3127), u of the same shape as x. */
+int galois_b200_rms_norm_mul_f32(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, const float* w,
+                                 const galois_dim* wd, float* y, const galois_dim* yd, float eps);
+int galois_b200_silu_mul_f32(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, const float* u,
+                             const galois_dim* ud, float* y, const galois_dim* yd);
+
 /* CudaMap2::f_g_c for CudaScale (src/cuda.rs:1597-1638, scale.cu:1-11): the
  * scalar lives on the host, as in the (Gpu, Cpu, Gpu) arm of galois_scale
  * (src/op.rs:3271-3273). */

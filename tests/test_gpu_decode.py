@@ -80,3 +80,35 @@ def test_decode_layer_step(dev, oracle, hidden, heads, ffn, ctx, position):
     assert np.array_equal(gv[:, :, untouched], v_cache[:, :, untouched])
     assert_close(O.f16_to_f32(gk[:, position, :]), O.f16_to_f32(kc[:, position, :]), rel_l2=2e-3, max_abs=1e-2)
     assert_close(O.f16_to_f32(gv[:, :, position]), O.f16_to_f32(vc[:, :, position]), rel_l2=2e-3, max_abs=1e-2)
+
+
+@pytest.mark.parametrize("hidden,heads,ffn,ctx,position", [(512, 4, 1024, 256, 17), (4096, 32, 11008, 2048, 2047)])
+def test_fused_layer_equals_op_by_op_layer(dev, oracle, hidden, heads, ffn, ctx, position):
+    """Stacked Q/K/V and gate/up weights, one rope over q and k, and the two-op fusions give the
+    numbers of the op-by-op layer bit for bit (outputs and both caches)."""
+    import galois_b200 as gb
+    from galois_b200.decode import DecodeLayer, LayerShape, weight_shapes
+
+    O = oracle
+    s = LayerShape(hidden=hidden, heads=heads, head_dim=hidden // heads, ffn=ffn, ctx=ctx)
+    wq4 = {name: O.quantize_q4_0(O.fill_normal(n * k, 4300 + i, 0, 0.02).reshape(n, k))
+           for i, (name, (n, k)) in enumerate(weight_shapes(s).items())}
+    attn_norm = 1.0 + 0.1 * O.fill_normal(hidden, 4400)
+    ffn_norm = 1.0 + 0.1 * O.fill_normal(hidden, 4401)
+    k_cache = O.f32_to_f16(O.fill_normal(heads * ctx * s.head_dim, 4402).reshape(heads, ctx, s.head_dim)).view(np.float16)
+    v_cache = O.f32_to_f16(O.fill_normal(heads * ctx * s.head_dim, 4403).reshape(heads, s.head_dim, ctx)).view(np.float16)
+    x = O.fill_normal(hidden, 4404).reshape(1, hidden)
+    G = gb.Device.Gpu(dev)
+    xt = gb.Tensor.from_numpy(x, gb.GGmlType.F32, G)
+    pt = gb.Tensor.from_numpy(np.array([position], np.int32), gb.GGmlType.I32, G)
+    plain = DecodeLayer(dev, s, wq4, attn_norm, ffn_norm, k_cache, v_cache)
+    fused = DecodeLayer(dev, s, wq4, attn_norm, ffn_norm, k_cache, v_cache, fused=True)
+    l0 = dev.launch_count()
+    a = plain.step(xt, pt, position).to_numpy()
+    l1 = dev.launch_count()
+    b = fused.step(xt, pt, position).to_numpy()
+    l2 = dev.launch_count()
+    assert np.array_equal(a, b)
+    assert np.array_equal(plain.k_cache.to_numpy().view(np.uint16), fused.k_cache.to_numpy().view(np.uint16))
+    assert np.array_equal(plain.v_cache.to_numpy().view(np.uint16), fused.v_cache.to_numpy().view(np.uint16))
+    assert (l1 - l0, l2 - l1) == (22, 15)

@@ -437,3 +437,34 @@ def test_cpy_bit_exact(gb, dev, oracle):
     assert np.array_equal(dst.to_numpy(), x[0].T)
     with pytest.raises(gb.GError):   # element counts differ
         gb.galois_cpy(_gpu(gb, dev, x), gb.Tensor.zeros((64, 5), gb.GGmlType.F32, G))
+
+
+def test_two_op_fusions_are_bit_identical(gb, dev, oracle):
+    """rms_norm_mul == rms_norm then mul; silu_mul == silu then mul: on the GPU bit for bit, and
+    against the oracle's two-op sequence."""
+    O = oracle
+    G = gb.Device.Gpu(dev)
+    for (k, rows, seed) in [(4096, 1, 1), (70, 5, 2), (11008, 3, 3)]:
+        x = O.fill_normal(rows * k, 600 + seed).reshape(rows, k)
+        w = 1.0 + 0.1 * O.fill_normal(k, 700 + seed).reshape(1, k)
+        u = O.fill_normal(rows * k, 800 + seed).reshape(rows, k)
+        xt, wt, ut = _gpu(gb, dev, x), _gpu(gb, dev, w), _gpu(gb, dev, u)
+        y1, y2, t = (gb.Tensor.zeros((k, rows), gb.GGmlType.F32, G) for _ in range(3))
+        gb.galois_rms_norm(xt, t, 1e-6)
+        gb.galois_mul(t, wt, y1)
+        gb.galois_rms_norm_mul(xt, wt, y2, 1e-6)
+        assert np.array_equal(y1.to_numpy(), y2.to_numpy())
+        assert_close(y2.to_numpy(), O.mul(O.rms_norm(x, 1e-6), w))
+        gb.galois_unary(xt, t, gb.UnaryOp.Silu)
+        gb.galois_mul(t, ut, y1)
+        gb.galois_silu_mul(xt, ut, y2)
+        assert np.array_equal(y1.to_numpy(), y2.to_numpy())
+        assert np.array_equal(y2.to_numpy(), O.mul(O.silu(x), u))
+    # shape errors
+    bad = gb.Tensor.zeros((8, 2), gb.GGmlType.F32, G)
+    with pytest.raises(gb.GError) as ei:
+        gb.galois_silu_mul(_gpu(gb, dev, np.zeros((2, 16), np.float32)), bad, gb.Tensor.zeros((16, 2), gb.GGmlType.F32, G))
+    assert ei.value.code == -2
+    with pytest.raises(gb.GError) as ei:
+        gb.galois_rms_norm_mul(_gpu(gb, dev, np.zeros((2, 16), np.float32)), bad, gb.Tensor.zeros((16, 2), gb.GGmlType.F32, G), 1e-6)
+    assert ei.value.code == -2
