@@ -11,6 +11,7 @@ from .op import (  # noqa: F401
     galois_cont,
     galois_cpy,
     galois_matmul,
+    galois_matmul_add,
     galois_mul,
     galois_rms_norm,
     galois_rms_norm_mul,

@@ -9,6 +9,7 @@
 #include "mul_mat_q4_0.cuh"
 #include "mul_mat_q4_0_tc.cuh"
 #include "mmq_skinny.cuh"
+#include "gather.cuh"
 #include "quantize.cuh"
 
 static char g_init_err[512] = "";
@@ -125,8 +126,8 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
         if ((q = strstr(t, "smem_kb="))) ctx->tune_smem_kb = atoi(q + 8);
         if ((q = strstr(t, "cps="))) ctx->tune_ctas_per_sm = atoi(q + 4);
         if ((q = strstr(t, "pdl="))) ctx->pdl = atoi(q + 4);
-        if ((q = strstr(t, "dbg="))) ctx->tune_dbg = atoi(q + 4);
         if ((q = strstr(t, "cluster="))) ctx->tune_cluster = atoi(q + 8);
+        if ((q = strstr(t, "seg="))) ctx->tune_seg = atoi(q + 4);
         if ((q = strstr(t, "variant="))) ctx->variant = atoi(q + 8);
     }
 
@@ -343,6 +344,29 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
         ctx->prof_n++;
     }
     return rc;
+}
+
+extern "C" int galois_b200_mul_mat_q4_0_f32_add(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
+                                                const galois_dim* xd, const float* res, const galois_dim* rd, float* dst,
+                                                const galois_dim* dd) {
+    GB_CHECK_CTX(ctx);
+    if (!res || !rd || !dd) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_add: null pointer");
+    if (!gb_same_shape(rd, dd)) return gb_fail(ctx, GALOIS_B200_E_SHAPE, "mul_mat_q4_0_add: residual and dst shapes differ");
+    if (rd->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0_add: residual rows must be contiguous");
+    int rc = gb_validate_mul_mat(ctx, w, wd, x, xd, dst, dd);
+    if (rc) return rc;
+    const int64_t nrows = xd->ne[1] * xd->ne[2] * xd->ne[3];
+    if (wd->ne[1] == 0 || nrows == 0) return 0;
+    // one activation row on the streaming GEMV: the sum is formed where the result is stored
+    if (ctx->variant == 0 && wd->ne[0] > 0 && xd->ne[1] < GB_SKINNY_MIN_BATCH && rd->nb[1] < (1ll << 30) &&
+        gb_gemv_supported(ctx, w, wd, x, xd, dd)) {
+        gb_gather_args none = {};
+        return gb_gemv_q4_0_gather(ctx, w, wd, x, xd, dst, dd, &none, res, rd->nb[1]);
+    }
+    // any other shape: the two ops one after the other (Add::f needs a contiguous dst; it may alias src1)
+    rc = galois_b200_mul_mat_q4_0_f32(ctx, w, wd, x, xd, dst, dd);
+    if (rc) return rc;
+    return galois_b200_add_f32(ctx, res, rd, dst, dd, dst, dd);
 }
 
 extern "C" int galois_b200_set_pdl(galois_b200_ctx* ctx, int on) {

@@ -21,7 +21,7 @@ struct galois_b200_ctx {
     int sm_count;
     int variant;           // forced Q4_0 mat-mul variant (0 = automatic)
     // launch-geometry overrides for the bulk-copy GEMV (0 = automatic), from GALOIS_B200_TUNE
-    int tune_warps, tune_r, tune_stages, tune_smem_kb, tune_ctas_per_sm, tune_dbg, tune_cluster;
+    int tune_warps, tune_r, tune_stages, tune_smem_kb, tune_ctas_per_sm, tune_cluster, tune_seg;
     int pdl;               // launch the streaming kernels with programmatic dependent launch (default on)
     int64_t launches;      // kernels launched through this context
     // f16 look-up tables (65 536 entries each), device copies

@@ -135,7 +135,7 @@ extern "C" int galois_b200_mul_mat_q4_0_f32_gather(galois_b200_ctx* ctx, const v
         if (rc != 0) return rc;
         // the same kernel choice as the unsharded entry point, so that sharded and unsharded results agree bit for bit
         if (ctx->variant == 0 && wd->ne[0] > 0 && xd->ne[1] < GB_SKINNY_MIN_BATCH && gb_gemv_supported(ctx, w_band, wd, x, xd, &band))
-            return gb_gemv_q4_0_gather(ctx, w_band, wd, x, xd, local, &band, &args);  // one kernel in all
+            return gb_gemv_q4_0_gather(ctx, w_band, wd, x, xd, local, &band, &args, nullptr, 0);  // one kernel in all
         rc = galois_b200_mul_mat_q4_0_f32(ctx, w_band, wd, x, xd, local, &band);
         if (rc != 0) return rc;
     }

@@ -176,7 +176,7 @@ __device__ __forceinline__ void quantize_rows_cluster(const float* __restrict__ 
 template <int NB, int SEG, bool SPLIT, int NPASS>
 __global__ void __launch_bounds__(GEMV_THREADS)
     gemv_q4_0_kernel(const uint8_t* __restrict__ w, const float* __restrict__ x, int x_stride, float* __restrict__ dst, int nb1, int K, int N, int nbatch, int stages,
-                     int* __restrict__ status, int dbg, const gb_gather_args G) {
+                     int* __restrict__ status, const gb_gather_args G, const float* __restrict__ res, int res_nb1) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
 
@@ -224,11 +224,8 @@ __global__ void __launch_bounds__(GEMV_THREADS)
     cluster_arrive_relaxed();  // this CTA's shared memory and act_bar exist
     pdl_wait();                // the activations (and whatever dst aliases) belong to the preceding kernels
     cluster_wait();            // so do every peer's
-    bool ok = true;
-    if (!(dbg & 2)) {
-        quantize_rows_cluster<SEG>(x, x_stride, K, nbatch, NB, act_qs, act_ds, nsegk, crank, csize, act_bar);
-        ok = mbar_wait_bounded(act_bar, 0);  // all slices of the quantised activations have landed here
-    }
+    quantize_rows_cluster<SEG>(x, x_stride, K, nbatch, NB, act_qs, act_ds, nsegk, crank, csize, act_bar);
+    bool ok = mbar_wait_bounded(act_bar, 0);  // all slices of the quantised activations have landed here
 
     int yh[HOIST ? NPASS : 1][HOIST ? 16 * SEG : 1];
     float4 dh[HOIST ? NPASS : 1][HOIST ? SEG : 1];
@@ -250,7 +247,7 @@ __global__ void __launch_bounds__(GEMV_THREADS)
 
     for (int j = 0; j < my_chunks && ok; j++) {
         const int s = j % stages;
-        ok = mbar_wait_bounded(&my_bars[s], (uint32_t)(j / stages) & 1u, (dbg >> 8) ? (uint32_t)(dbg >> 8) : 20000u);
+        ok = mbar_wait_bounded(&my_bars[s], (uint32_t)(j / stages) & 1u);
         if (!ok) break;
         const uint8_t* buf = ring + (uint32_t)s * chunk_bytes;
         const int row0 = (gw + j * tw) * rows_per_chunk;
@@ -259,9 +256,7 @@ __global__ void __launch_bounds__(GEMV_THREADS)
 #pragma unroll
         for (int b = 0; b < NB; b++) acc[b] = 0.0f;
 
-        if (dbg & 1) {
-            acc[0] = __uint_as_float(reinterpret_cast<const uint32_t*>(buf)[lane]);
-        } else if (HOIST) {
+        if (HOIST) {
 #pragma unroll
             for (int q = 0; q < NPASS; q++) {
                 const int sg = lane + 32 * q;  // SPLIT: NPASS == 1 and the chunk is exactly 32 segments
@@ -298,6 +293,7 @@ __global__ void __launch_bounds__(GEMV_THREADS)
                 float v = acc[b];
                 for (int o = nsegk >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
                 if ((lane & (nsegk - 1)) == 0 && row0 + r < N && b < nbatch) {
+                    if (res) v = __fadd_rn(res[b * res_nb1 + row0 + r], v);  // Add::f on top of the mat-mul result
                     dst[b * nb1 + row0 + r] = v;
                     if (G.P.nranks) gb_gather_send(G, b, row0 + r, v);
                 }
@@ -305,8 +301,9 @@ __global__ void __launch_bounds__(GEMV_THREADS)
         } else {
 #pragma unroll
             for (int b = 0; b < NB; b++) {
-                const float v = gb_warp_sum(acc[b]);
+                float v = gb_warp_sum(acc[b]);
                 if (lane == 0 && b < nbatch) {
+                    if (res) v = __fadd_rn(res[b * res_nb1 + row0], v);
                     dst[b * nb1 + row0] = v;
                     if (G.P.nranks) gb_gather_send(G, b, row0, v);
                 }
@@ -336,7 +333,7 @@ gemv_plan plan_gemv(const galois_b200_ctx* ctx, int64_t K, int64_t N, int64_t B)
     // Else the (segment, passes) pair with the best lane utilisation; with one activation row it
     // must keep at most 6 block pairs per lane so that the activations fit in registers.
     int max_seg = p.nbt == 1 ? 4 : 2;  // wider segments spill when activations are not hoisted
-    if (ctx->tune_r == 1 || ctx->tune_r == 2) max_seg = ctx->tune_r;
+    if (ctx->tune_seg == 1 || ctx->tune_seg == 2) max_seg = ctx->tune_seg;
     p.seg = 0;
     for (int seg = max_seg; seg >= 1 && !p.seg; seg >>= 1) {
         const int64_t nsegk = npair / seg;
@@ -398,7 +395,7 @@ cudaError_t gemv_attr() {
 
 template <int NB, int SEG, bool SPLIT, int NPASS>
 int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, const float* x, int x_stride, float* dst, int nb1,
-                int K, int N, int B, const gb_gather_args& gather) {
+                int K, int N, int B, const gb_gather_args& gather, const float* res, int res_nb1) {
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute at[2];
     int na = 0;
@@ -419,7 +416,7 @@ int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, cons
     cfg.blockDim = dim3(GEMV_THREADS);
     cfg.dynamicSmemBytes = p.smem;
     GB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_0_kernel<NB, SEG, SPLIT, NPASS>, w, x, x_stride, dst, nb1, K, N, B, p.stages,
-                                    ctx->dev_status, ctx->tune_dbg, gather));
+                                    ctx->dev_status, gather, res, res_nb1));
     ctx->launches++;
     return 0;
 }
@@ -449,11 +446,11 @@ bool gb_gemv_supported(const galois_b200_ctx* ctx, const void* w, const galois_d
 int gb_gemv_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
                  const galois_dim* dd) {
     gb_gather_args none = {};
-    return gb_gemv_q4_0_gather(ctx, w, wd, x, xd, dst, dd, &none);
+    return gb_gemv_q4_0_gather(ctx, w, wd, x, xd, dst, dd, &none, nullptr, 0);
 }
 
 int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
-                        const galois_dim* dd, const gb_gather_args* gather) {
+                        const galois_dim* dd, const gb_gather_args* gather, const float* res, int64_t res_nb1) {
     const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
     const gemv_plan p = plan_gemv(ctx, K, N, B);
     if (!p.ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: shape not supported by the streaming GEMV");
@@ -461,7 +458,7 @@ int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* w
     const int nb1 = (int)dd->nb[1], xs = (int)xd->nb[1];
 #define X(NB_, SEG_, SPLIT_, NP_)                                                   \
     if (p.nbt == NB_ && p.seg == SEG_ && p.split == SPLIT_ && p.npass == NP_)       \
-        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, x, xs, dst, nb1, K, N, B, *gather);
+        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, x, xs, dst, nb1, K, N, B, *gather, res, (int)res_nb1);
     GB_GEMV_INSTANCES(X)
 #undef X
     return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: no streaming-GEMV instance for this shape");

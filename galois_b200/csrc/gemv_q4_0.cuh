@@ -16,5 +16,7 @@ int gb_gemv_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, cons
 // The same launch for one band of a row-sharded mat-mul: `dst` points at the band's first row
 // inside this rank's full result (gather->P.nranks == 0: not sharded).  Each result also goes to
 // every peer's inbox and the kernel's tail receives the peers' bands (protocol of gather.cuh).
+// `res` (optional, same shape as dst, row stride res_nb1): dst = res + mat-mul result, the sum
+// rounded once as Add::f rounds it.
 int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
-                        const galois_dim* dd, const gb_gather_args* gather);
+                        const galois_dim* dd, const gb_gather_args* gather, const float* res, int64_t res_nb1);

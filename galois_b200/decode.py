@@ -17,7 +17,7 @@ from dataclasses import dataclass
 
 import numpy as np
 
-from .op import (RopeCustomOption, UnaryOp, galois_add, galois_cpy, galois_matmul, galois_mul, galois_rms_norm,
+from .op import (RopeCustomOption, UnaryOp, galois_add, galois_cpy, galois_matmul, galois_matmul_add, galois_mul, galois_rms_norm,
                  galois_rms_norm_mul, galois_rope_custom, galois_silu_mul, galois_soft_max_ext, galois_unary)
 from .tensor import Device, GGmlType, Tensor
 
@@ -47,10 +47,11 @@ class DecodeLayer:
     enqueues the kernels of one token on the device's stream and returns the output tensor.
 
     ``fused=False``: the op-by-op sequence a galois caller writes, 22 kernels.
-    ``fused=True`` : the same arithmetic in 15 kernels.  The rows of Wq, Wk, Wv (and of W_gate,
+    ``fused=True`` : the same arithmetic in 13 kernels.  The rows of Wq, Wk, Wv (and of W_gate,
     W_up) are stacked into one Q4_0 weight at upload, so the three (two) projections of the same
     input are one mat-mul whose result is split by views; rope runs once over the 2 x heads rows of
-    q and k; rms_norm + gain and silu + gate product use the two-op fusions of the library.  Rows
+    q and k; rms_norm + gain, silu + gate product and mat-mul + residual use the two-op fusions of
+    the library.  Rows
     of a mat-mul are independent and the fusions round like the op pairs, so both variants give
     the same numbers bit for bit."""
 
@@ -152,16 +153,14 @@ class DecodeLayer:
         galois_soft_max_ext(sc, pr, self.scale, pos)
         galois_matmul(self.v_cache, self.probs, self.ctxv)
         ctx_flat = self.ctxv.view((H, 1), (1, H, H, H))
-        galois_matmul(self.w["wo"], ctx_flat, self.o)
-        galois_add(x, self.o, self.x2)
+        galois_matmul_add(self.w["wo"], ctx_flat, x, self.x2)  # x2 = x + Wo ctx
         # feed-forward block (SwiGLU)
         galois_rms_norm_mul(self.x2, self.ffn_norm, self.h2, s.eps)
         galois_matmul(self.w["w_gate_up"], self.h2, self.gu)  # rows [0, ffn) = gate, [ffn, 2 ffn) = up
         g = self.gu.view((s.ffn, 1), (1, s.ffn, s.ffn, s.ffn))
         u = self.gu.view((s.ffn, 1), (1, s.ffn, s.ffn, s.ffn), offset=s.ffn)
         galois_silu_mul(g, u, self.a)
-        galois_matmul(self.w["w_down"], self.a, self.d)
-        galois_add(self.x2, self.d, self.out)
+        galois_matmul_add(self.w["w_down"], self.a, self.x2, self.out)  # out = x2 + Wdown a
         return self.out
 
     def algorithmic_bytes(self) -> int:

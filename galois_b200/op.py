@@ -92,6 +92,17 @@ def galois_rms_norm(src: Tensor, dst: Tensor, eps: float) -> None:
     _check(ctx, lib.galois_b200_rms_norm_f32(ctx, _p(src), _d(src), _p(dst), _d(dst), eps), "galois_rms_norm")
 
 
+def galois_matmul_add(src0: Tensor, src1: Tensor, res: Tensor, dst: Tensor) -> None:
+    """galois_matmul (src/op.rs:3093-3111, Q4_0 x F32) followed by galois_add of `res` (src/op.rs:3073-3091) in one
+    call; bit-identical to the two calls.  Not part of the reference API."""
+    ctx = _gpu_ctx(src0, src1, res, dst)
+    _want(src0, GGmlType.Q4_0, "galois_matmul_add src0")
+    for t in (src1, res, dst):
+        _want(t, GGmlType.F32, "galois_matmul_add")
+    rc = lib.galois_b200_mul_mat_q4_0_f32_add(ctx, _p(src0), _d(src0), _p(src1), _d(src1), _p(res), _d(res), _p(dst), _d(dst))
+    _check(ctx, rc, "galois_matmul_add")
+
+
 def galois_rms_norm_mul(src: Tensor, gain: Tensor, dst: Tensor, eps: float) -> None:
     """galois_rms_norm (src/op.rs:3155-3169) followed by galois_mul with `gain` (src/op.rs:3113-3127) in one
     launch; bit-identical to the two calls.  Not part of the reference API."""

@@ -132,6 +132,16 @@ int galois_b200_block_isums_q4_0_q8_0(galois_b200_ctx* ctx, const void* w, const
 int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
                                  const galois_dim* xd, float* dst, const galois_dim* dd);
 
+/* galois_matmul followed by galois_add of a residual (src/op.rs:3093-3111 then
+ * :3073-3091) in one call: dst = res + mat-mul result, the sum rounded once as
+ * Add::f rounds it, so the result is bit-identical to the two calls.  `res` has
+ * the shape of dst.  With one activation row the sum is formed inside the
+ * streaming GEMV (no second launch); other shapes run the two ops.  Not part of
+ * the reference API. */
+int galois_b200_mul_mat_q4_0_f32_add(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
+                                     const galois_dim* xd, const float* res, const galois_dim* rd, float* dst,
+                                     const galois_dim* dd);
+
 /* Same op with the activation and result in HOST memory: upload x, run,
  * download dst, synchronise.  This is the sequence Tensor::from_vec(.., Gpu)
  * -> galois_matmul -> to_cpu_tensor (src/lib.rs:2467-2523, src/op.rs:3093,

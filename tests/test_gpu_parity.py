@@ -460,6 +460,18 @@ def test_two_op_fusions_are_bit_identical(gb, dev, oracle):
         gb.galois_silu_mul(xt, ut, y2)
         assert np.array_equal(y1.to_numpy(), y2.to_numpy())
         assert np.array_equal(y2.to_numpy(), O.mul(O.silu(x), u))
+    # mat-mul + residual: inside the GEMV at one activation row, two launches otherwise
+    for (n, k, b, seed) in [(4096, 4096, 1, 11), (4096, 11008, 1, 12), (1185, 512, 1, 13), (11008, 4096, 4, 14), (70, 96, 2, 15)]:
+        wq = O.quantize_q4_0(O.fill_normal(n * k, 900 + seed, 0, 0.02).reshape(n, k))
+        x = O.fill_normal(b * k, 910 + seed).reshape(b, k)
+        r = O.fill_normal(b * n, 920 + seed).reshape(b, n)
+        wt, xt, rt = _q4(gb, dev, wq, n, k), _gpu(gb, dev, x), _gpu(gb, dev, r)
+        y1, y2, t = (gb.Tensor.zeros((n, b), gb.GGmlType.F32, G) for _ in range(3))
+        gb.galois_matmul(wt, xt, t)
+        gb.galois_add(rt, t, y1)
+        gb.galois_matmul_add(wt, xt, rt, y2)
+        assert np.array_equal(y1.to_numpy(), y2.to_numpy())
+        assert_close(y2.to_numpy(), O.add(r, O.mul_mat_q4_0(wq, x)))
     # shape errors
     bad = gb.Tensor.zeros((8, 2), gb.GGmlType.F32, G)
     with pytest.raises(gb.GError) as ei:
