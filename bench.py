@@ -498,6 +498,46 @@ def run_ours(args):
         us_f = time_mm(28672, 8192, 16, 4)
         extra["config5_ffn70b_batch16"] = {"us": us_f, "hbm_gbs": algorithmic_bytes(28672, 8192, 16) / us_f / 1e3}
 
+    # ---- N > 1: the config-5 shapes (output head, 70B FFN; batch 16) row-sharded with the fused exchange
+    if peer_exchange and not args.no_extra:
+        from galois_b200.shard import PeerArena, PeerInbox, band_slots, inbox_bytes
+
+        extra = {}
+        xb16 = 16
+        c5 = [("config5_head_batch16", 32000, 4096, 6), ("config5_ffn70b_batch16", 28672, 8192, 4)]
+        slots5 = max(band_slots(n, world, xb16) for _, n, _, _ in c5)
+        arena5 = PeerArena(dev, inbox_bytes(world, slots5) + 4096)
+        inbox5 = PeerInbox(arena5, slots5)
+        for key, n, k, copies in c5:
+            r0, nr = shard_rows(n, world, rank)
+            wsb = [make_q4_0(nr, k, 35000 + c + 100 * rank, device) for c in range(copies)]
+            wdim = gb.Dim.ggml((k, nr), gb.GGmlType.Q4_0).c_struct()
+            xb = torch.randn(xb16, k, device=device, dtype=torch.float32)
+            yb = torch.zeros(xb16, n, device=device, dtype=torch.float32)
+            xd_, yd_ = gb.Dim.ggml((k, xb16), gb.GGmlType.F32).c_struct(), gb.Dim.ggml((n, xb16), gb.GGmlType.F32).c_struct()
+
+            def run5():
+                for wbuf in wsb:
+                    rc = lib.galois_b200_mul_mat_q4_0_f32_gather(ctx, C.c_void_p(wbuf.data_ptr()), C.byref(wdim), C.c_void_p(xb.data_ptr()),
+                                                                 C.byref(xd_), C.c_void_p(yb.data_ptr()), C.byref(yd_), r0,
+                                                                 C.byref(inbox5.peers), inbox5.next_epoch())
+                    if rc != 0:
+                        raise RuntimeError(f"mul_mat_q4_0 gather failed: {lib.galois_b200_last_error(ctx)} ({rc})")
+            for _ in range(5):
+                run5()
+            sync_all()
+            e0.record(stream)
+            for _ in range(20):
+                run5()
+            e1.record(stream)
+            sync_all()
+            t = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us5 = float(t.item()) * 1e3 / (20 * copies)
+            extra[key] = {"us": us5, "hbm_gbs": algorithmic_bytes(n, k, xb16) / us5 / 1e3, "rows_per_rank": nr}
+        dev.synchronize()
+        arena5.close()
+
     # ---- CPU baseline (rank 0, N = 1): the oracle's restatement of the reference CPU path, 4 tasks
     cpu = None
     if world == 1 and not args.no_cpu:

@@ -45,20 +45,39 @@ __device__ __forceinline__ void gb_gather_send(const gb_gather_args& G, int b, i
 // Thread `tid` of `nthreads` moves its share of the peers' packets of this epoch from the local
 // inbox into the full result.  Polls are bounded by the global timer; on time-out the thread
 // records GALOIS_B200_E_TIMEOUT in *status and stops.
-__device__ __forceinline__ void gb_gather_receive(const gb_gather_args& G, long long tid, long long nthreads, int* status) {
+__device__ __forceinline__ void gb_gather_receive(const gb_gather_args& G, long long tid, long long nthreads, int* status,
+                                                  int b_begin = 0, int b_count = -1) {
+    if (b_count < 0) b_count = G.B;  // default: all activation rows; a pass over rows [b_begin, b_begin + b_count) otherwise
+    constexpr int U = 4;             // packets a thread polls at the same time
     unsigned long long t0 = 0;
     for (int p = 0; p < G.P.nranks; p++) {
         if (p == G.P.rank) continue;
-        const uint64_t* area = G.P.inbox[G.P.rank] + ((long long)(G.epoch & 1u) * G.P.nranks + p) * G.P.slots;
         const int n_p = G.band_rows[p];
-        const long long total = (long long)G.B * n_p;
-        for (long long i = tid; i < total; i += nthreads) {
-            unsigned long long pkt;
+        const uint64_t* area = G.P.inbox[G.P.rank] + ((long long)(G.epoch & 1u) * G.P.nranks + p) * G.P.slots + (long long)b_begin * n_p;
+        float* out = G.dst_full + (long long)b_begin * G.nb1 + G.band_row0[p];
+        const long long total = (long long)b_count * n_p;
+        for (long long base = tid; base < total; base += nthreads * U) {
+            unsigned pending = 0;
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                if (base + u * nthreads < total) pending |= 1u << u;
             unsigned spins = 0;
-            for (;;) {
-                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(pkt) : "l"(area + i) : "memory");
-                if ((uint32_t)(pkt >> 32) == G.epoch) break;
-                if ((++spins & 255u) == 0) {
+            while (pending) {
+                unsigned long long pkt[U];
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (pending & (1u << u))
+                        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(pkt[u]) : "l"(area + base + u * nthreads) : "memory");
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    if ((pending & (1u << u)) && (uint32_t)(pkt[u] >> 32) == G.epoch) {
+                        const long long i = base + u * nthreads;
+                        const long long b = i / n_p, r = i - b * n_p;
+                        out[b * G.nb1 + r] = __uint_as_float((uint32_t)pkt[u]);
+                        pending &= ~(1u << u);
+                    }
+                }
+                if (pending && (++spins & 255u) == 0) {
                     const unsigned long long now = gb_globaltimer_ns();
                     if (t0 == 0) t0 = now;
                     if (now - t0 > GB_GATHER_WAIT_NS) {
@@ -67,8 +86,6 @@ __device__ __forceinline__ void gb_gather_receive(const gb_gather_args& G, long 
                     }
                 }
             }
-            const long long b = i / n_p, r = i - b * n_p;
-            G.dst_full[b * G.nb1 + G.band_row0[p] + r] = __uint_as_float((uint32_t)pkt);
         }
     }
 }

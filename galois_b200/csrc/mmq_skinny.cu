@@ -20,6 +20,7 @@
 //
 // Quantisation is bit-exact with <BlockQ8_0 as QuantType>::from_f32 (src/ggml_quants.rs:736-764).
 #include "common.cuh"
+#include "gather.cuh"
 #include "mmq_skinny.cuh"
 #include "ptx.cuh"
 
@@ -142,7 +143,8 @@ __device__ __forceinline__ void stage_mma(const uint8_t* ra, const uint8_t* rb, 
 template <int NT>
 __global__ void __launch_bounds__(SK_THREADS) mmq_skinny_kernel(const uint8_t* __restrict__ w, const uint2* __restrict__ qfrag,
                                                                 const float4* __restrict__ ds4, float* __restrict__ dst, long long nb1,
-                                                                int K, int N, int nbatch, int stages, int* __restrict__ status) {
+                                                                int K, int N, int nbatch, int stages, int* __restrict__ status,
+                                                                const gb_gather_args G, int b_begin) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -225,10 +227,16 @@ __global__ void __launch_bounds__(SK_THREADS) mmq_skinny_kernel(const uint8_t* _
 #pragma unroll
             for (int ww = 0; ww < SK_WARPS; ww++) v += col[ww * (NT * 128)];
             const int row = tile * SK_ROWS + r;
-            if (b < nbatch && row < N) dst[b * nb1 + row] = v;
+            if (b < nbatch && row < N) {
+                dst[b * nb1 + row] = v;
+                if (G.P.nranks) gb_gather_send(G, b_begin + b, row, v);  // sharded call: the band's rows go to every peer
+            }
         }
     }
     if (!ok && lane == 0) atomicExch(status, GALOIS_B200_E_TIMEOUT);
+    // sharded call: collect the peers' results for the activation rows of this pass
+    if (G.P.nranks > 0)
+        gb_gather_receive(G, (long long)blockIdx.x * SK_THREADS + threadIdx.x, (long long)gridDim.x * SK_THREADS, status, b_begin, nbatch);
 }
 
 struct skinny_plan {
@@ -287,7 +295,9 @@ size_t gb_mmq_skinny_scratch_bytes(const galois_dim* wd, const galois_dim* xd) {
 }
 
 int gb_mmq_skinny(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
-                  const galois_dim* dd, void* scratch) {
+                  const galois_dim* dd, void* scratch, const gb_gather_args* gather) {
+    gb_gather_args none = {};
+    const gb_gather_args& G = gather ? *gather : none;
     const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
     const int nblk = K / GB_QK;
     const uint8_t* wb = (const uint8_t*)w;
@@ -306,10 +316,10 @@ int gb_mmq_skinny(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, con
         GB_LAUNCHED(ctx, "quantize_q8_frag");
         if (p.nt == 1)
             gb_launch(ctx, mmq_skinny_kernel<1>, dim3((unsigned)p.grid), dim3(SK_THREADS), p.smem, wb, reinterpret_cast<const uint2*>(qfrag),
-                      reinterpret_cast<const float4*>(ds), dp, (long long)dd->nb[1], K, N, bc, p.stages, ctx->dev_status);
+                      reinterpret_cast<const float4*>(ds), dp, (long long)dd->nb[1], K, N, bc, p.stages, ctx->dev_status, G, b0);
         else
             gb_launch(ctx, mmq_skinny_kernel<2>, dim3((unsigned)p.grid), dim3(SK_THREADS), p.smem, wb, reinterpret_cast<const uint2*>(qfrag),
-                      reinterpret_cast<const float4*>(ds), dp, (long long)dd->nb[1], K, N, bc, p.stages, ctx->dev_status);
+                      reinterpret_cast<const float4*>(ds), dp, (long long)dd->nb[1], K, N, bc, p.stages, ctx->dev_status, G, b0);
         GB_LAUNCHED(ctx, "mmq_skinny");
     }
     return 0;

@@ -1,6 +1,7 @@
 // Internal interface of the skinny (2..96 activation rows) Q4_0 mat-mul on mma.sync (mmq_skinny.cu).
 #pragma once
 #include "common.cuh"
+#include "gather.cuh"
 
 // 16 activation rows per pass over the weights; up to 6 passes before the tcgen05 GEMM takes over.
 constexpr int GB_SKINNY_MAX_BATCH = 96;
@@ -16,5 +17,8 @@ bool gb_mmq_skinny_supported(const galois_b200_ctx* ctx, const void* w, const ga
 // Bytes of scratch the two launches share (the quantised activations in fragment order).
 size_t gb_mmq_skinny_scratch_bytes(const galois_dim* wd, const galois_dim* xd);
 // Two launches per 16 activation rows: the fragment-order Q8_0 quantiser, then the mat-mul.
+// `gather` (optional): the call computes one band of a row-sharded mat-mul; `dst` points at the
+// band's first row inside this rank's full result, every result also goes to the peers' inboxes and
+// each pass's tail receives the peers' rows (protocol of gather.cuh).
 int gb_mmq_skinny(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
-                  const galois_dim* dd, void* scratch);
+                  const galois_dim* dd, void* scratch, const gb_gather_args* gather = nullptr);
