@@ -565,7 +565,7 @@ def run_ours(args):
                        "launch": "cuda_graph" if use_graph else "stream",
                        "parallelism": (f"rows/{world} + " + ("packet exchange over NVLink peer memory fused into the mat-mul kernel" if peer_exchange else "nccl all_gather"))
                        if world > 1 else "single gpu"},
-            "roofline": {"bound": "hbm", "kernel": "gemv_q4_0_kernel" if B <= 1 else ("mmq_skinny_kernel" if B <= 96 else "mm_q4_0_tc_kernel"), "achieved": achieved, "peak": peak, "unit": UNIT,
+            "roofline": {"bound": "hbm", "kernel": "gemv_q4_0_kernel" if B <= 1 else ("mmq_skinny_kernel" if B <= 192 else "mm_q4_0_tc_kernel"), "achieved": achieved, "peak": peak, "unit": UNIT,
                          "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
                          "kernel_us": kernel_ms * 1e3, "algorithmic_bytes_per_launch": local_bytes_call,
                          "timed_launches": calls_step * args.steps, "launches_per_mat_mul": launches_step / calls_step,

@@ -281,6 +281,37 @@ int gb_validate_mul_mat(galois_b200_ctx* ctx, const void* w, const galois_dim* w
     return 0;
 }
 
+// Between 17 and 192 activation rows both the skinny kernel (one pass over the weights per 16 rows) and
+// the tcgen05 kernel (one 128 x 128 output tile per CTA, whole waves of CTAs) apply; the choice follows
+// a cost model fitted to measurements on a B200: a skinny pass costs max(6.8 us, weight bytes at
+// 1.6 TB/s) (passes after the first read the weights from L2), a wave of tensor-core tiles 0.68 us
+// per 32-element block of K.
+static bool skinny_beats_tc(const galois_b200_ctx* ctx, const galois_dim* wd, const galois_dim* xd) {
+    const double K = (double)wd->ne[0], N = (double)wd->ne[1], B = (double)xd->ne[1];
+    const double pass_us = fmax(6.8, N * (K / 32.0) * 18.0 / 1.6e6);
+    const double skinny_us = ceil(B / 16.0) * pass_us;
+    const double tiles = ceil(N / 128.0) * ceil(B / 128.0);
+    const double tc_us = ceil(tiles / (double)ctx->sm_count) * (K / 32.0) * 0.68;
+    return skinny_us <= tc_us;
+}
+
+// The kernel the automatic choice (or the forced variant) takes for this problem:
+// 1 = direct, 2 = streaming GEMV / wide-batch dp4a, 3 = tcgen05 GEMM, 4 = skinny mma.sync.
+int gb_choose_mul_mat_variant(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
+                              const galois_dim* dd) {
+    if (ctx->variant != 0) return ctx->variant;
+    const bool tc_ok = gb_mm_tc_supported(ctx, w, wd, x, xd, dd);
+    const bool gemv_ok = gb_gemv_supported(ctx, w, wd, x, xd, dd);
+    const bool bulk_ok = gb_mmv_bulk_supported(ctx, w, wd, xd, dd);
+    const bool skinny_ok = gb_mmq_skinny_supported(ctx, w, wd, x, xd, dd);
+    // one activation row: dp4a GEMV; 2..16 rows: mma.sync skinny kernel; 17..192: whichever the cost model
+    // prefers; more: tcgen05 GEMM
+    if (gemv_ok && xd->ne[1] < GB_SKINNY_MIN_BATCH) return 2;
+    if (skinny_ok && (!tc_ok || xd->ne[1] <= 16 || skinny_beats_tc(ctx, wd, xd))) return 4;
+    if (tc_ok && xd->ne[1] >= GB_TC_MIN_BATCH) return 3;
+    return (gemv_ok || bulk_ok) ? 2 : 1;
+}
+
 extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
                                             const galois_dim* xd, float* dst, const galois_dim* dd) {
     GB_CHECK_CTX(ctx);
@@ -300,15 +331,8 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
     const bool gemv_ok = gb_gemv_supported(ctx, w, wd, x, xd, dd);
     const bool bulk_ok = gb_mmv_bulk_supported(ctx, w, wd, xd, dd);
     const bool skinny_ok = gb_mmq_skinny_supported(ctx, w, wd, x, xd, dd);
-    int variant = ctx->variant;
-    if (variant == 0) {
-        // one activation row: dp4a GEMV; 2..96 rows: mma.sync skinny kernel; more: tcgen05 GEMM
-        if (gemv_ok && xd->ne[1] < GB_SKINNY_MIN_BATCH) variant = 2;
-        else if (skinny_ok) variant = 4;
-        else if (tc_ok && xd->ne[1] >= GB_TC_MIN_BATCH) variant = 3;
-        else variant = (gemv_ok || bulk_ok) ? 2 : 1;
-    }
-    if (variant == 4 && !skinny_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: skinny variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned operands, batch <= 96");
+    const int variant = gb_choose_mul_mat_variant(ctx, w, wd, x, xd, dd);
+    if (variant == 4 && !skinny_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: skinny variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned operands, batch <= 192");
     if (variant == 2 && !(gemv_ok || bulk_ok)) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: streaming variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned base, batch <= 8");
     if (variant == 3 && !tc_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: tensor-core variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned operands");
 

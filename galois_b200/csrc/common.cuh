@@ -52,6 +52,10 @@ int gb_scratch(galois_b200_ctx* ctx, size_t bytes, void** out);
 int gb_validate_mul_mat(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const void* x, const galois_dim* xd,
                         const void* dst, const galois_dim* dd);
 
+// The mat-mul kernel the dispatcher takes for this problem (1 direct, 2 streaming dp4a, 3 tcgen05, 4 skinny).
+int gb_choose_mul_mat_variant(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
+                              const galois_dim* dd);
+
 #define GB_CHECK_CTX(ctx)              \
     do {                               \
         if ((ctx) == nullptr) return GALOIS_B200_E_STATE; \

@@ -11,7 +11,7 @@
 // Polls are bounded by the global timer; when they run out the kernel records
 // GALOIS_B200_E_TIMEOUT in the context's status word and returns, so the context stays usable.
 //
-// The streaming GEMV (one activation row) and the skinny kernel (2..96 rows) do all of this inside
+// The streaming GEMV (one activation row) and the skinny kernel (2..192 rows) do all of this inside
 // their own launches; for the other mat-mul kernels a second, dependent launch sends the band and
 // receives the peers' bands.
 //
@@ -135,10 +135,11 @@ extern "C" int galois_b200_mul_mat_q4_0_f32_gather(galois_b200_ctx* ctx, const v
         rc = gb_validate_mul_mat(ctx, w_band, wd, x, xd, local, &band);
         if (rc != 0) return rc;
         // the same kernel choice as the unsharded entry point, so that sharded and unsharded results agree bit for bit
-        if (ctx->variant == 0 && wd->ne[0] > 0 && xd->ne[1] < GB_SKINNY_MIN_BATCH && gb_gemv_supported(ctx, w_band, wd, x, xd, &band))
+        const int variant = wd->ne[0] > 0 ? gb_choose_mul_mat_variant(ctx, w_band, wd, x, xd, &band) : 1;
+        if (variant == 2 && xd->ne[1] < GB_SKINNY_MIN_BATCH && gb_gemv_supported(ctx, w_band, wd, x, xd, &band))
             return gb_gemv_q4_0_gather(ctx, w_band, wd, x, xd, local, &band, &args, nullptr, 0);  // one kernel in all
-        if (ctx->variant == 0 && wd->ne[0] > 0 && gb_mmq_skinny_supported(ctx, w_band, wd, x, xd, &band)) {
-            // 2..96 activation rows: the skinny kernel sends and receives inside its own launches
+        if (variant == 4 && gb_mmq_skinny_supported(ctx, w_band, wd, x, xd, &band)) {
+            // 2..192 activation rows: the skinny kernel sends and receives inside its own launches
             void* scratch = nullptr;
             rc = gb_scratch(ctx, gb_mmq_skinny_scratch_bytes(wd, xd), &scratch);
             if (rc != 0) return rc;

@@ -1,4 +1,4 @@
-// Skinny Q4_0 x Q8_0 mat-mul for 2..16 activation rows: the weights stream once from HBM and the
+// Skinny Q4_0 x Q8_0 mat-mul for 2..16 activation rows per pass (up to 192 rows in passes of 16): the weights stream once from HBM and the
 // per-block integer dot products run on the warp-level int8 tensor-core instruction
 // (mma.sync m16n8k32, u8 x s8 -> s32), 16 weight rows x 8 activation rows x one 32-element block
 // per instruction.  The mat-mul stays HBM-bound work; the MMA only replaces the dp4a sequence
@@ -86,18 +86,17 @@ __global__ void __launch_bounds__(256) quantize_q8_frag_kernel(const float* __re
 }
 
 // One block of 16 weight rows (fragment words qa for row g, qb for row g + 8; scales dwa, dwb)
-// against NT n-tiles of activations.
+// against NT n-tiles of activations (fragments bf, {d, m} pairs sc of activation rows 2t, 2t + 1).
 template <int NT>
-__device__ __forceinline__ void block_mma(uint32_t qa, uint32_t qb, float dwa, float dwb, const uint2* __restrict__ qfrag,
-                                          const float4* __restrict__ ds4, int blk, int lane, float (&acc)[NT][4]) {
+__device__ __forceinline__ void block_mma(uint32_t qa, uint32_t qb, float dwa, float dwb, const uint2 (&bf)[NT], const float4 (&sc)[NT],
+                                          float (&acc)[NT][4]) {
     const uint32_t a0 = qa & 0x0F0F0F0Fu, a2 = (qa >> 4) & 0x0F0F0F0Fu;
     const uint32_t a1 = qb & 0x0F0F0F0Fu, a3 = (qb >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
-        const uint2 bf = __ldg(qfrag + ((long long)blk * NT + nt) * 32 + lane);
-        const float4 s = __ldg(ds4 + ((long long)blk * NT + nt) * 4 + (lane & 3));  // {d, m} of rows 2t, 2t + 1
+        const float4 s = sc[nt];
         int c[4];
-        mma_u8s8(c, a0, a1, a2, a3, bf.x, bf.y);
+        mma_u8s8(c, a0, a1, a2, a3, bf[nt].x, bf[nt].y);
         // float(isum) = float(c - 8 * sum q) through the 1.5 * 2^23 trick: exact for |isum| < 2^22
         const float f0 = __int_as_float(c[0] + __float_as_int(s.y)) - SK_MAGIC;
         const float f1 = __int_as_float(c[1] + __float_as_int(s.w)) - SK_MAGIC;
@@ -111,25 +110,50 @@ __device__ __forceinline__ void block_mma(uint32_t qa, uint32_t qb, float dwa, f
 }
 
 // NP block pairs of one stage: rows g and g + 8 of the tile (ra, rb) against the activations of
-// blocks blk0 .. blk0 + 2 NP - 1.  Fully unrolled so that the loads of later pairs overlap the
-// MMAs and scale arithmetic of earlier ones.
-template <int NT, int NP>
+// blocks blk0 .. blk0 + 2 NP - 1.  The activation operands come from global memory (L1 / L2); they
+// are loaded in groups of PF pairs, one group ahead of the MMAs that use them, so their latency is
+// paid once per group and overlaps the arithmetic of the group before.
+template <int NT, int NP, int PF>
 __device__ __forceinline__ void stage_mma(const uint8_t* ra, const uint8_t* rb, const uint2* __restrict__ qfrag,
                                           const float4* __restrict__ ds4, int blk0, int lane, float (&acc)[NT][4]) {
+    static_assert(NP % PF == 0, "whole groups");
     const int t = lane & 3;
+    uint2 bf[2][2 * PF][NT];
+    float4 sc[2][2 * PF][NT];
 #pragma unroll
-    for (int p = 0; p < NP; p++) {
-        // a block pair is nine aligned words: {d0 | qs0[0:2]}, qs0[2:14], {qs0[14:16] | d1}, qs1[0:16]
-        const uint32_t* ta = reinterpret_cast<const uint32_t*>(ra + p * 36);
-        const uint32_t* tb = reinterpret_cast<const uint32_t*>(rb + p * 36);
-        const uint32_t a_lo = ta[t], a_hi = ta[t + 1], a_1 = ta[5 + t];
-        const uint32_t b_lo = tb[t], b_hi = tb[t + 1], b_1 = tb[5 + t];
-        const float dwa0 = __half2float(*reinterpret_cast<const __half*>(ra + p * 36));
-        const float dwa1 = __half2float(*reinterpret_cast<const __half*>(ra + p * 36 + 18));
-        const float dwb0 = __half2float(*reinterpret_cast<const __half*>(rb + p * 36));
-        const float dwb1 = __half2float(*reinterpret_cast<const __half*>(rb + p * 36 + 18));
-        block_mma<NT>(__funnelshift_r(a_lo, a_hi, 16), __funnelshift_r(b_lo, b_hi, 16), dwa0, dwb0, qfrag, ds4, blk0 + 2 * p, lane, acc);
-        block_mma<NT>(a_1, b_1, dwa1, dwb1, qfrag, ds4, blk0 + 2 * p + 1, lane, acc);
+    for (int i = 0; i < 2 * PF; i++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            bf[0][i][nt] = __ldg(qfrag + ((long long)(blk0 + i) * NT + nt) * 32 + lane);
+            sc[0][i][nt] = __ldg(ds4 + ((long long)(blk0 + i) * NT + nt) * 4 + t);
+        }
+#pragma unroll
+    for (int grp = 0; grp < NP / PF; grp++) {
+        if (grp + 1 < NP / PF) {
+#pragma unroll
+            for (int i = 0; i < 2 * PF; i++)
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const int blk = blk0 + 2 * PF * (grp + 1) + i;
+                    bf[(grp + 1) & 1][i][nt] = __ldg(qfrag + ((long long)blk * NT + nt) * 32 + lane);
+                    sc[(grp + 1) & 1][i][nt] = __ldg(ds4 + ((long long)blk * NT + nt) * 4 + t);
+                }
+        }
+#pragma unroll
+        for (int q = 0; q < PF; q++) {
+            const int p = grp * PF + q;
+            // a block pair is nine aligned words: {d0 | qs0[0:2]}, qs0[2:14], {qs0[14:16] | d1}, qs1[0:16]
+            const uint32_t* ta = reinterpret_cast<const uint32_t*>(ra + p * 36);
+            const uint32_t* tb = reinterpret_cast<const uint32_t*>(rb + p * 36);
+            const uint32_t a_lo = ta[t], a_hi = ta[t + 1], a_1 = ta[5 + t];
+            const uint32_t b_lo = tb[t], b_hi = tb[t + 1], b_1 = tb[5 + t];
+            const float dwa0 = __half2float(*reinterpret_cast<const __half*>(ra + p * 36));
+            const float dwa1 = __half2float(*reinterpret_cast<const __half*>(ra + p * 36 + 18));
+            const float dwb0 = __half2float(*reinterpret_cast<const __half*>(rb + p * 36));
+            const float dwb1 = __half2float(*reinterpret_cast<const __half*>(rb + p * 36 + 18));
+            block_mma<NT>(__funnelshift_r(a_lo, a_hi, 16), __funnelshift_r(b_lo, b_hi, 16), dwa0, dwb0, bf[grp & 1][2 * q], sc[grp & 1][2 * q], acc);
+            block_mma<NT>(a_1, b_1, dwa1, dwb1, bf[grp & 1][2 * q + 1], sc[grp & 1][2 * q + 1], acc);
+        }
     }
 }
 
@@ -141,7 +165,7 @@ __device__ __forceinline__ void stage_mma(const uint8_t* ra, const uint8_t* rb, 
 // A warp's (tile, step) pairs form one sequence that its ring runs through without draining
 // between tiles.
 template <int NT>
-__global__ void __launch_bounds__(SK_THREADS) mmq_skinny_kernel(const uint8_t* __restrict__ w, const uint2* __restrict__ qfrag,
+__global__ void __launch_bounds__(SK_THREADS, 2) mmq_skinny_kernel(const uint8_t* __restrict__ w, const uint2* __restrict__ qfrag,
                                                                 const float4* __restrict__ ds4, float* __restrict__ dst, long long nb1,
                                                                 int K, int N, int nbatch, int stages, int* __restrict__ status,
                                                                 const gb_gather_args G, int b_begin) {
@@ -201,10 +225,11 @@ __global__ void __launch_bounds__(SK_THREADS) mmq_skinny_kernel(const uint8_t* _
             const int blocks = min(SK_KC, nblk - step * SK_KC);
             const uint8_t* ra = ring + (size_t)s * SK_STAGE_BYTES + g * SK_PITCH;
             const uint8_t* rb = ra + 8 * SK_PITCH;
+            constexpr int PF = NT == 1 ? 2 : 1;  // pairs per operand group: 48 registers of operands in flight either way
             if (blocks == SK_KC)
-                stage_mma<NT, SK_KC / 2>(ra, rb, qfrag, ds4, step * SK_KC, lane, acc);
+                stage_mma<NT, SK_KC / 2, PF>(ra, rb, qfrag, ds4, step * SK_KC, lane, acc);
             else  // K % 256 == 0: the ragged last step of a row is a whole number of 8 blocks
-                for (int p8 = 0; p8 < blocks / 8; p8++) stage_mma<NT, 4>(ra + p8 * 144, rb + p8 * 144, qfrag, ds4, step * SK_KC + 8 * p8, lane, acc);
+                for (int p8 = 0; p8 < blocks / 8; p8++) stage_mma<NT, 4, PF>(ra + p8 * 144, rb + p8 * 144, qfrag, ds4, step * SK_KC + 8 * p8, lane, acc);
             __syncwarp();  // every lane has consumed the stage: refill it
             if (idx + stages < total) issue(idx + stages, s);
         }

@@ -1,16 +1,17 @@
-// Internal interface of the skinny (2..96 activation rows) Q4_0 mat-mul on mma.sync (mmq_skinny.cu).
+// Internal interface of the skinny (2..192 activation rows) Q4_0 mat-mul on mma.sync (mmq_skinny.cu).
 #pragma once
 #include "common.cuh"
 #include "gather.cuh"
 
-// 16 activation rows per pass over the weights; up to 6 passes before the tcgen05 GEMM takes over.
-constexpr int GB_SKINNY_MAX_BATCH = 96;
+// 16 activation rows per pass over the weights; up to 12 passes before the tcgen05 GEMM takes over
+// (4096 x 4096: 28 us at 64 rows against 57 us there; the two meet near 200 rows).
+constexpr int GB_SKINNY_MAX_BATCH = 192;
 // The automatic choice uses this kernel from this many activation rows on (below it: the dp4a GEMV).
 constexpr int GB_SKINNY_MIN_BATCH = 2;
 
 // Sets the shared-memory limit of the kernel instances on the current device.
 int gb_mmq_skinny_init(galois_b200_ctx* ctx);
-// True for 2-D contiguous weights with K % 256 == 0 and a 16-byte aligned base, batch <= 96,
+// True for 2-D contiguous weights with K % 256 == 0 and a 16-byte aligned base, batch <= 192,
 // 16-byte aligned f32 activations.
 bool gb_mmq_skinny_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
                              const galois_dim* dd);

@@ -169,11 +169,11 @@ def test_mul_mat_q4_0_tensor_core(gb, dev, oracle, n, k, b):
     _mul_mat_case(gb, dev, oracle, n, k, b, 9500 + n + k + b, 3)
 
 
-# variant 4 = skinny mma.sync kernel (K % 256 == 0, batch <= 96 in passes of 16): config 2 at batch 4 / 8, config 5 at batch 16
+# variant 4 = skinny mma.sync kernel (K % 256 == 0, batch <= 192 in passes of 16): config 2 at batch 4 / 8, config 5 at batch 16
 @pytest.mark.parametrize("n,k,b", [(11008, 4096, 4), (4096, 11008, 8), (11008, 4096, 8), (4096, 11008, 4), (32000, 4096, 16),
                                    (16, 256, 2), (1, 256, 1), (17, 512, 3), (1185, 512, 9), (2371, 4096, 16), (149, 8192, 5),
                                    (300, 768, 12), (31, 1024, 7), (4096, 4096, 1), (500, 14336, 6), (15, 2048, 13), (4096, 4096, 37),
-                                   (200, 768, 96), (1000, 11008, 65)])
+                                   (200, 768, 96), (1000, 11008, 65), (128, 256, 192), (77, 512, 130)])
 def test_mul_mat_q4_0_skinny(gb, dev, oracle, n, k, b):
     _mul_mat_case(gb, dev, oracle, n, k, b, 9700 + n + k + b, 4)
 
