@@ -44,6 +44,11 @@ def ffn_shapes():
 
 
 # ----------------------------------------------------------------------------- synthetic data
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q4_0_kernel launch at config 2, batch 1 (ncu capture,
+# mean of the gate/up and down instances: 25 423 872 and 25 453 312 bytes read, 0 written)
+NCU_DRAM_BYTES_PER_LAUNCH = (2 * 25423872 + 25453312) / 3.0
+
+
 def make_q4_0(n: int, k: int, seed: int, device):
     """Seeded N(0, 0.02) weights quantised to Q4_0 blocks ({f16 d; 16 bytes of nibbles}; element
     j in the low nibble of byte j, element j+16 in the high nibble; value (q - 8) * d) with torch
@@ -566,7 +571,10 @@ def run_ours(args):
                        "parallelism": (f"rows/{world} + " + ("packet exchange over NVLink peer memory fused into the mat-mul kernel" if peer_exchange else "nccl all_gather"))
                        if world > 1 else "single gpu"},
             "roofline": {"bound": "hbm", "kernel": "gemv_q4_0_kernel" if B <= 1 else ("mmq_skinny_kernel" if B <= 192 else "mm_q4_0_tc_kernel"), "achieved": achieved, "peak": peak, "unit": UNIT,
-                         "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                         "frac": achieved / peak, "peak_kind": peak_kind,
+                         # DRAM bytes per launch from the ncu capture of this kernel on this workload (profiles/): read + write
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (B == 1 and world == 1) else None,
+                         "traffic_source": "ncu --set full capture summarised in profiles/gemv_q4_0_config2_batch1.md" if (B == 1 and world == 1) else None,
                          "kernel_us": kernel_ms * 1e3, "algorithmic_bytes_per_launch": local_bytes_call,
                          "timed_launches": calls_step * args.steps, "launches_per_mat_mul": launches_step / calls_step,
                          "isolated_kernel_us": isolated_ms * 1e3, "isolated_launches": cnt.value, "frac_of_8000_nominal": achieved / 8000.0},
