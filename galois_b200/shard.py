@@ -128,6 +128,14 @@ def inbox_bytes(world: int, slots: int) -> int:
     return 2 * world * int(slots) * 8
 
 
+def packet_slot(epoch: int, world: int, sender: int, slots: int, b: int, sender_rows: int, r: int) -> int:
+    """Index, in 8-byte packets from the start of a receiver's inbox, of the packet carrying result
+    (activation row b, row r of `sender`'s band) of call `epoch`: the inbox half alternates with the
+    epoch's parity, each half has one area of `slots` packets per sender, and inside an area packets
+    are ordered by activation row, then by row of the band (the layout `csrc/gather.cuh` uses)."""
+    return ((epoch & 1) * world + sender) * slots + b * sender_rows + r
+
+
 def band_slots(n_total: int, world: int, batch: int) -> int:
     """Packets the largest band of an N-row result sends per call."""
     return batch * max(shard_rows(n_total, world, r)[1] for r in range(world))

@@ -60,3 +60,50 @@ def test_row_sharded_gather(world, n, batch):
         assert p.exitcode == 0
     res = sorted(q.get(timeout=5) for _ in range(world))
     assert res == [(r, True) for r in range(world)]
+
+
+@pytest.mark.parametrize("world,n,batch", [(2, 4096, 1), (3, 1000, 4), (8, 11008, 8), (8, 96, 2), (4, 32000, 16)])
+def test_packet_inbox_layout(world, n, batch):
+    """CPU model of the fused exchange's inbox (all ranks in one process): every rank's packets of an
+    epoch land in slots that no other (sender, half) uses, fit the area sized by band_slots, and a
+    receiver that reads them back by the same arithmetic rebuilds the full [B][N] result; packets of
+    the previous epoch stay untouched in the other half."""
+    from galois_b200.shard import band_slots, inbox_bytes, packet_slot, shard_rows
+
+    slots = band_slots(n, world, batch)
+    assert inbox_bytes(world, slots) == 2 * world * slots * 8
+    bands = [shard_rows(n, world, r) for r in range(world)]
+    assert sum(nr for _, nr in bands) == n and all(r0 % 32 == 0 for r0, _ in bands)
+    rng = np.random.default_rng(world * 1000 + n + batch)
+    inbox = np.zeros((world, 2 * world * slots), np.uint64)  # [receiver][packet]
+    results = {}
+    for epoch in (1, 2, 3):
+        full = rng.standard_normal((batch, n)).astype(np.float32)
+        results[epoch] = full
+        for sender, (r0, nr) in enumerate(bands):
+            for b in range(batch):
+                idx = np.array([packet_slot(epoch, world, sender, slots, b, nr, r) for r in range(nr)], np.int64)
+                if nr:
+                    assert idx.max() < ((epoch & 1) * world + sender + 1) * slots  # stays inside its own area
+                pk = (np.uint64(epoch) << np.uint64(32)) | full[b, r0 : r0 + nr].view(np.uint32).astype(np.uint64)
+                for receiver in range(world):
+                    if receiver != sender:
+                        inbox[receiver, idx] = pk
+        for receiver in range(world):
+            got = np.full((batch, n), np.nan, np.float32)
+            got[:, bands[receiver][0] : bands[receiver][0] + bands[receiver][1]] = full[:, bands[receiver][0] : bands[receiver][0] + bands[receiver][1]]
+            for sender, (r0, nr) in enumerate(bands):
+                if sender == receiver:
+                    continue
+                for b in range(batch):
+                    idx = [packet_slot(epoch, world, sender, slots, b, nr, r) for r in range(nr)]
+                    pk = inbox[receiver, idx]
+                    assert np.all((pk >> np.uint64(32)) == epoch)
+                    got[b, r0 : r0 + nr] = (pk & np.uint64(0xFFFFFFFF)).astype(np.uint32).view(np.float32)
+            assert np.array_equal(got, full)
+        if epoch >= 2:
+            # the other half still holds the previous epoch's packets: a peer that is one call behind can read them
+            prev, (r0, nr) = epoch - 1, bands[0]
+            if nr and world > 1:
+                idx = [packet_slot(prev, world, 0, slots, 0, nr, r) for r in range(nr)]
+                assert np.all((inbox[1, idx] >> np.uint64(32)) == prev)
