@@ -12,6 +12,7 @@ from .op import (  # noqa: F401
     galois_cpy,
     galois_matmul,
     galois_matmul_add,
+    galois_matmul_fused,
     galois_mul,
     galois_rms_norm,
     galois_rms_norm_mul,

@@ -29,6 +29,12 @@ class GaloisPeers(C.Structure):
     _fields_ = [("rank", C.c_int32), ("nranks", C.c_int32), ("slots", C.c_int64), ("inbox", C.c_void_p * MAX_RANKS)]
 
 
+class GaloisPrologue(C.Structure):
+    """``galois_b200_prologue``: an op pair applied to the activations inside the fused mat-mul call."""
+
+    _fields_ = [("kind", C.c_int32), ("aux", C.c_void_p), ("eps", C.c_float)]
+
+
 _P, _F, _I, _I64, _SZ = C.c_void_p, C.c_float, C.c_int, C.c_int64, C.c_size_t
 _DP = C.POINTER(GaloisDim)
 
@@ -51,6 +57,7 @@ SIGNATURES = {
     "galois_b200_quantize_q8_0": ([_P, _P, _I64, _P, _I64, _I64], _I),
     "galois_b200_block_isums_q4_0_q8_0": ([_P, _P, _P, _I64, _P], _I),
     "galois_b200_mul_mat_q4_0_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
+    "galois_b200_mul_mat_q4_0_f32_fused": ([_P, _P, _DP, _P, _DP, C.POINTER(GaloisPrologue), _P, _DP, _P, _DP], _I),
     "galois_b200_mul_mat_q4_0_f32_add": ([_P, _P, _DP, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_mul_mat_q4_0_f32_host": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_mul_mat_q4_0_f32_static": ([_P, _P, _DP, _P, _DP, _P, _DP, C.c_char_p, _SZ], _I),

@@ -182,6 +182,7 @@ extern "C" int galois_b200_destroy(galois_b200_ctx* ctx) {
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->io) cudaFree(ctx->io);
+    if (ctx->tmp) cudaFree(ctx->tmp);
     if (ctx->prof_ev) {
         for (int i = 0; i < 2 * GB_PROF_MAX; i++)
             if (ctx->prof_ev[i]) cudaEventDestroy(ctx->prof_ev[i]);
@@ -370,27 +371,82 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
     return rc;
 }
 
+// A context-owned buffer for the intermediate of a fused call that has to run as separate ops.
+static int gb_tmp(galois_b200_ctx* ctx, size_t bytes, void** out) {
+    if (bytes > ctx->tmp_bytes) {
+        GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->tmp) GB_CUDA(ctx, cudaFree(ctx->tmp));
+        ctx->tmp = nullptr;
+        ctx->tmp_bytes = 0;
+        const size_t want = (bytes + (1u << 20) - 1) & ~(size_t)((1u << 20) - 1);
+        const cudaError_t e = cudaMalloc(&ctx->tmp, want);
+        if (e != cudaSuccess) return gb_fail(ctx, GALOIS_B200_E_NOMEM, "fused mat-mul: cannot allocate %zu bytes: %s", want, cudaGetErrorString(e));
+        ctx->tmp_bytes = want;
+    }
+    *out = ctx->tmp;
+    return 0;
+}
+
+extern "C" int galois_b200_mul_mat_q4_0_f32_fused(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
+                                                  const galois_dim* xd, const galois_b200_prologue* pro, const float* res,
+                                                  const galois_dim* rd, float* dst, const galois_dim* dd) {
+    GB_CHECK_CTX(ctx);
+    if (!dd) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_fused: null pointer");
+    const int kind = pro ? pro->kind : GALOIS_B200_PROLOGUE_NONE;
+    if (kind < GALOIS_B200_PROLOGUE_NONE || kind > GALOIS_B200_PROLOGUE_SILU_MUL)
+        return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_fused: unknown prologue %d", kind);
+    if (kind != GALOIS_B200_PROLOGUE_NONE && !pro->aux) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_fused: prologue without its second operand");
+    if (res) {
+        if (!rd) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_fused: null pointer");
+        if (!gb_same_shape(rd, dd)) return gb_fail(ctx, GALOIS_B200_E_SHAPE, "mul_mat_q4_0_fused: residual and dst shapes differ");
+        if (rd->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0_fused: residual rows must be contiguous");
+    }
+    int rc = gb_validate_mul_mat(ctx, w, wd, x, xd, dst, dd);
+    if (rc) return rc;
+    const int64_t K = wd->ne[0], nrows = xd->ne[1] * xd->ne[2] * xd->ne[3];
+    if (wd->ne[1] == 0 || nrows == 0) return 0;
+    // one activation row on the streaming GEMV: the prologue runs where the row is quantised and the sum
+    // with the residual is formed where the result is stored -- one launch for up to four ops
+    const bool aux_ok = kind == GALOIS_B200_PROLOGUE_NONE || ((uintptr_t)pro->aux % 16 == 0 && gb_gemv_has_prologue());
+    if (ctx->variant == 0 && K > 0 && xd->ne[1] < GB_SKINNY_MIN_BATCH && aux_ok && (!res || rd->nb[1] < (1ll << 30)) &&
+        gb_gemv_supported(ctx, w, wd, x, xd, dd)) {
+        gb_gather_args none = {};
+        gb_gemv_extra ex = {};
+        ex.res = res;
+        ex.res_nb1 = res ? rd->nb[1] : 0;
+        ex.pro_kind = kind;
+        ex.pro_aux = pro ? pro->aux : nullptr;
+        ex.pro_eps = pro ? pro->eps : 0.0f;
+        return gb_gemv_q4_0_gather(ctx, w, wd, x, xd, dst, dd, &none, &ex);
+    }
+    // any other shape: the ops one after the other, the prologue's result in a context-owned buffer
+    const float* xin = x;
+    galois_dim td = *xd;
+    if (kind != GALOIS_B200_PROLOGUE_NONE) {
+        void* tmp = nullptr;
+        td.nb[0] = 1, td.nb[1] = xd->ne[0], td.nb[2] = td.nb[1] * xd->ne[1], td.nb[3] = td.nb[2] * xd->ne[2];
+        rc = gb_tmp(ctx, (size_t)gb_nelements(xd) * sizeof(float), &tmp);
+        if (rc) return rc;
+        if (kind == GALOIS_B200_PROLOGUE_RMS_NORM_MUL) {
+            galois_dim gd = {1, {xd->ne[0], 1, 1, 1}, {1, xd->ne[0], xd->ne[0], xd->ne[0]}};
+            rc = galois_b200_rms_norm_mul_f32(ctx, x, xd, pro->aux, &gd, (float*)tmp, &td, pro->eps);
+        } else {
+            rc = galois_b200_silu_mul_f32(ctx, x, xd, pro->aux, xd, (float*)tmp, &td);
+        }
+        if (rc) return rc;
+        xin = (const float*)tmp;
+    }
+    rc = galois_b200_mul_mat_q4_0_f32(ctx, w, wd, xin, &td, dst, dd);
+    if (rc || !res) return rc;
+    return galois_b200_add_f32(ctx, res, rd, dst, dd, dst, dd);  // Add::f needs a contiguous dst; it may alias src1
+}
+
 extern "C" int galois_b200_mul_mat_q4_0_f32_add(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
                                                 const galois_dim* xd, const float* res, const galois_dim* rd, float* dst,
                                                 const galois_dim* dd) {
     GB_CHECK_CTX(ctx);
-    if (!res || !rd || !dd) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_add: null pointer");
-    if (!gb_same_shape(rd, dd)) return gb_fail(ctx, GALOIS_B200_E_SHAPE, "mul_mat_q4_0_add: residual and dst shapes differ");
-    if (rd->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0_add: residual rows must be contiguous");
-    int rc = gb_validate_mul_mat(ctx, w, wd, x, xd, dst, dd);
-    if (rc) return rc;
-    const int64_t nrows = xd->ne[1] * xd->ne[2] * xd->ne[3];
-    if (wd->ne[1] == 0 || nrows == 0) return 0;
-    // one activation row on the streaming GEMV: the sum is formed where the result is stored
-    if (ctx->variant == 0 && wd->ne[0] > 0 && xd->ne[1] < GB_SKINNY_MIN_BATCH && rd->nb[1] < (1ll << 30) &&
-        gb_gemv_supported(ctx, w, wd, x, xd, dd)) {
-        gb_gather_args none = {};
-        return gb_gemv_q4_0_gather(ctx, w, wd, x, xd, dst, dd, &none, res, rd->nb[1]);
-    }
-    // any other shape: the two ops one after the other (Add::f needs a contiguous dst; it may alias src1)
-    rc = galois_b200_mul_mat_q4_0_f32(ctx, w, wd, x, xd, dst, dd);
-    if (rc) return rc;
-    return galois_b200_add_f32(ctx, res, rd, dst, dd, dst, dd);
+    if (!res || !rd) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_add: null pointer");
+    return galois_b200_mul_mat_q4_0_f32_fused(ctx, w, wd, x, xd, nullptr, res, rd, dst, dd);
 }
 
 extern "C" int galois_b200_set_pdl(galois_b200_ctx* ctx, int on) {

@@ -39,6 +39,9 @@ struct galois_b200_ctx {
     // device staging for the entry points that take host buffers
     void* io;
     size_t io_bytes;
+    // intermediate of a fused call that runs as separate ops
+    void* tmp;
+    size_t tmp_bytes;
     char err[512];
 };
 
@@ -131,6 +134,31 @@ __device__ __forceinline__ float gb_warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
+}
+
+// rms_norm's sum of squares over xr[0, n) in ONE fixed order, shared by every kernel that forms
+// the scale (the rms_norm kernels and the mat-mul that applies rms_norm to its own input), so that
+// they agree bit for bit: thread t of exactly 128 adds elements t, t + 128, ... with fmaf, lanes are
+// combined by xor-shuffles (16, 8, 4, 2, 1) and the four warp sums as ((w0 + w1) + w2) + w3.
+// Every thread of the 128 calls it (it synchronises the block) and receives the sum.
+// `red`: at least 4 floats of shared memory.
+__device__ __forceinline__ float gb_row_sumsq_128(const float* __restrict__ xr, int64_t n, float* red) {
+    float s = 0.0f;
+    for (int64_t i = threadIdx.x; i < n; i += 128) {
+        const float v = xr[i];
+        s = fmaf(v, v, s);
+    }
+    s = gb_warp_sum(s);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    const float t = ((red[0] + red[1]) + red[2]) + red[3];
+    __syncthreads();
+    return t;
+}
+// f32::rms_norm's scale (src/lib.rs:594-604 of galois): 1 / sqrt(sum / K + eps), each step rounded.
+__device__ __forceinline__ float gb_rms_scale(float sumsq, int64_t K, float eps) {
+    const float mean = __fdiv_rn(sumsq, (float)K);
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
 }
 
 #endif  // __CUDACC__

@@ -137,7 +137,7 @@ extern "C" int galois_b200_mul_mat_q4_0_f32_gather(galois_b200_ctx* ctx, const v
         // the same kernel choice as the unsharded entry point, so that sharded and unsharded results agree bit for bit
         const int variant = wd->ne[0] > 0 ? gb_choose_mul_mat_variant(ctx, w_band, wd, x, xd, &band) : 1;
         if (variant == 2 && xd->ne[1] < GB_SKINNY_MIN_BATCH && gb_gemv_supported(ctx, w_band, wd, x, xd, &band))
-            return gb_gemv_q4_0_gather(ctx, w_band, wd, x, xd, local, &band, &args, nullptr, 0);  // one kernel in all
+            return gb_gemv_q4_0_gather(ctx, w_band, wd, x, xd, local, &band, &args, nullptr);  // one kernel in all
         if (variant == 4 && gb_mmq_skinny_supported(ctx, w_band, wd, x, xd, &band)) {
             // 2..192 activation rows: the skinny kernel sends and receives inside its own launches
             void* scratch = nullptr;

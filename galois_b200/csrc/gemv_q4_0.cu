@@ -33,7 +33,8 @@ namespace {
 constexpr int GEMV_WARPS = GB_GEMV_WARPS;
 constexpr int GEMV_THREADS = GEMV_WARPS * 32;
 constexpr int GEMV_MAX_STAGES = 6;
-constexpr int GEMV_BAR_BYTES = ((GEMV_WARPS * GEMV_MAX_STAGES + 1) * 8 + 127) & ~127;  // the mbarriers, padded
+constexpr int GEMV_BAR_BYTES = ((GEMV_WARPS * GEMV_MAX_STAGES + 1) * 8 + 16 + 127) & ~127;  // the mbarriers + 4 floats, padded
+constexpr int GEMV_RED_OFFSET = (GEMV_WARPS * GEMV_MAX_STAGES + 1) * 8;  // 4 floats of block-reduction space behind the barriers
 
 // One 36-byte block pair held as nine aligned words t[0..8] ({d0 | qs0[0:2]}, qs0[2:14],
 // {qs0[14:16] | d1}, qs1[0:16]) against the 64 int8 activations y[0..15] of the same two blocks.
@@ -101,10 +102,37 @@ __device__ __forceinline__ void load_act(const uint8_t* qs, const uint8_t* ds, i
 // asynchronously into the activation area of all `csize` CTAs (this one included), each store
 // counting its bytes on the destination's `act_bar`, in the piece-major layout:
 // row b's quants at act_qs + b * K, its {d, -8 * sum} pairs at act_ds + b * (K/32) * 8.
+// `pro` (one activation row only) applies an op pair to the row on the way in, with the roundings of the
+// separate ops: kind 1 = rms_norm then mul by a gain row, (x * scale) * gain; kind 2 = silu then mul,
+// silu(x) * aux through the f16 table of f32::vec_silu (src/lib.rs:543-549 of galois).
+struct gemv_prologue {
+    int kind;               // 0 = none
+    const float* aux;       // gain row (kind 1) or the second operand, laid out like x (kind 2)
+    float scale;            // kind 1: rms_norm's scale of this row
+    const uint16_t* lut;    // kind 2: silu table
+};
+
+__device__ __forceinline__ float4 apply_prologue(const gemv_prologue& pro, float4 v, size_t elem) {
+    if (pro.kind == 1) {
+        const float4 g = __ldg(reinterpret_cast<const float4*>(pro.aux + elem));
+        v.x = __fmul_rn(__fmul_rn(v.x, pro.scale), g.x);
+        v.y = __fmul_rn(__fmul_rn(v.y, pro.scale), g.y);
+        v.z = __fmul_rn(__fmul_rn(v.z, pro.scale), g.z);
+        v.w = __fmul_rn(__fmul_rn(v.w, pro.scale), g.w);
+    } else if (pro.kind == 2) {
+        const float4 u = __ldg(reinterpret_cast<const float4*>(pro.aux + elem));
+        v.x = __fmul_rn(__half2float(__ushort_as_half(__ldg(pro.lut + __half_as_ushort(__float2half_rn(v.x))))), u.x);
+        v.y = __fmul_rn(__half2float(__ushort_as_half(__ldg(pro.lut + __half_as_ushort(__float2half_rn(v.y))))), u.y);
+        v.z = __fmul_rn(__half2float(__ushort_as_half(__ldg(pro.lut + __half_as_ushort(__float2half_rn(v.z))))), u.z);
+        v.w = __fmul_rn(__half2float(__ushort_as_half(__ldg(pro.lut + __half_as_ushort(__float2half_rn(v.w))))), u.w);
+    }
+    return v;
+}
+
 template <int SEG>
 __device__ __forceinline__ void quantize_rows_cluster(const float* __restrict__ x, int x_stride, int K, int nbatch, int NB,
                                                       uint8_t* act_qs, uint8_t* act_ds, int nsegk, uint32_t crank, uint32_t csize,
-                                                      uint64_t* act_bar) {
+                                                      uint64_t* act_bar, const gemv_prologue& pro) {
     const int nblk = K >> 5;
     const int total = NB * nblk;
     const int per = (total + (int)csize - 1) / (int)csize;
@@ -124,7 +152,10 @@ __device__ __forceinline__ void quantize_rows_cluster(const float* __restrict__ 
             v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (g < last) {
                 const int b = g / nblk, blk = g - b * nblk;
-                if (b < nbatch) v[u] = __ldg(reinterpret_cast<const float4*>(x + (size_t)b * x_stride + blk * 32) + sub);
+                if (b < nbatch) {
+                    const size_t elem = (size_t)b * x_stride + blk * 32 + sub * 4;
+                    v[u] = apply_prologue(pro, __ldg(reinterpret_cast<const float4*>(x + elem)), elem);
+                }
             }
         }
 #pragma unroll
@@ -176,7 +207,8 @@ __device__ __forceinline__ void quantize_rows_cluster(const float* __restrict__ 
 template <int NB, int SEG, bool SPLIT, int NPASS>
 __global__ void __launch_bounds__(GEMV_THREADS)
     gemv_q4_0_kernel(const uint8_t* __restrict__ w, const float* __restrict__ x, int x_stride, float* __restrict__ dst, int nb1, int K, int N, int nbatch, int stages,
-                     int* __restrict__ status, const gb_gather_args G, const float* __restrict__ res, int res_nb1) {
+                     int* __restrict__ status, const gb_gather_args G, const float* __restrict__ res, int res_nb1,
+                     int pro_kind, const float* __restrict__ pro_aux, float pro_eps, const uint16_t* __restrict__ silu_lut) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents();
 
@@ -224,7 +256,13 @@ __global__ void __launch_bounds__(GEMV_THREADS)
     cluster_arrive_relaxed();  // this CTA's shared memory and act_bar exist
     pdl_wait();                // the activations (and whatever dst aliases) belong to the preceding kernels
     cluster_wait();            // so do every peer's
-    quantize_rows_cluster<SEG>(x, x_stride, K, nbatch, NB, act_qs, act_ds, nsegk, crank, csize, act_bar);
+    gemv_prologue pro = {pro_kind, pro_aux, 1.0f, silu_lut};
+    if (NB == 1 && GEMV_THREADS == 128 && pro_kind == 1) {
+        // rms_norm's scale of the row, every CTA for itself (the row is a few KB and sits in L2), in the
+        // summation order the rms_norm kernels use
+        pro.scale = gb_rms_scale(gb_row_sumsq_128(x, K, reinterpret_cast<float*>(smem + GEMV_RED_OFFSET)), K, pro_eps);
+    }
+    quantize_rows_cluster<SEG>(x, x_stride, K, nbatch, NB, act_qs, act_ds, nsegk, crank, csize, act_bar, pro);
     bool ok = mbar_wait_bounded(act_bar, 0);  // all slices of the quantised activations have landed here
 
     int yh[HOIST ? NPASS : 1][HOIST ? 16 * SEG : 1];
@@ -395,7 +433,7 @@ cudaError_t gemv_attr() {
 
 template <int NB, int SEG, bool SPLIT, int NPASS>
 int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, const float* x, int x_stride, float* dst, int nb1,
-                int K, int N, int B, const gb_gather_args& gather, const float* res, int res_nb1) {
+                int K, int N, int B, const gb_gather_args& gather, const gb_gemv_extra& ex) {
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute at[2];
     int na = 0;
@@ -416,7 +454,8 @@ int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, cons
     cfg.blockDim = dim3(GEMV_THREADS);
     cfg.dynamicSmemBytes = p.smem;
     GB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_0_kernel<NB, SEG, SPLIT, NPASS>, w, x, x_stride, dst, nb1, K, N, B, p.stages,
-                                    ctx->dev_status, gather, res, res_nb1));
+                                    ctx->dev_status, gather, ex.res, (int)ex.res_nb1, ex.pro_kind, ex.pro_aux, ex.pro_eps,
+                                    ctx->silu_lut));
     ctx->launches++;
     return 0;
 }
@@ -429,6 +468,8 @@ int gb_gemv_init(galois_b200_ctx* ctx) {
 #undef X
     return 0;
 }
+
+bool gb_gemv_has_prologue() { return GEMV_THREADS == 128; }
 
 bool gb_gemv_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
                        const galois_dim* dd) {
@@ -446,11 +487,13 @@ bool gb_gemv_supported(const galois_b200_ctx* ctx, const void* w, const galois_d
 int gb_gemv_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
                  const galois_dim* dd) {
     gb_gather_args none = {};
-    return gb_gemv_q4_0_gather(ctx, w, wd, x, xd, dst, dd, &none, nullptr, 0);
+    return gb_gemv_q4_0_gather(ctx, w, wd, x, xd, dst, dd, &none, nullptr);
 }
 
 int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
-                        const galois_dim* dd, const gb_gather_args* gather, const float* res, int64_t res_nb1) {
+                        const galois_dim* dd, const gb_gather_args* gather, const gb_gemv_extra* extra) {
+    gb_gemv_extra ex = {};
+    if (extra) ex = *extra;
     const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
     const gemv_plan p = plan_gemv(ctx, K, N, B);
     if (!p.ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: shape not supported by the streaming GEMV");
@@ -458,7 +501,7 @@ int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* w
     const int nb1 = (int)dd->nb[1], xs = (int)xd->nb[1];
 #define X(NB_, SEG_, SPLIT_, NP_)                                                   \
     if (p.nbt == NB_ && p.seg == SEG_ && p.split == SPLIT_ && p.npass == NP_)       \
-        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, x, xs, dst, nb1, K, N, B, *gather, res, (int)res_nb1);
+        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, x, xs, dst, nb1, K, N, B, *gather, ex);
     GB_GEMV_INSTANCES(X)
 #undef X
     return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: no streaming-GEMV instance for this shape");

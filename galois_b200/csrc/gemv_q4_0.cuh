@@ -16,7 +16,18 @@ int gb_gemv_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, cons
 // The same launch for one band of a row-sharded mat-mul: `dst` points at the band's first row
 // inside this rank's full result (gather->P.nranks == 0: not sharded).  Each result also goes to
 // every peer's inbox and the kernel's tail receives the peers' bands (protocol of gather.cuh).
-// `res` (optional, same shape as dst, row stride res_nb1): dst = res + mat-mul result, the sum
-// rounded once as Add::f rounds it.
+// `extra` (optional): a residual `res` of the shape of dst (row stride res_nb1): dst = res + mat-mul
+// result, the sum rounded once as Add::f rounds it; and, for one activation row, an op pair applied
+// to the row before it is quantised (pro_kind 1: rms_norm with `pro_eps` then mul by the gain row
+// `pro_aux`; 2: silu then mul by `pro_aux`, laid out like x), rounded as the separate ops round.
+struct gb_gemv_extra {
+    const float* res;
+    int64_t res_nb1;
+    int pro_kind;
+    const float* pro_aux;
+    float pro_eps;
+};
 int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
-                        const galois_dim* dd, const gb_gather_args* gather, const float* res, int64_t res_nb1);
+                        const galois_dim* dd, const gb_gather_args* gather, const gb_gemv_extra* extra);
+// True when the GEMV was built with the 128-thread CTAs the in-kernel rms_norm needs.
+bool gb_gemv_has_prologue();

@@ -48,20 +48,13 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, int64_t xb1, int64_
                                 const float* __restrict__ w, int64_t wb1, int64_t wb2, int64_t wb3, int64_t we1, int64_t we2,
                                 int64_t we3) {
     gb_pdl_entry();
-    __shared__ float red[33];
+    __shared__ float red[4];
     const int64_t r = blockIdx.x;
     const int64_t i1 = r % ne1, i2 = (r / ne1) % ne2, i3 = r / (ne1 * ne2);
     const float* xr = x + i1 * xb1 + i2 * xb2 + i3 * xb3;
     float* yr = y + i1 * yb1 + i2 * yb2 + i3 * yb3;
-    const int64_t n32 = K & ~(int64_t)31;
-    float s = 0.0f;
-    for (int64_t i = threadIdx.x; i < n32; i += blockDim.x) {
-        const float v = xr[i];
-        s = fmaf(v, v, s);
-    }
-    s = block_sum(s, red);
-    const float mean = __fdiv_rn(s, (float)K);
-    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    // 128 threads per row: the summation order of gb_row_sumsq_128 is part of the op's definition here
+    const float scale = gb_rms_scale(gb_row_sumsq_128(xr, K & ~(int64_t)31, red), K, eps);
     if (w == nullptr) {
         for (int64_t i = threadIdx.x; i < K; i += blockDim.x) yr[i] = __fmul_rn(xr[i], scale);
     } else {
@@ -251,7 +244,7 @@ extern "C" int galois_b200_rms_norm_f32(galois_b200_ctx* ctx, const float* x, co
     if (xd->nb[0] != 1 || yd->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "rms_norm: rows must be contiguous");
     const int64_t K = xd->ne[0], nr = xd->ne[1] * xd->ne[2] * xd->ne[3];
     if (K == 0 || nr == 0) return 0;
-    gb_launch(ctx, rms_norm_kernel, dim3((unsigned)nr), dim3(row_threads(K)), 0, x, xd->nb[1], xd->nb[2], xd->nb[3], y, yd->nb[1],
+    gb_launch(ctx, rms_norm_kernel, dim3((unsigned)nr), dim3(128), 0, x, xd->nb[1], xd->nb[2], xd->nb[3], y, yd->nb[1],
               yd->nb[2], yd->nb[3], K, xd->ne[1], xd->ne[2], eps, (const float*)nullptr, (int64_t)0, (int64_t)0, (int64_t)0, (int64_t)1,
               (int64_t)1, (int64_t)1);
     GB_LAUNCHED(ctx, "rms_norm");
@@ -268,7 +261,7 @@ extern "C" int galois_b200_rms_norm_mul_f32(galois_b200_ctx* ctx, const float* x
         return gb_fail(ctx, GALOIS_B200_E_SHAPE, "rms_norm_mul: gain row shorter than src row");
     const int64_t K = xd->ne[0], nr = xd->ne[1] * xd->ne[2] * xd->ne[3];
     if (K == 0 || nr == 0) return 0;
-    gb_launch(ctx, rms_norm_kernel, dim3((unsigned)nr), dim3(row_threads(K)), 0, x, xd->nb[1], xd->nb[2], xd->nb[3], y, yd->nb[1],
+    gb_launch(ctx, rms_norm_kernel, dim3((unsigned)nr), dim3(128), 0, x, xd->nb[1], xd->nb[2], xd->nb[3], y, yd->nb[1],
               yd->nb[2], yd->nb[3], K, xd->ne[1], xd->ne[2], eps, w, wd->nb[1], wd->nb[2], wd->nb[3], wd->ne[1], wd->ne[2], wd->ne[3]);
     GB_LAUNCHED(ctx, "rms_norm_mul");
     return 0;

@@ -17,7 +17,7 @@ from dataclasses import dataclass
 
 import numpy as np
 
-from .op import (RopeCustomOption, UnaryOp, galois_add, galois_cpy, galois_matmul, galois_matmul_add, galois_mul, galois_rms_norm,
+from .op import (RopeCustomOption, UnaryOp, galois_add, galois_cpy, galois_matmul, galois_matmul_add, galois_matmul_fused, galois_mul, galois_rms_norm,
                  galois_rms_norm_mul, galois_rope_custom, galois_silu_mul, galois_soft_max_ext, galois_unary)
 from .tensor import Device, GGmlType, Tensor
 
@@ -47,11 +47,11 @@ class DecodeLayer:
     enqueues the kernels of one token on the device's stream and returns the output tensor.
 
     ``fused=False``: the op-by-op sequence a galois caller writes, 22 kernels.
-    ``fused=True`` : the same arithmetic in 13 kernels.  The rows of Wq, Wk, Wv (and of W_gate,
+    ``fused=True`` : the same arithmetic in 10 kernels.  The rows of Wq, Wk, Wv (and of W_gate,
     W_up) are stacked into one Q4_0 weight at upload, so the three (two) projections of the same
     input are one mat-mul whose result is split by views; rope runs once over the 2 x heads rows of
-    q and k; rms_norm + gain, silu + gate product and mat-mul + residual use the two-op fusions of
-    the library.  Rows
+    q and k; rms_norm + gain and silu + gate product run inside the mat-mul that consumes them, the
+    residual sums inside the mat-mul that produces their other operand (``galois_matmul_fused``).  Rows
     of a mat-mul are independent and the fusions round like the op pairs, so both variants give
     the same numbers bit for bit."""
 
@@ -136,8 +136,8 @@ class DecodeLayer:
         s = self.shape
         hd, nh, ctx, H = s.head_dim, s.heads, s.ctx, s.hidden
         # attention block
-        galois_rms_norm_mul(x, self.attn_norm, self.h, s.eps)
-        galois_matmul(self.w["wqkv"], self.h, self.qkv)  # rows [0, H) = q, [H, 2H) = k, [2H, 3H) = v
+        # rms_norm + gain run where the GEMV quantises its input; rows [0, H) = q, [H, 2H) = k, [2H, 3H) = v
+        galois_matmul_fused(self.w["wqkv"], x, self.qkv, rms_gain=self.attn_norm, eps=s.eps)
         qk3 = self.qkv.view((hd, 2 * nh, 1), (1, hd, hd * 2 * nh, hd * 2 * nh))
         galois_rope_custom(self.rope, qk3, pos, self.qkr)  # heads 0..nh-1 of q, then of k
         k_src = self.qkr.view((hd, 1, nh), (1, hd, hd, hd * nh), offset=H)
@@ -155,12 +155,11 @@ class DecodeLayer:
         ctx_flat = self.ctxv.view((H, 1), (1, H, H, H))
         galois_matmul_add(self.w["wo"], ctx_flat, x, self.x2)  # x2 = x + Wo ctx
         # feed-forward block (SwiGLU)
-        galois_rms_norm_mul(self.x2, self.ffn_norm, self.h2, s.eps)
-        galois_matmul(self.w["w_gate_up"], self.h2, self.gu)  # rows [0, ffn) = gate, [ffn, 2 ffn) = up
+        # rows [0, ffn) = gate, [ffn, 2 ffn) = up
+        galois_matmul_fused(self.w["w_gate_up"], self.x2, self.gu, rms_gain=self.ffn_norm, eps=s.eps)
         g = self.gu.view((s.ffn, 1), (1, s.ffn, s.ffn, s.ffn))
         u = self.gu.view((s.ffn, 1), (1, s.ffn, s.ffn, s.ffn), offset=s.ffn)
-        galois_silu_mul(g, u, self.a)
-        galois_matmul_add(self.w["w_down"], self.a, self.x2, self.out)  # out = x2 + Wdown a
+        galois_matmul_fused(self.w["w_down"], g, self.out, silu_mul=u, res=self.x2)  # out = x2 + Wdown (silu(g) * u)
         return self.out
 
     def algorithmic_bytes(self) -> int:

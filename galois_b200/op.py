@@ -103,6 +103,37 @@ def galois_matmul_add(src0: Tensor, src1: Tensor, res: Tensor, dst: Tensor) -> N
     _check(ctx, rc, "galois_matmul_add")
 
 
+def galois_matmul_fused(src0: Tensor, src1: Tensor, dst: Tensor, *, rms_gain: Tensor | None = None, eps: float = 0.0,
+                        silu_mul: Tensor | None = None, res: Tensor | None = None) -> None:
+    """Up to four reference ops in one call, bit-identical to running them one after the other:
+    [galois_rms_norm(src1, eps) then galois_mul by `rms_gain`  |  galois_unary(Silu)(src1) then galois_mul by
+    `silu_mul`] -> galois_matmul(src0, .) -> [galois_add(res, .)] (src/op.rs:3155-3169, 3113-3127, 3232-3256,
+    3093-3111, 3073-3091).  Not part of the reference API."""
+    from ._lib import GaloisPrologue
+
+    if rms_gain is not None and silu_mul is not None:
+        raise GError("galois_matmul_fused: one prologue at most")
+    ops = [t for t in (src0, src1, dst, rms_gain, silu_mul, res) if t is not None]
+    ctx = _gpu_ctx(*ops)
+    _want(src0, GGmlType.Q4_0, "galois_matmul_fused src0")
+    for t in ops[1:]:
+        _want(t, GGmlType.F32, "galois_matmul_fused")
+    pro = GaloisPrologue()
+    if rms_gain is not None:
+        if rms_gain.dim().shape[0] < src1.dim().shape[0]:
+            raise GError("galois_matmul_fused: gain row shorter than the activation row")
+        pro.kind, pro.aux, pro.eps = 1, rms_gain.data_ptr(), eps
+    elif silu_mul is not None:
+        if tuple(silu_mul.dim().shape) != tuple(src1.dim().shape) or tuple(silu_mul.dim().stride) != tuple(src1.dim().stride):
+            raise GError("galois_matmul_fused: the silu product's second operand must be laid out like src1")
+        pro.kind, pro.aux, pro.eps = 2, silu_mul.data_ptr(), 0.0
+    import ctypes as C
+
+    rc = lib.galois_b200_mul_mat_q4_0_f32_fused(ctx, _p(src0), _d(src0), _p(src1), _d(src1), C.byref(pro), _p(res) if res is not None else None,
+                                                _d(res) if res is not None else None, _p(dst), _d(dst))
+    _check(ctx, rc, "galois_matmul_fused")
+
+
 def galois_rms_norm_mul(src: Tensor, gain: Tensor, dst: Tensor, eps: float) -> None:
     """galois_rms_norm (src/op.rs:3155-3169) followed by galois_mul with `gain` (src/op.rs:3113-3127) in one
     launch; bit-identical to the two calls.  Not part of the reference API."""

@@ -132,12 +132,31 @@ int galois_b200_block_isums_q4_0_q8_0(galois_b200_ctx* ctx, const void* w, const
 int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
                                  const galois_dim* xd, float* dst, const galois_dim* dd);
 
-/* galois_matmul followed by galois_add of a residual (src/op.rs:3093-3111 then
- * :3073-3091) in one call: dst = res + mat-mul result, the sum rounded once as
- * Add::f rounds it, so the result is bit-identical to the two calls.  `res` has
- * the shape of dst.  With one activation row the sum is formed inside the
- * streaming GEMV (no second launch); other shapes run the two ops.  Not part of
- * the reference API. */
+/* Up to four reference ops in one call (not part of the reference API; results are
+ * bit-identical to running the ops one after the other):
+ *   t   = prologue(x)   none | galois_rms_norm(x, eps) then galois_mul by the gain row `aux`
+ *                            (src/op.rs:3155-3169, :3113-3127) | galois_unary(Silu)(x) then
+ *                            galois_mul by `aux`, a tensor laid out exactly like x (:3232-3256)
+ *   y   = galois_matmul(W, t)                                   (src/op.rs:3093-3111)
+ *   dst = res ? galois_add(res, y) : y                          (src/op.rs:3073-3091)
+ * With one activation row all of it is ONE launch of the streaming GEMV: the prologue runs
+ * where the row is quantised (rms_norm's sum in the same order as galois_b200_rms_norm_f32),
+ * the residual is added where a result is stored.  Other shapes run the separate ops, the
+ * prologue's result in a context-owned buffer.  `pro` may be NULL (no prologue), `res` may be
+ * NULL (no residual; `rd` is then ignored).  `aux` must be 16-byte aligned for the one-launch
+ * path. */
+#define GALOIS_B200_PROLOGUE_NONE 0
+#define GALOIS_B200_PROLOGUE_RMS_NORM_MUL 1
+#define GALOIS_B200_PROLOGUE_SILU_MUL 2
+typedef struct galois_b200_prologue {
+    int32_t kind;     /* GALOIS_B200_PROLOGUE_* */
+    const float* aux; /* gain row of >= K floats, or the second operand of the product */
+    float eps;        /* rms_norm only */
+} galois_b200_prologue;
+int galois_b200_mul_mat_q4_0_f32_fused(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
+                                       const galois_dim* xd, const galois_b200_prologue* pro, const float* res,
+                                       const galois_dim* rd, float* dst, const galois_dim* dd);
+/* The same with no prologue and a residual: galois_matmul then galois_add. */
 int galois_b200_mul_mat_q4_0_f32_add(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
                                      const galois_dim* xd, const float* res, const galois_dim* rd, float* dst,
                                      const galois_dim* dd);

@@ -472,6 +472,33 @@ def test_two_op_fusions_are_bit_identical(gb, dev, oracle):
         gb.galois_matmul_add(wt, xt, rt, y2)
         assert np.array_equal(y1.to_numpy(), y2.to_numpy())
         assert_close(y2.to_numpy(), O.add(r, O.mul_mat_q4_0(wq, x)))
+    # prologue + mat-mul + residual in one call: one launch at one activation row, separate ops otherwise
+    for (n, k, b, seed) in [(4096, 4096, 1, 21), (4096, 11008, 1, 22), (1185, 512, 1, 23), (2048, 1024, 3, 24), (70, 96, 1, 25)]:
+        wq = O.quantize_q4_0(O.fill_normal(n * k, 1000 + seed, 0, 0.02).reshape(n, k))
+        x = O.fill_normal(b * k, 1010 + seed).reshape(b, k)
+        u = O.fill_normal(b * k, 1020 + seed).reshape(b, k)
+        gain = 1.0 + 0.1 * O.fill_normal(k, 1030 + seed).reshape(1, k)
+        r = O.fill_normal(b * n, 1040 + seed).reshape(b, n)
+        wt, xt, ut, gt, rt = _q4(gb, dev, wq, n, k), _gpu(gb, dev, x), _gpu(gb, dev, u), _gpu(gb, dev, gain), _gpu(gb, dev, r)
+        t = gb.Tensor.zeros((k, b), gb.GGmlType.F32, G)
+        y1, y2, y3 = (gb.Tensor.zeros((n, b), gb.GGmlType.F32, G) for _ in range(3))
+        l0 = dev.launch_count()
+        gb.galois_matmul_fused(wt, xt, y2, rms_gain=gt, eps=1e-6, res=rt)
+        launches = dev.launch_count() - l0
+        gb.galois_rms_norm(xt, t, 1e-6)
+        gb.galois_mul(t, gt, t)
+        gb.galois_matmul(wt, t, y3)
+        gb.galois_add(rt, y3, y1)
+        assert np.array_equal(y1.to_numpy(), y2.to_numpy()), (n, k, b)
+        if b == 1 and k % 256 == 0:
+            assert launches == 1
+        assert_close(y2.to_numpy(), O.add(r, O.mul_mat_q4_0(wq, O.mul(O.rms_norm(x, 1e-6), gain))))
+        gb.galois_matmul_fused(wt, xt, y2, silu_mul=ut)
+        gb.galois_unary(xt, t, gb.UnaryOp.Silu)
+        gb.galois_mul(t, ut, t)
+        gb.galois_matmul(wt, t, y1)
+        assert np.array_equal(y1.to_numpy(), y2.to_numpy()), (n, k, b)
+        assert_close(y2.to_numpy(), O.mul_mat_q4_0(wq, O.mul(O.silu(x), u)))
     # shape errors
     bad = gb.Tensor.zeros((8, 2), gb.GGmlType.F32, G)
     with pytest.raises(gb.GError) as ei:
