@@ -10,6 +10,7 @@ from .op import (  # noqa: F401
     galois_add,
     galois_cont,
     galois_cpy,
+    galois_cpy_pair,
     galois_matmul,
     galois_matmul_add,
     galois_matmul_fused,

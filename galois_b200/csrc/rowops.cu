@@ -407,6 +407,35 @@ extern "C" int galois_b200_scale_f32(galois_b200_ctx* ctx, const float* x, const
     return 0;
 }
 
+// Two independent f32 -> f16 copies in one launch (blockIdx.y picks the copy): the K and the V append of
+// a decode step.
+struct cpy_job {
+    const float* x;
+    void* y;
+    dim4 xd, yd;
+    int64_t total;
+};
+__global__ void cpy_pair_f16_kernel(cpy_job j0, cpy_job j1) {
+    gb_pdl_entry();
+    const cpy_job& j = blockIdx.y == 0 ? j0 : j1;
+    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < j.total; k += (int64_t)gridDim.x * blockDim.x) {
+        int64_t t = k;
+        const int64_t i00 = t % j.xd.ne[0];
+        t /= j.xd.ne[0];
+        const int64_t i01 = t % j.xd.ne[1];
+        t /= j.xd.ne[1];
+        const int64_t i02 = t % j.xd.ne[2], i03 = t / j.xd.ne[2];
+        t = k;
+        const int64_t i10 = t % j.yd.ne[0];
+        t /= j.yd.ne[0];
+        const int64_t i11 = t % j.yd.ne[1];
+        t /= j.yd.ne[1];
+        const int64_t i12 = t % j.yd.ne[2], i13 = t / j.yd.ne[2];
+        const float v = j.x[i00 * j.xd.nb[0] + i01 * j.xd.nb[1] + i02 * j.xd.nb[2] + i03 * j.xd.nb[3]];
+        reinterpret_cast<__half*>(j.y)[i10 * j.yd.nb[0] + i11 * j.yd.nb[1] + i12 * j.yd.nb[2] + i13 * j.yd.nb[3]] = __float2half_rn(v);
+    }
+}
+
 template <typename OUT>
 static int cpy_impl(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, OUT* y, const galois_dim* yd) {
     if (any_null(x, xd, y, yd)) return gb_fail(ctx, GALOIS_B200_E_BADARG, "cpy: null pointer");
@@ -425,6 +454,35 @@ static int cpy_impl(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, 
     GB_LAUNCHED(ctx, "cpy");
     return 0;
 }
+extern "C" int galois_b200_cpy_f32_f16_pair(galois_b200_ctx* ctx, const float* x0, const galois_dim* x0d, void* y0_f16,
+                                            const galois_dim* y0d, const float* x1, const galois_dim* x1d, void* y1_f16,
+                                            const galois_dim* y1d) {
+    GB_CHECK_CTX(ctx);
+    if (any_null(x0, x0d, y0_f16, y0d) || any_null(x1, x1d, y1_f16, y1d)) return gb_fail(ctx, GALOIS_B200_E_BADARG, "cpy pair: null pointer");
+    cpy_job j[2];
+    const float* xs[2] = {x0, x1};
+    void* ys[2] = {y0_f16, y1_f16};
+    const galois_dim* xds[2] = {x0d, x1d};
+    const galois_dim* yds[2] = {y0d, y1d};
+    int64_t most = 0;
+    for (int c = 0; c < 2; c++) {
+        j[c].total = gb_nelements(xds[c]);
+        // assert_eq!(inp_d.elem_count(), dst_d.elem_count())  (src/op.rs:1930)
+        if (j[c].total != gb_nelements(yds[c])) return gb_fail(ctx, GALOIS_B200_E_SHAPE, "cpy pair: element counts of copy %d differ", c);
+        j[c].x = xs[c];
+        j[c].y = ys[c];
+        for (int i = 0; i < 4; i++) {
+            j[c].xd.ne[i] = xds[c]->ne[i], j[c].xd.nb[i] = xds[c]->nb[i];
+            j[c].yd.ne[i] = yds[c]->ne[i], j[c].yd.nb[i] = yds[c]->nb[i];
+        }
+        most = j[c].total > most ? j[c].total : most;
+    }
+    if (most == 0) return 0;
+    gb_launch(ctx, cpy_pair_f16_kernel, dim3(ew_grid(most, ctx->sm_count), 2), dim3(256), 0, j[0], j[1]);
+    GB_LAUNCHED(ctx, "cpy pair");
+    return 0;
+}
+
 extern "C" int galois_b200_cpy_f32_f32(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, float* y,
                                        const galois_dim* yd) {
     GB_CHECK_CTX(ctx);

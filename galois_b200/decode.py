@@ -17,7 +17,7 @@ from dataclasses import dataclass
 
 import numpy as np
 
-from .op import (RopeCustomOption, UnaryOp, galois_add, galois_cpy, galois_matmul, galois_matmul_add, galois_matmul_fused, galois_mul, galois_rms_norm,
+from .op import (RopeCustomOption, UnaryOp, galois_add, galois_cpy, galois_cpy_pair, galois_matmul, galois_matmul_add, galois_matmul_fused, galois_mul, galois_rms_norm,
                  galois_rms_norm_mul, galois_rope_custom, galois_silu_mul, galois_soft_max_ext, galois_unary)
 from .tensor import Device, GGmlType, Tensor
 
@@ -47,7 +47,7 @@ class DecodeLayer:
     enqueues the kernels of one token on the device's stream and returns the output tensor.
 
     ``fused=False``: the op-by-op sequence a galois caller writes, 22 kernels.
-    ``fused=True`` : the same arithmetic in 10 kernels.  The rows of Wq, Wk, Wv (and of W_gate,
+    ``fused=True`` : the same arithmetic in 9 kernels.  The rows of Wq, Wk, Wv (and of W_gate,
     W_up) are stacked into one Q4_0 weight at upload, so the three (two) projections of the same
     input are one mat-mul whose result is split by views; rope runs once over the 2 x heads rows of
     q and k; rms_norm + gain and silu + gate product run inside the mat-mul that consumes them, the
@@ -142,10 +142,9 @@ class DecodeLayer:
         galois_rope_custom(self.rope, qk3, pos, self.qkr)  # heads 0..nh-1 of q, then of k
         k_src = self.qkr.view((hd, 1, nh), (1, hd, hd, hd * nh), offset=H)
         k_dst = self.k_cache.view((hd, 1, nh), (1, hd, hd * ctx, hd * ctx * nh), offset=position * hd)
-        galois_cpy(k_src, k_dst)
         v_src = self.qkv.view((1, hd, nh), (1, 1, hd, hd * nh), offset=2 * H)
         v_dst = self.v_cache.view((1, hd, nh), (1, ctx, hd * ctx, hd * ctx * nh), offset=position)
-        galois_cpy(v_src, v_dst)
+        galois_cpy_pair(k_src, k_dst, v_src, v_dst)  # both cache appends in one launch
         qh = self.qkr.view((hd, 1, nh), (1, hd, hd, hd * nh))
         galois_matmul(self.k_cache, qh, self.scores)
         sc = self.scores.view((ctx, nh, 1), (1, ctx, ctx * nh, ctx * nh))

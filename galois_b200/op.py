@@ -238,6 +238,18 @@ def galois_cpy(src: Tensor, dst: Tensor) -> None:
     _check(ctx, rc, "galois_cpy")
 
 
+def galois_cpy_pair(src0: Tensor, dst0: Tensor, src1: Tensor, dst1: Tensor) -> None:
+    """Two independent f32 -> f16 galois_cpy calls (src/op.rs:3171-3185) in one launch (the K and the V
+    append of a decode step).  Not part of the reference API."""
+    ctx = _gpu_ctx(src0, dst0, src1, dst1)
+    for t in (src0, src1):
+        _want(t, GGmlType.F32, "galois_cpy_pair src")
+    for t in (dst0, dst1):
+        _want(t, GGmlType.F16, "galois_cpy_pair dst")
+    rc = lib.galois_b200_cpy_f32_f16_pair(ctx, _p(src0), _d(src0), _p(dst0), _d(dst0), _p(src1), _d(src1), _p(dst1), _d(dst1))
+    _check(ctx, rc, "galois_cpy_pair")
+
+
 def galois_cont(src: Tensor, dst: Tensor) -> None:
     """src/op.rs:3187-3201: same kernel as galois_cpy."""
     galois_cpy(src, dst)

@@ -260,6 +260,11 @@ int galois_b200_cpy_f32_f32(galois_b200_ctx* ctx, const float* x, const galois_d
                             const galois_dim* yd);
 int galois_b200_cpy_f32_f16(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, void* y_f16,
                             const galois_dim* yd);
+/* Two independent f32 -> f16 galois_cpy calls (src/op.rs:3171-3185) in one launch: the K and the V
+ * append of a decode step.  The two destinations must not overlap.  Not part of the reference API. */
+int galois_b200_cpy_f32_f16_pair(galois_b200_ctx* ctx, const float* x0, const galois_dim* x0d, void* y0_f16,
+                                 const galois_dim* y0d, const float* x1, const galois_dim* x1d, void* y1_f16,
+                                 const galois_dim* y1d);
 
 /* ---- row sharding across GPUs ------------------------------------------ */
 

@@ -111,4 +111,4 @@ def test_fused_layer_equals_op_by_op_layer(dev, oracle, hidden, heads, ffn, ctx,
     assert np.array_equal(a, b)
     assert np.array_equal(plain.k_cache.to_numpy().view(np.uint16), fused.k_cache.to_numpy().view(np.uint16))
     assert np.array_equal(plain.v_cache.to_numpy().view(np.uint16), fused.v_cache.to_numpy().view(np.uint16))
-    assert (l1 - l0, l2 - l1) == (22, 10)
+    assert (l1 - l0, l2 - l1) == (22, 9)

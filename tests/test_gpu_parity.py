@@ -507,3 +507,29 @@ def test_two_op_fusions_are_bit_identical(gb, dev, oracle):
     with pytest.raises(gb.GError) as ei:
         gb.galois_rms_norm_mul(_gpu(gb, dev, np.zeros((2, 16), np.float32)), bad, gb.Tensor.zeros((16, 2), gb.GGmlType.F32, G), 1e-6)
     assert ei.value.code == -2
+
+
+def test_cpy_pair_equals_two_copies(gb, dev, oracle):
+    """The paired f32 -> f16 copy (K and V cache appends in one launch) writes what two galois_cpy calls write."""
+    G = gb.Device.Gpu(dev)
+    hd, nh, ctx, pos = 64, 4, 32, 7
+    k = oracle.fill_normal(hd * nh, 51).reshape(nh, 1, hd)
+    v = oracle.fill_normal(hd * nh, 52).reshape(nh, hd, 1)
+    kt, vt = _gpu(gb, dev, k), _gpu(gb, dev, v)
+    caches = []
+    for paired in (False, True):
+        kc = gb.Tensor.zeros((hd, ctx, nh), gb.GGmlType.F16, G)
+        vc = gb.Tensor.zeros((ctx, hd, nh), gb.GGmlType.F16, G)
+        k_dst = kc.view((hd, 1, nh), (1, hd, hd * ctx, hd * ctx * nh), offset=pos * hd)
+        v_dst = vc.view((1, hd, nh), (1, ctx, hd * ctx, hd * ctx * nh), offset=pos)
+        if paired:
+            gb.galois_cpy_pair(kt, k_dst, vt, v_dst)
+        else:
+            gb.galois_cpy(kt, k_dst)
+            gb.galois_cpy(vt, v_dst)
+        caches.append((kc.to_numpy().view(np.uint16), vc.to_numpy().view(np.uint16)))
+    assert np.array_equal(caches[0][0], caches[1][0]) and np.array_equal(caches[0][1], caches[1][1])
+    assert caches[1][0].any() and caches[1][1].any()
+    with pytest.raises(gb.GError) as ei:
+        gb.galois_cpy_pair(kt, gb.Tensor.zeros((hd, 1, nh + 1), gb.GGmlType.F16, G), vt, gb.Tensor.zeros((1, hd, nh), gb.GGmlType.F16, G))
+    assert ei.value.code == -2
