@@ -524,6 +524,9 @@ def run_ours(args):
             us_g, us_d = time_mm(FFN, HIDDEN, bb, 16), time_mm(HIDDEN, FFN, bb, 16)
             ab = algorithmic_bytes(FFN, HIDDEN, bb)
             extra[f"config2_batch{bb}"] = {"us_gate_up": us_g, "us_down": us_d, "hbm_gbs": 3 * ab / (2 * us_g + us_d) / 1e3}
+        us_s = time_mm(2 * FFN, HIDDEN, 1, 12)
+        extra["config2_stacked_gate_up_batch1"] = {"us": us_s, "hbm_gbs": algorithmic_bytes(2 * FFN, HIDDEN, 1) / us_s / 1e3,
+                                                   "note": "gate and up rows stacked into one 22016 x 4096 weight: one launch for both"}
         us_h = time_mm(32000, 4096, 16, 8)
         extra["config5_head_batch16"] = {"us": us_h, "hbm_gbs": algorithmic_bytes(32000, 4096, 16) / us_h / 1e3}
         us_f = time_mm(28672, 8192, 16, 4)
