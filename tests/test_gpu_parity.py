@@ -499,6 +499,21 @@ def test_two_op_fusions_are_bit_identical(gb, dev, oracle):
         gb.galois_matmul(wt, t, y1)
         assert np.array_equal(y1.to_numpy(), y2.to_numpy()), (n, k, b)
         assert_close(y2.to_numpy(), O.mul_mat_q4_0(wq, O.mul(O.silu(x), u)))
+    # argument errors of the fused call
+    from galois_b200._lib import GaloisPrologue
+    wt, xt = _q4(gb, dev, O.quantize_q4_0(O.fill_normal(8 * 256, 5, 0, 0.02).reshape(8, 256)), 8, 256), _gpu(gb, dev, O.fill_normal(256, 6).reshape(1, 256))
+    yt = gb.Tensor.zeros((8, 1), gb.GGmlType.F32, G)
+    fused = lambda pro, res, rd: gb.lib.galois_b200_mul_mat_q4_0_f32_fused(  # noqa: E731
+        dev.ctx, C.c_void_p(wt.data_ptr()), C.byref(wt.dim().c_struct()), C.c_void_p(xt.data_ptr()), C.byref(xt.dim().c_struct()), pro, res, rd,
+        C.c_void_p(yt.data_ptr()), C.byref(yt.dim().c_struct()))
+    pro = GaloisPrologue()
+    pro.kind = 7
+    assert fused(C.byref(pro), None, None) == -1          # unknown prologue
+    pro.kind, pro.aux = 1, None
+    assert fused(C.byref(pro), None, None) == -1          # rms_norm without its gain row
+    wrong = gb.Tensor.zeros((9, 1), gb.GGmlType.F32, G)
+    assert fused(None, C.c_void_p(wrong.data_ptr()), C.byref(wrong.dim().c_struct())) == -2  # residual of another shape
+    assert fused(None, None, None) == 0                   # no prologue, no residual: the plain mat-mul
     # shape errors
     bad = gb.Tensor.zeros((8, 2), gb.GGmlType.F32, G)
     with pytest.raises(gb.GError) as ei:

@@ -140,3 +140,50 @@ def test_two_or_more_gpus_real_exchange():
            "--master-port", "29613", os.path.join(ROOT, "tests", "peer_gather_worker.py")]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert res.returncode == 0 and "PEER_GATHER_OK" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
+
+
+_IPC_CHILD = r"""
+import ctypes as C, sys
+import numpy as np
+sys.path.insert(0, sys.argv[1])
+import galois_b200 as gb
+from galois_b200 import lib
+dev = gb.CudaDevice(0)
+handle = bytes.fromhex(sys.argv[2])
+n = int(sys.argv[3])
+ptr = C.c_void_p()
+assert lib.galois_b200_ipc_import(dev.ctx, handle, C.byref(ptr)) == 0, lib.galois_b200_last_error(dev.ctx)
+got = np.empty(n, np.float32)
+assert lib.galois_b200_dtoh(dev.ctx, got.ctypes.data_as(C.c_void_p), ptr, 4 * n) == 0
+assert np.array_equal(got, np.arange(n, dtype=np.float32)), "child read something else"
+back = (2.0 * got).astype(np.float32)
+assert lib.galois_b200_htod(dev.ctx, ptr, back.ctypes.data_as(C.c_void_p), 4 * n) == 0
+assert lib.galois_b200_synchronize(dev.ctx) == 0
+assert lib.galois_b200_ipc_close(dev.ctx, ptr) == 0
+print("IPC_CHILD_OK")
+"""
+
+
+def test_ipc_export_import_between_processes(dev):
+    """A buffer exported by this process is mapped by a second process (same GPU), read and
+    rewritten there; the first process sees the new contents."""
+    from galois_b200 import lib
+
+    n = 4096
+    ptr = C.c_void_p()
+    assert lib.galois_b200_alloc(dev.ctx, 4 * n, C.byref(ptr)) == 0
+    try:
+        src = np.arange(n, dtype=np.float32)
+        assert lib.galois_b200_htod(dev.ctx, ptr, src.ctypes.data_as(C.c_void_p), 4 * n) == 0
+        dev.synchronize()
+        handle = C.create_string_buffer(64)
+        assert lib.galois_b200_ipc_export(dev.ctx, ptr, handle) == 0
+        res = subprocess.run([sys.executable, "-c", _IPC_CHILD, ROOT, handle.raw.hex(), str(n)], capture_output=True, text=True, timeout=300)
+        assert res.returncode == 0 and "IPC_CHILD_OK" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+        got = np.empty(n, np.float32)
+        assert lib.galois_b200_dtoh(dev.ctx, got.ctypes.data_as(C.c_void_p), ptr, 4 * n) == 0
+        assert np.array_equal(got, 2.0 * src)
+        assert lib.galois_b200_ipc_export(dev.ctx, None, handle) == -1
+        assert lib.galois_b200_ipc_import(dev.ctx, None, C.byref(C.c_void_p())) == -1
+    finally:
+        lib.galois_b200_free(dev.ctx, ptr)
