@@ -11,6 +11,7 @@ from .op import (  # noqa: F401
     galois_cont,
     galois_cpy,
     galois_cpy_pair,
+    galois_get_rows,
     galois_matmul,
     galois_matmul_add,
     galois_matmul_fused,

@@ -75,6 +75,7 @@ SIGNATURES = {
     "galois_b200_cpy_f32_f32": ([_P, _P, _DP, _P, _DP], _I),
     "galois_b200_cpy_f32_f16": ([_P, _P, _DP, _P, _DP], _I),
     "galois_b200_cpy_f32_f16_pair": ([_P, _P, _DP, _P, _DP, _P, _DP, _P, _DP], _I),
+    "galois_b200_get_rows_q4_0_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_shard_rows": ([_I64, _I, _I, C.POINTER(_I64), C.POINTER(_I64)], _I),
     "galois_b200_ipc_export": ([_P, _P, C.c_char_p], _I),
     "galois_b200_ipc_import": ([_P, C.c_char_p, C.POINTER(_P)], _I),

@@ -436,6 +436,40 @@ __global__ void cpy_pair_f16_kernel(cpy_job j0, cpy_job j1) {
     }
 }
 
+// ---------------------------------------------------------------- get_rows (Q4_0 table -> f32 rows)
+// GetRows::f_q_x_f32::<BlockQ4_0> (src/op.rs:2546-2571) with <BlockQ4_0 as QuantType>::to_f32
+// (src/ggml_quants.rs:209-228): dst row i = dequantised table row idx[i]; element j of a block is
+// (low nibble of byte j - 8) * d, element j + 16 the high nibble.  One thread per 18-byte block.
+// An index outside the table (the reference panics on the slice) leaves zeros in that row and
+// records GALOIS_B200_E_BADARG in the context's status word.
+__global__ void get_rows_q4_0_kernel(const uint8_t* __restrict__ w, int64_t w_row_blocks, int64_t table_rows,
+                                     const int32_t* __restrict__ idx, float* __restrict__ dst, int64_t dst_stride, int64_t nblk,
+                                     int64_t nr, int* __restrict__ status) {
+    gb_pdl_entry();
+    const int64_t total = nr * nblk;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = t / nblk, b = t - i * nblk;
+        const int64_t r = idx[i];
+        float* out = dst + i * dst_stride + b * 32;
+        if (r < 0 || r >= table_rows) {
+            for (int j = 0; j < 32; j++) out[j] = 0.0f;
+            if (b == 0) atomicExch(status, GALOIS_B200_E_BADARG);
+            continue;
+        }
+        const unsigned short* blk = reinterpret_cast<const unsigned short*>(w + (r * w_row_blocks + b) * GB_Q4_BYTES);
+        const float d = __half2float(__ushort_as_half(__ldg(blk)));
+#pragma unroll
+        for (int h = 0; h < 8; h++) {
+            const unsigned short two = __ldg(blk + 1 + h);  // bytes 2h, 2h + 1 of qs
+            const int q0 = two & 0xff, q1 = two >> 8;
+            out[2 * h] = __fmul_rn((float)((q0 & 0x0F) - 8), d);
+            out[2 * h + 1] = __fmul_rn((float)((q1 & 0x0F) - 8), d);
+            out[2 * h + 16] = __fmul_rn((float)((q0 >> 4) - 8), d);
+            out[2 * h + 17] = __fmul_rn((float)((q1 >> 4) - 8), d);
+        }
+    }
+}
+
 template <typename OUT>
 static int cpy_impl(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, OUT* y, const galois_dim* yd) {
     if (any_null(x, xd, y, yd)) return gb_fail(ctx, GALOIS_B200_E_BADARG, "cpy: null pointer");
@@ -454,6 +488,26 @@ static int cpy_impl(galois_b200_ctx* ctx, const float* x, const galois_dim* xd, 
     GB_LAUNCHED(ctx, "cpy");
     return 0;
 }
+extern "C" int galois_b200_get_rows_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const int32_t* idx,
+                                             const galois_dim* id, float* dst, const galois_dim* dd) {
+    GB_CHECK_CTX(ctx);
+    if (any_null(w, wd, idx, id) || any_null(dst, dd)) return gb_fail(ctx, GALOIS_B200_E_BADARG, "get_rows: null pointer");
+    const int64_t nc = wd->ne[0], nr = gb_nelements(id);
+    if (nc % GB_QK != 0) return gb_fail(ctx, GALOIS_B200_E_BADARG, "get_rows: %lld is not divisible by 32", (long long)nc);
+    // assert!(ne0 == nc); assert!(ne1 == nr); assert!(inp0_d.stride_1d() == 1)  (src/op.rs:2559-2561)
+    if (dd->ne[0] != nc || dd->ne[1] * dd->ne[2] * dd->ne[3] != nr) return gb_fail(ctx, GALOIS_B200_E_SHAPE, "get_rows: dst must be {K, number of indices}");
+    if (wd->nb[0] != 1 || dd->nb[0] != 1 || id->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "get_rows: rows must be contiguous");
+    if (dd->ne[2] != 1 || dd->ne[3] != 1 || wd->ne[2] != 1 || wd->ne[3] != 1 || !gb_is_contiguous(id))
+        return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "get_rows: 2-D table and dst, contiguous indices");
+    if ((uintptr_t)w % 2 != 0 || (uintptr_t)dst % 4 != 0 || (uintptr_t)idx % 4 != 0) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "get_rows: misaligned pointer");
+    if (nr == 0 || nc == 0) return 0;
+    const int64_t nblk = nc / GB_QK;
+    gb_launch(ctx, get_rows_q4_0_kernel, dim3(ew_grid(nr * nblk, ctx->sm_count)), dim3(256), 0, (const uint8_t*)w, wd->nb[1], wd->ne[1], idx,
+              dst, dd->nb[1], nblk, nr, ctx->dev_status);
+    GB_LAUNCHED(ctx, "get_rows");
+    return 0;
+}
+
 extern "C" int galois_b200_cpy_f32_f16_pair(galois_b200_ctx* ctx, const float* x0, const galois_dim* x0d, void* y0_f16,
                                             const galois_dim* y0d, const float* x1, const galois_dim* x1d, void* y1_f16,
                                             const galois_dim* y1d) {

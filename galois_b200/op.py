@@ -250,6 +250,16 @@ def galois_cpy_pair(src0: Tensor, dst0: Tensor, src1: Tensor, dst1: Tensor) -> N
     _check(ctx, rc, "galois_cpy_pair")
 
 
+def galois_get_rows(src0: Tensor, src1: Tensor, dst: Tensor) -> None:
+    """src/op.rs:3281-3292 (the reference implements the CPU arm only): rows `src1` (i32) of the Q4_0 table
+    `src0`, dequantised, into the f32 tensor `dst` {K, number of indices}."""
+    ctx = _gpu_ctx(src0, src1, dst)
+    _want(src0, GGmlType.Q4_0, "galois_get_rows src0")
+    _want(src1, GGmlType.I32, "galois_get_rows src1")
+    _want(dst, GGmlType.F32, "galois_get_rows dst")
+    _check(ctx, lib.galois_b200_get_rows_q4_0_f32(ctx, _p(src0), _d(src0), _p(src1), _d(src1), _p(dst), _d(dst)), "galois_get_rows")
+
+
 def galois_cont(src: Tensor, dst: Tensor) -> None:
     """src/op.rs:3187-3201: same kernel as galois_cpy."""
     galois_cpy(src, dst)

@@ -266,6 +266,15 @@ int galois_b200_cpy_f32_f16_pair(galois_b200_ctx* ctx, const float* x0, const ga
                                  const galois_dim* y0d, const float* x1, const galois_dim* x1d, void* y1_f16,
                                  const galois_dim* y1d);
 
+/* galois_get_rows for a Q4_0 table (src/op.rs:3281-3292; its GPU arm is todo!() in the reference):
+ * numerics of GetRows::f_q_x_f32::<BlockQ4_0> (src/op.rs:2546-2571) with
+ * <BlockQ4_0 as QuantType>::to_f32 (src/ggml_quants.rs:209-228) -- the embedding look-up in front
+ * of the first layer.  w: Q4_0 {K, table rows}; idx: i32, any shape, n elements; dst: f32 {K, n}.
+ * Bit-exact.  An index outside the table (the reference panics) zeroes that row and makes the next
+ * galois_b200_synchronize return GALOIS_B200_E_BADARG. */
+int galois_b200_get_rows_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const int32_t* idx,
+                                  const galois_dim* id, float* dst, const galois_dim* dd);
+
 /* ---- row sharding across GPUs ------------------------------------------ */
 
 /* Row range [*row0, *row0 + *nrows) of an N-row weight owned by `rank` of

@@ -180,6 +180,21 @@ def dequantize_q4_0(w: np.ndarray, k: int) -> np.ndarray:
     return out
 
 
+def get_rows_q4_0(w: np.ndarray, k: int, idx: np.ndarray) -> np.ndarray:
+    """GetRows::f_q_x_f32::<BlockQ4_0> (src/op.rs:2546-2571): row idx[i] of the Q4_0 table `w`
+    ([rows][K/32*18] bytes), dequantised with <BlockQ4_0 as QuantType>::to_f32
+    (src/ggml_quants.rs:209-228), becomes row i of the f32 result [len(idx)][K]."""
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    wr = w.reshape(-1, k // QK * Q4_0_BYTES)
+    idx = np.asarray(idx).reshape(-1)
+    out = np.empty((idx.size, k), dtype=np.float32)
+    for i, r in enumerate(idx):
+        if not 0 <= int(r) < wr.shape[0]:
+            raise OracleError(f"get_rows: index {int(r)} outside the table of {wr.shape[0]} rows (the reference panics)")
+        lib().orc_dequantize_row_q4_0(_p(wr[int(r)]), _p(out[i]), k)
+    return out
+
+
 def quantize_q8_0(x: np.ndarray) -> np.ndarray:
     """f32 [..., K] -> uint8 [..., K/32*34] Q8_0 blocks (quantize_row_q8_0)."""
     x = np.ascontiguousarray(x, dtype=np.float32)

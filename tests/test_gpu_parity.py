@@ -548,3 +548,42 @@ def test_cpy_pair_equals_two_copies(gb, dev, oracle):
     with pytest.raises(gb.GError) as ei:
         gb.galois_cpy_pair(kt, gb.Tensor.zeros((hd, 1, nh + 1), gb.GGmlType.F16, G), vt, gb.Tensor.zeros((1, hd, nh), gb.GGmlType.F16, G))
     assert ei.value.code == -2
+
+
+@pytest.mark.parametrize("n,k,idx", [(32000, 4096, [0, 31999, 17, 17, 4096, 1]), (37, 256, [5, 0, 36]), (3, 32, [2]), (100, 11008, list(range(0, 100, 7)))])
+def test_get_rows_q4_0(gb, dev, oracle, n, k, idx):
+    """galois_get_rows over a Q4_0 table (the embedding look-up): bit-exact against the oracle, contiguous and strided dst."""
+    O = oracle
+    G = gb.Device.Gpu(dev)
+    w = O.quantize_q4_0(O.fill_normal(n * k, 3000 + n + k, 0, 0.02).reshape(n, k))
+    idx = np.array(idx, np.int32)
+    want = O.get_rows_q4_0(w, k, idx)
+    wt = _q4(gb, dev, w, n, k)
+    it = gb.Tensor.from_numpy(idx, gb.GGmlType.I32, G)
+    dst = gb.Tensor.zeros((k, len(idx)), gb.GGmlType.F32, G)
+    gb.galois_get_rows(wt, it, dst)
+    assert np.array_equal(dst.to_numpy(), want)
+    wide = gb.Tensor.zeros((k + 32, len(idx)), gb.GGmlType.F32, G)  # rows of a wider buffer
+    view = wide.view((k, len(idx)), (1, k + 32, (k + 32) * len(idx), (k + 32) * len(idx)))
+    gb.galois_get_rows(wt, it, view)
+    got = wide.to_numpy()
+    assert np.array_equal(got[:, :k], want) and not got[:, k:].any()
+
+
+def test_get_rows_q4_0_errors(gb, dev, oracle):
+    G = gb.Device.Gpu(dev)
+    w = oracle.quantize_q4_0(oracle.fill_normal(4 * 64, 9, 0, 0.02).reshape(4, 64))
+    wt = _q4(gb, dev, w, 4, 64)
+    it = gb.Tensor.from_numpy(np.array([1, 4], np.int32), gb.GGmlType.I32, G)  # 4 is outside the table
+    dst = gb.Tensor.zeros((64, 2), gb.GGmlType.F32, G)
+    gb.galois_get_rows(wt, it, dst)
+    with pytest.raises(gb.GError) as ei:
+        dev.synchronize()
+    assert ei.value.code == -1
+    got = dst.to_numpy()
+    assert np.array_equal(got[0], oracle.get_rows_q4_0(w, 64, np.array([1], np.int32))[0]) and not got[1].any()
+    with pytest.raises(gb.GError) as ei:  # dst of the wrong shape
+        gb.galois_get_rows(wt, it, gb.Tensor.zeros((64, 3), gb.GGmlType.F32, G))
+    assert ei.value.code == -2
+    gb.galois_get_rows(wt, gb.Tensor.from_numpy(np.array([3], np.int32), gb.GGmlType.I32, G), gb.Tensor.zeros((64, 1), gb.GGmlType.F32, G))
+    dev.synchronize()  # the context is fine

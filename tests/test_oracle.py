@@ -271,3 +271,27 @@ def test_fill_normal_is_deterministic(oracle):
     assert np.array_equal(a, oracle.fill_normal(1001, 42, 0, 0.02))
     assert abs(a.std() - 0.02) < 2e-3 and abs(a.mean()) < 3e-3
     assert not np.array_equal(a, oracle.fill_normal(1001, 43, 0, 0.02))
+
+
+def test_get_rows_q4_0(oracle):
+    """GetRows over a Q4_0 table (src/op.rs:2546-2571 of galois): a hand-built block, an independent numpy
+    restatement of to_f32 (src/ggml_quants.rs:209-228), repeated indices, and the out-of-range panic."""
+    O = oracle
+    # one block by hand: d = 0.5, byte j = j | ((15 - j) << 4)  ->  element j = (j - 8) / 2, element 16 + j = (7 - j) / 2
+    blk = np.zeros(18, np.uint8)
+    blk[0:2] = np.array([0.5], np.float16).view(np.uint8)
+    blk[2:] = [j | ((15 - j) << 4) for j in range(16)]
+    got = O.get_rows_q4_0(blk.reshape(1, 18), 32, np.array([0, 0], np.int32))
+    want = np.array([(j - 8) / 2 for j in range(16)] + [(7 - j) / 2 for j in range(16)], np.float32)
+    assert np.array_equal(got[0], want) and np.array_equal(got[1], want)
+    # random table against a vectorised numpy restatement
+    n, k = 37, 256
+    w = O.quantize_q4_0(O.fill_normal(n * k, 77, 0, 0.02).reshape(n, k)).reshape(n, k // 32, 18)
+    d = w[:, :, 0:2].copy().view(np.float16).astype(np.float32)            # [n][nblk][1]
+    qs = w[:, :, 2:].astype(np.int32)
+    lo, hi = (qs & 0x0F) - 8, (qs >> 4) - 8
+    table = np.concatenate([lo.astype(np.float32) * d, hi.astype(np.float32) * d], axis=2).reshape(n, k)
+    idx = np.array([5, 0, 36, 5, 17], np.int32)
+    assert np.array_equal(O.get_rows_q4_0(w, k, idx), table[idx])
+    with pytest.raises(O.OracleError):
+        O.get_rows_q4_0(w, k, np.array([37], np.int32))
