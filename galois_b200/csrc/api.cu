@@ -159,7 +159,6 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
     } else {
         void* p;
         rc = gb_scratch(ctx, (size_t)16 << 20, &p);
-        if (rc == 0) rc = gb_mmv_bulk_init(ctx);
         if (rc == 0) rc = gb_gemv_init(ctx);
         if (rc == 0) rc = gb_mmq_skinny_init(ctx);
         if (rc == 0) rc = gb_mm_tc_init(ctx);
@@ -297,20 +296,19 @@ static bool skinny_beats_tc(const galois_b200_ctx* ctx, const galois_dim* wd, co
 }
 
 // The kernel the automatic choice (or the forced variant) takes for this problem:
-// 1 = direct, 2 = streaming GEMV / wide-batch dp4a, 3 = tcgen05 GEMM, 4 = skinny mma.sync.
+// 1 = direct, 2 = streaming GEMV, 3 = tcgen05 GEMM, 4 = skinny mma.sync.
 int gb_choose_mul_mat_variant(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
                               const galois_dim* dd) {
     if (ctx->variant != 0) return ctx->variant;
     const bool tc_ok = gb_mm_tc_supported(ctx, w, wd, x, xd, dd);
     const bool gemv_ok = gb_gemv_supported(ctx, w, wd, x, xd, dd);
-    const bool bulk_ok = gb_mmv_bulk_supported(ctx, w, wd, xd, dd);
     const bool skinny_ok = gb_mmq_skinny_supported(ctx, w, wd, x, xd, dd);
     // one activation row: dp4a GEMV; 2..16 rows: mma.sync skinny kernel; 17..192: whichever the cost model
     // prefers; more: tcgen05 GEMM
     if (gemv_ok && xd->ne[1] < GB_SKINNY_MIN_BATCH) return 2;
     if (skinny_ok && (!tc_ok || xd->ne[1] <= 16 || skinny_beats_tc(ctx, wd, xd))) return 4;
     if (tc_ok && xd->ne[1] >= GB_TC_MIN_BATCH) return 3;
-    return (gemv_ok || bulk_ok) ? 2 : 1;
+    return gemv_ok ? 2 : 1;
 }
 
 extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
@@ -330,14 +328,13 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
     }
     const bool tc_ok = gb_mm_tc_supported(ctx, w, wd, x, xd, dd);
     const bool gemv_ok = gb_gemv_supported(ctx, w, wd, x, xd, dd);
-    const bool bulk_ok = gb_mmv_bulk_supported(ctx, w, wd, xd, dd);
     const bool skinny_ok = gb_mmq_skinny_supported(ctx, w, wd, x, xd, dd);
     const int variant = gb_choose_mul_mat_variant(ctx, w, wd, x, xd, dd);
     if (variant == 4 && !skinny_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: skinny variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned operands, batch <= 192");
-    if (variant == 2 && !(gemv_ok || bulk_ok)) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: streaming variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned base, batch <= 8");
+    if (variant == 2 && !gemv_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: streaming GEMV needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned operands, one activation row");
     if (variant == 3 && !tc_ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: tensor-core variant needs 2-D contiguous weights, K %% 256 == 0, 16-byte aligned operands");
 
-    const bool gemv = variant == 2 && gemv_ok;
+    const bool gemv = variant == 2;
     gb_q8_soa xq = {nullptr, nullptr};
     void* scratch = nullptr;
     if (variant == 3) {
@@ -360,8 +357,6 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
         rc = gb_mmq_skinny(ctx, w, wd, x, xd, dst, dd, scratch);
     else if (gemv)
         rc = gb_gemv_q4_0(ctx, w, wd, x, xd, dst, dd);
-    else if (variant == 2)
-        rc = gb_mmv_q4_0_bulk(ctx, w, wd, xq, xd, dst, dd);
     else
         rc = gb_mmv_q4_0_direct(ctx, w, wd, xq, xd, dst, dd);
     if (prof) {

@@ -1,4 +1,4 @@
-// Streaming Q4_0 x Q8_0 GEMV for decode (batch 1-4): ONE kernel per mat-mul, no scratch memory.
+// Streaming Q4_0 x Q8_0 GEMV for decode (one activation row): ONE kernel per mat-mul, no scratch memory.
 //
 //   * the f32 activations are quantised to Q8_0 inside the kernel, bit-exact with
 //     <BlockQ8_0 as QuantType>::from_f32 (src/ggml_quants.rs:736-764 of galois).  The CTAs of a
@@ -364,7 +364,7 @@ struct gemv_plan {
 gemv_plan plan_gemv(const galois_b200_ctx* ctx, int64_t K, int64_t N, int64_t B) {
     gemv_plan p{};
     p.ok = false;
-    if (B < 1 || B > 4 || K % 256 != 0) return p;  // rows are whole multiples of 16 bytes for the bulk copies
+    if (B != 1 || K % 256 != 0) return p;  // one activation row; rows are whole multiples of 16 bytes for the bulk copies
     p.nbt = B <= 1 ? 1 : (B <= 2 ? 2 : 4);
     const int64_t npair = K / 64;
     // Lane segment: 4 / 2 / 1 block pairs.  First choice: whole rows per pass (every lane busy).
@@ -421,9 +421,7 @@ gemv_plan plan_gemv(const galois_b200_ctx* ctx, int64_t K, int64_t N, int64_t B)
     X(1, 4, true, 1) X(1, 2, true, 1) X(1, 1, true, 1)                               \
     X(1, 4, false, 1) X(1, 2, false, 1) X(1, 2, false, 2) X(1, 2, false, 3)          \
     X(1, 1, false, 1) X(1, 1, false, 2) X(1, 1, false, 3)                            \
-    X(1, 4, false, 0) X(1, 2, false, 0) X(1, 1, false, 0)                            \
-    X(2, 2, true, 0) X(2, 1, true, 0) X(2, 2, false, 0) X(2, 1, false, 0)            \
-    X(4, 2, true, 0) X(4, 1, true, 0) X(4, 2, false, 0) X(4, 1, false, 0)
+    X(1, 4, false, 0) X(1, 2, false, 0) X(1, 1, false, 0)
 
 template <int NB, int SEG, bool SPLIT, int NPASS>
 cudaError_t gemv_attr() {
@@ -478,7 +476,7 @@ bool gb_gemv_supported(const galois_b200_ctx* ctx, const void* w, const galois_d
     if ((uintptr_t)w % 16 != 0) return false;  // rows must start on 16-byte boundaries for the bulk copies
     if (wd->ne[2] != 1 || wd->ne[3] != 1 || xd->ne[2] != 1 || xd->ne[3] != 1) return false;
     if (wd->nb[1] != K / GB_QK) return false;
-    if (xd->ne[1] < 1 || xd->ne[1] > 4) return false;
+    if (xd->ne[1] != 1) return false;  // two rows and more take the skinny MMA kernel
     if (dd->nb[1] > (1 << 30) || xd->nb[1] > (1 << 30)) return false;
     if ((uintptr_t)x % 16 != 0 || xd->nb[1] % 4 != 0) return false;  // float4 loads in the quantiser
     return plan_gemv(ctx, K, N, xd->ne[1]).ok;

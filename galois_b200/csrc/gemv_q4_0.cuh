@@ -6,7 +6,7 @@
 // Sets the shared-memory limit of every kernel instance on the current device.
 int gb_gemv_init(galois_b200_ctx* ctx);
 // True when the streaming GEMV can take this problem: 2-D contiguous weights with 16-byte
-// aligned rows (K % 256 == 0), batch <= 4, 16-byte aligned f32 activations.
+// aligned rows (K % 256 == 0), one activation row, 16-byte aligned f32 activations.
 bool gb_gemv_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
                        const galois_dim* dd);
 // One launch: quantises x inside the kernel and runs the GEMV (cluster launch, with programmatic

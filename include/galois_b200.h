@@ -73,7 +73,7 @@ const char* galois_b200_last_error(galois_b200_ctx* ctx);
 /* Number of kernels this context has launched so far (for benches). */
 int64_t galois_b200_launch_count(galois_b200_ctx* ctx);
 /* Selects among equivalent implementations of the Q4_0 mat-mul:
- * 0 = automatic, 1 = generic direct-load kernel, 2 = bulk-copy streaming GEMV (batch <= 8),
+ * 0 = automatic, 1 = generic direct-load kernel, 2 = bulk-copy streaming GEMV (one activation row),
  * 3 = tensor-core (tcgen05) GEMM, 4 = skinny mma.sync kernel (batch <= 192).  Unsupported shapes for a forced variant
  * return GALOIS_B200_E_LAYOUT. */
 int galois_b200_set_mul_mat_variant(galois_b200_ctx* ctx, int variant);

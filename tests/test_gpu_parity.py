@@ -125,12 +125,9 @@ def test_mul_mat_q4_0_direct(gb, dev, oracle, n, k, b):
     _mul_mat_case(gb, dev, oracle, n, k, b, 7000 + n + k + b, 1)
 
 
-# variant 2 = bulk-copy streaming kernels (K % 256 == 0): fused-quantiser GEMV for batch <= 2,
-# streaming GEMV on pre-quantised activations for batch 3-4, wide-batch kernel for 5-8
-@pytest.mark.parametrize("n,k,b", [(4096, 4096, 1), (11008, 4096, 1), (4096, 11008, 1), (11008, 4096, 2), (11008, 4096, 4),
-                                   (4096, 11008, 2), (4096, 11008, 4), (1, 256, 1), (3, 256, 2), (77, 512, 1), (1185, 512, 3),
-                                   (130, 1024, 1), (131, 2048, 2), (2371, 4096, 4), (2371, 4096, 5), (301, 5120, 1), (300, 768, 2),
-                                   (149, 8192, 1), (149, 8192, 3), (149, 8192, 7), (500, 14336, 1), (32000, 4096, 8)])
+# variant 2 = the streaming GEMV (K % 256 == 0, one activation row; in-kernel cluster-cooperative quantiser)
+@pytest.mark.parametrize("n,k,b", [(4096, 4096, 1), (11008, 4096, 1), (4096, 11008, 1), (1, 256, 1), (77, 512, 1), (130, 1024, 1),
+                                   (301, 5120, 1), (149, 8192, 1), (500, 14336, 1), (32000, 4096, 1), (3, 16384, 1)])
 def test_mul_mat_q4_0_streaming(gb, dev, oracle, n, k, b):
     _mul_mat_case(gb, dev, oracle, n, k, b, 8000 + n + k + b, 2)
 
@@ -173,6 +170,7 @@ def test_mul_mat_q4_0_tensor_core(gb, dev, oracle, n, k, b):
 @pytest.mark.parametrize("n,k,b", [(11008, 4096, 4), (4096, 11008, 8), (11008, 4096, 8), (4096, 11008, 4), (32000, 4096, 16),
                                    (16, 256, 2), (1, 256, 1), (17, 512, 3), (1185, 512, 9), (2371, 4096, 16), (149, 8192, 5),
                                    (300, 768, 12), (31, 1024, 7), (4096, 4096, 1), (500, 14336, 6), (15, 2048, 13), (4096, 4096, 37),
+                                   (11008, 4096, 2), (4096, 11008, 2), (3, 256, 2), (131, 2048, 2), (2371, 4096, 5), (149, 8192, 3), (32000, 4096, 8),
                                    (200, 768, 96), (1000, 11008, 65), (128, 256, 192), (77, 512, 130)])
 def test_mul_mat_q4_0_skinny(gb, dev, oracle, n, k, b):
     _mul_mat_case(gb, dev, oracle, n, k, b, 9700 + n + k + b, 4)
