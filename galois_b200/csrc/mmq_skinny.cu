@@ -1,5 +1,6 @@
 // Skinny Q4_0 x Q8_0 mat-mul for 2..16 activation rows per pass (up to 192 rows in passes of
-// 16): the weights stream once from HBM and the per-block integer dot products run on the warp-level int8 tensor-core instruction
+// 16): the weights stream once from HBM and the per-block integer dot products run on the
+// warp-level int8 tensor-core instruction
 // (mma.sync m16n8k32, u8 x s8 -> s32), 16 weight rows x 8 activation rows x one 32-element block
 // per instruction.  The mat-mul stays HBM-bound work; the MMA only replaces the dp4a sequence
 // whose shared-memory reads of the activations grow with the batch.
