@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
 
-Workload (BASELINE config 2): gate / up 11008x4096 and down 4096x11008 Q4_0 weights,
+Workload (config 2 of the benchmark): gate / up 11008x4096 and down 4096x11008 Q4_0 weights,
 seeded N(0, 0.02) synthetic values, f32 N(0, 1) activations at batch B (default 1).
 A *step* is one pass over a pool of `--sets` distinct FFN weight sets (3 mat-muls per
 set); the pool is larger than the 126 MB L2 several times over, so every weight byte
@@ -45,8 +45,11 @@ def ffn_shapes():
 
 # ----------------------------------------------------------------------------- synthetic data
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q4_0_kernel launch at config 2, batch 1 (ncu capture,
-# mean of the gate/up and down instances: 25 423 872 and 25 453 312 bytes read, 0 written)
+# mean of the gate/up and down instances: 25 423 872 and 25 453 312 bytes read, 0 written).  A citation of the
+# capture summarised in profiles/gemv_q4_0_config2_batch1.md, not a live measurement: NCU_CAPTURE_OF names the
+# kernel revision it was taken on (the weight streaming of the kernel has not changed since).
 NCU_DRAM_BYTES_PER_LAUNCH = (2 * 25423872 + 25453312) / 3.0
+NCU_CAPTURE_OF = "gemv_q4_0_kernel as of commit c7c2a0d"
 
 
 def make_q4_0(n: int, k: int, seed: int, device):
@@ -180,6 +183,7 @@ def run_reference(args):
     import oracle as O
 
     O.build()
+    build_kind = O.use_native_build()  # -march=native on this host, as the reference's README flags ask
     nsets = 4  # 304 MB of weights: larger than any host L3
     sets_host, xs = make_host_sets(nsets, args.batch)
     bytes_pass = nsets * sum(algorithmic_bytes(n, k, args.batch) for _, n, k in ffn_shapes())
@@ -194,12 +198,13 @@ def run_reference(args):
     sample = f"{nsets} FFN weight sets ({nsets * 3} mat-muls, {bytes_pass / 1e6:.0f} MB) per step at batch {args.batch}"
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak",
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": {"workload": "config2: LLaMA-7B FFN decode skinny-GEMM, gate/up 11008x4096 + down 4096x11008, Q4_0 x Q8_0",
                    "batch": args.batch, "sets_per_step": nsets},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": nth, "kind": "port", "sample": sample,
-                         "host_cpus": os.cpu_count()},
+                         "host_cpus": os.cpu_count(), "build": f"g++ -O3 -mavx2 -mfma -mf16c ({build_kind})",
+                         "parity": "unpinned: the reference cannot be built here (no Rust toolchain); C++ restatement"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -298,6 +303,49 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # ---- N > 1, outside the timed region: the sharded call against the same rank's unsharded mat-mul, bit for bit
+    exchange_check = None
+    if peer_exchange:
+        from galois_b200.shard import PeerArena, PeerInbox, band_slots, inbox_bytes
+
+        cases, ok = [], True
+        ck_slots = max(band_slots(n, world, 16) for _, n, _ in shapes)
+        ck_arena = PeerArena(dev, inbox_bytes(world, ck_slots) + 4096)
+        ck_inbox = PeerInbox(ck_arena, ck_slots)
+        for ci, (n, k) in enumerate(((FFN, HIDDEN), (HIDDEN, FFN))):
+            w_full = make_q4_0(n, k, 515000 + ci, device)  # the same seed on every rank: the same full matrix
+            r0, nr = shard_rows(n, world, rank)
+            row_bytes = k // 32 * 18
+            w_band = w_full[r0 * row_bytes:(r0 + nr) * row_bytes].clone()
+            wd_full = gb.Dim.ggml((k, n), gb.GGmlType.Q4_0).c_struct()
+            wd_band = gb.Dim.ggml((k, nr), gb.GGmlType.Q4_0).c_struct()
+            for bb in (1, 8, 16):
+                gx = torch.Generator(device=device)
+                gx.manual_seed(516000 + bb)
+                xb = torch.randn(bb, k, generator=gx, device=device, dtype=torch.float32)
+                xd_, yd_ = gb.Dim.ggml((k, bb), gb.GGmlType.F32).c_struct(), gb.Dim.ggml((n, bb), gb.GGmlType.F32).c_struct()
+                want = torch.zeros(bb, n, device=device, dtype=torch.float32)
+                got = torch.full((bb, n), -1.0, device=device, dtype=torch.float32)
+                rc = lib.galois_b200_mul_mat_q4_0_f32(ctx, C.c_void_p(w_full.data_ptr()), C.byref(wd_full), C.c_void_p(xb.data_ptr()), C.byref(xd_),
+                                                      C.c_void_p(want.data_ptr()), C.byref(yd_))
+                if rc == 0:
+                    rc = lib.galois_b200_mul_mat_q4_0_f32_gather(ctx, C.c_void_p(w_band.data_ptr()), C.byref(wd_band), C.c_void_p(xb.data_ptr()),
+                                                                 C.byref(xd_), C.c_void_p(got.data_ptr()), C.byref(yd_), r0, C.byref(ck_inbox.peers),
+                                                                 ck_inbox.next_epoch())
+                if rc != 0:
+                    raise RuntimeError(f"exchange check failed to launch: {lib.galois_b200_last_error(ctx)} ({rc})")
+                dev.synchronize()
+                same = bool(torch.equal(got.view(torch.int32), want.view(torch.int32)))
+                ok = ok and same
+                cases.append({"n": n, "k": k, "batch": bb, "bit_identical": same})
+            del w_full, w_band
+        flag = torch.tensor([1 if ok else 0], device=device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        exchange_check = {"ok": bool(flag.item() == 1), "cases": len(cases), "detail_rank0": cases,
+                          "what": "gathered [B][N] of the sharded call == the same rank's unsharded mat-mul, compared as bits, on every rank"}
+        dev.synchronize()
+        ck_arena.close()
+
     sampler = ClockSampler(local_rank)
     for _ in range(max(3, args.warmup)):
         step()
@@ -306,6 +354,7 @@ def run_ours(args):
     # ---- `value`: whole-job throughput, inputs resident in HBM; one CUDA graph per step at N = 1
     use_graph = world == 1 and not args.no_graph  # the sharded step (with its NCCL all-gathers) runs as plain stream launches
     launches0 = dev.launch_count()
+    modes0 = dev.overlap_counts()
     if use_graph:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
@@ -316,6 +365,7 @@ def run_ours(args):
         step()
         launches_step = dev.launch_count() - launches0
         run_step = step
+    modes_step = dict(zip(("wait_at_entry", "deferred_wait", "barrier"), (a - b for a, b in zip(dev.overlap_counts(), modes0))))
     for _ in range(max(3, args.warmup)):
         run_step()
     sync_all()
@@ -434,7 +484,7 @@ def run_ours(args):
                                       "flow": "galois_b200_mul_mat_q4_0_f32_host per mat-mul: upload, kernel, result, synchronise"}
     sampler.stop()
 
-    # ---- other BASELINE configs measured beside the headline (N = 1 only; reported under "extra")
+    # ---- the other configurations of the benchmark measured beside the headline (N = 1 only; reported under "extra")
     extra = None
     if world == 1 and not args.no_extra:
         extra = {}
@@ -486,6 +536,23 @@ def run_ours(args):
 
         extra["decode_layer"] = measure_layer(False)       # the op-by-op sequence a galois caller writes
         extra["decode_layer_fused"] = measure_layer(True)  # stacked QKV / gate-up weights + two-op fusions, same numbers
+        if not args.no_cpu:
+            # the same layer step on the CPU oracle (the reference's op sequence, mat-muls on its 4 fixed tasks)
+            import oracle as O2
+            from oracle.layer import make_layer_inputs, oracle_layer_step
+
+            O2.build()
+            O2.use_native_build()
+            li = make_layer_inputs(O2, shp, 4000)
+            oracle_layer_step(O2, shp, *li, shp.ctx - 1)  # appends to its caches in place, at the same position every time
+            t0, reps = time.perf_counter(), 0
+            while reps < 3 or time.perf_counter() - t0 < 2.0:
+                oracle_layer_step(O2, shp, *li, shp.ctx - 1)
+                reps += 1
+            cpu_layer_us = (time.perf_counter() - t0) / reps * 1e6
+            for key in ("decode_layer", "decode_layer_fused"):
+                extra[key]["cpu_us_4thr"] = cpu_layer_us
+                extra[key]["host_cpus"] = os.cpu_count()
         # config 3: prefill 4096 x 4096 x 512 tokens on the tcgen05 int8 path; config 2 at batch 4 and 8
         def time_mm(n, k, b, copies):
             ws = [make_q4_0(n, k, 33000 + c, device) for c in range(copies)]
@@ -515,22 +582,102 @@ def run_ours(args):
             torch.cuda.synchronize()
             return e0.elapsed_time(e1) * 1e3 / (10 * copies)
 
+        # CPU arm beside every row: the oracle's restatement of MatMul::f_q_f32_f32, the reference's fixed 4 tasks
+        # (src/op.rs:1438) and an all-cores variant, built -march=native on this host (README.md:33), bounded samples
+        import oracle as O
+
+        O.build()
+        cpu_build = "skipped" if args.no_cpu else O.use_native_build()
+        ncpu = os.cpu_count() or 1
+
+        def cpu_mm_us(n, k, b):
+            if args.no_cpu:
+                return None, None
+            wh = make_q4_0(n, k, 34000, torch.device("cpu")).numpy().reshape(n, -1)
+            xh = torch.randn(b, k).numpy().astype(np.float32)
+            res = []
+            for nth in (4, ncpu):
+                O.mul_mat_q4_0(wh, xh, nth=nth, avx=True)
+                t0, reps = time.perf_counter(), 0
+                while reps < 2 or (time.perf_counter() - t0 < 0.5 and reps < 50):
+                    O.mul_mat_q4_0(wh, xh, nth=nth, avx=True)
+                    reps += 1
+                res.append((time.perf_counter() - t0) / reps * 1e6)
+            return res[0], res[1]
+
+        def row(config, n, k, b, us, **more):
+            ab = algorithmic_bytes(n, k, b)
+            c4, call = cpu_mm_us(n, k, b)
+            r = {"config": config, "us": us, "hbm_gbs": ab / us / 1e3, "frac_of_measured": ab / us / 1e3 / peak, "algorithmic_bytes": ab,
+                 "cpu_us_4thr": c4, "cpu_us_all_cores": call, "host_cpus": ncpu}
+            r.update(more)
+            return r
+
+        extra["cpu_build"] = f"oracle port, g++ -O3 -mavx2 -mfma -mf16c, {cpu_build}; parity unpinned (the reference cannot be built here)"
+        extra["config1_batch1"] = row("config1: 4096 x 4096 Q4_0 mat-vec, one activation row", 4096, 4096, 1, time_mm(4096, 4096, 1, 40))
         us = time_mm(4096, 4096, 512, 16)
         ops = 2.0 * 512 * 4096 * 4096
-        extra["prefill"] = {"config": "config3: 4096 x 4096 Q4_0 weight x 512 tokens, tcgen05 kind::i8", "us": us,
-                            "int8_tops": ops / us / 1e6, "frac_of_4500_nominal_int8_tops": ops / us / 1e6 / 4500.0,
-                            "hbm_gbs": algorithmic_bytes(4096, 4096, 512) / us / 1e3}
-        for bb in (4, 8):
+        extra["prefill"] = row("config3: 4096 x 4096 Q4_0 weight x 512 tokens, tcgen05 kind::i8", 4096, 4096, 512, us, int8_tops=ops / us / 1e6,
+                               frac_of_4500_nominal_int8_tops=ops / us / 1e6 / 4500.0)
+        for bb in (1, 4, 8):
             us_g, us_d = time_mm(FFN, HIDDEN, bb, 16), time_mm(HIDDEN, FFN, bb, 16)
             ab = algorithmic_bytes(FFN, HIDDEN, bb)
-            extra[f"config2_batch{bb}"] = {"us_gate_up": us_g, "us_down": us_d, "hbm_gbs": 3 * ab / (2 * us_g + us_d) / 1e3}
+            cg4, cga = cpu_mm_us(FFN, HIDDEN, bb)
+            cd4, cda = cpu_mm_us(HIDDEN, FFN, bb)
+            extra[f"config2_batch{bb}"] = {"config": f"config2: gate/up 11008 x 4096 and down 4096 x 11008 at batch {bb}, each shape alone over 16 weights",
+                                           "us_gate_up": us_g, "us_down": us_d, "hbm_gbs": 3 * ab / (2 * us_g + us_d) / 1e3,
+                                           "frac_of_measured": 3 * ab / (2 * us_g + us_d) / 1e3 / peak,
+                                           "cpu_us_4thr_gate_up": cg4, "cpu_us_4thr_down": cd4, "cpu_us_all_cores_gate_up": cga,
+                                           "cpu_us_all_cores_down": cda, "host_cpus": ncpu}
         us_s = time_mm(2 * FFN, HIDDEN, 1, 12)
         extra["config2_stacked_gate_up_batch1"] = {"us": us_s, "hbm_gbs": algorithmic_bytes(2 * FFN, HIDDEN, 1) / us_s / 1e3,
                                                    "note": "gate and up rows stacked into one 22016 x 4096 weight: one launch for both"}
-        us_h = time_mm(32000, 4096, 16, 8)
-        extra["config5_head_batch16"] = {"us": us_h, "hbm_gbs": algorithmic_bytes(32000, 4096, 16) / us_h / 1e3}
-        us_f = time_mm(28672, 8192, 16, 4)
-        extra["config5_ffn70b_batch16"] = {"us": us_f, "hbm_gbs": algorithmic_bytes(28672, 8192, 16) / us_f / 1e3}
+        extra["config5_head_batch16"] = row("config5: output head 32000 x 4096 at batch 16", 32000, 4096, 16, time_mm(32000, 4096, 16, 8))
+        extra["config5_ffn70b_batch16"] = row("config5: 70B-shape FFN 28672 x 8192 at batch 16", 28672, 8192, 16, time_mm(28672, 8192, 16, 4))
+        # the headline step again with the overlap of independent mat-vecs switched off: every kernel waits for the
+        # kernel in front of it at entry, as if each mat-mul consumed its predecessor's result
+        lib.galois_b200_set_overlap(ctx, 0)
+        gs = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gs, stream=stream):
+            step()
+        for _ in range(3):
+            gs.replay()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(max(10, args.steps // 4)):
+            gs.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        lib.galois_b200_set_overlap(ctx, 1)
+        us_strict = e0.elapsed_time(e1) * 1e3 / (max(10, args.steps // 4) * calls_step)
+        extra["config2_batch1_strict_stream_order"] = {
+            "us_per_mat_mul": us_strict, "hbm_gbs": local_bytes_call / us_strict / 1e3, "frac_of_measured": local_bytes_call / us_strict / 1e3 / peak,
+            "note": "galois_b200_set_overlap(0): the same 48 mat-vecs, each waiting at entry for the one before it (a truly dependent chain)"}
+        # one launch over more than 1 GB of rows: what the GEMV kernel sustains once launch boundaries are out of the picture
+        n_big = 524288  # x 2304 bytes per row of K = 4096 = 1.2 GB
+        w_big = make_q4_0(n_big, HIDDEN, 36000, device)
+        wd_big = gb.Dim.ggml((HIDDEN, n_big), gb.GGmlType.Q4_0).c_struct()
+        y_big = torch.zeros(1, n_big, device=device, dtype=torch.float32)
+        yd_big = gb.Dim.ggml((n_big, 1), gb.GGmlType.F32).c_struct()
+
+        def big():
+            rc = lib.galois_b200_mul_mat_q4_0_f32(ctx, C.c_void_p(w_big.data_ptr()), C.byref(wd_big), C.c_void_p(xs[HIDDEN].data_ptr()),
+                                                  C.byref(xdims[HIDDEN]), C.c_void_p(y_big.data_ptr()), C.byref(yd_big))
+            if rc != 0:
+                raise RuntimeError(f"mul_mat_q4_0 failed: {lib.galois_b200_last_error(ctx)} ({rc})")
+        for _ in range(3):
+            big()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(10):
+            big()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        us_big = e0.elapsed_time(e1) * 1e3 / 10
+        ab_big = algorithmic_bytes(n_big, HIDDEN, 1)
+        extra["gemv_steady_state"] = {"config": f"one launch of gemv_q4_0_kernel over {n_big} x 4096 (1.2 GB of Q4_0 rows), one activation row",
+                                      "us": us_big, "hbm_gbs": ab_big / us_big / 1e3, "frac_of_measured": ab_big / us_big / 1e3 / peak}
+        del w_big, y_big
 
     # ---- N > 1: the config-5 shapes (output head, 70B FFN; batch 16) row-sharded with the fused exchange
     if peer_exchange and not args.no_extra:
@@ -590,20 +737,24 @@ def run_ours(args):
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": max(3, args.warmup),
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "u8", "data": "synthetic",
             "config": {"workload": "config2: LLaMA-7B FFN decode skinny-GEMM, gate/up 11008x4096 + down 4096x11008, Q4_0 x Q8_0",
                        "batch": B, "sets_per_step": nsets, "mat_muls_per_step": calls_step,
                        "weight_bytes_resident_per_gpu": weight_bytes,
                        "l2": f"inputs larger than L2: {weight_bytes / L2_BYTES:.1f}x the 126 MB L2 streamed between reuses",
                        "launch": "cuda_graph" if use_graph else "stream",
+                       "ordering": "stream order kept; one-row mat-vecs whose input no kernel in flight writes defer their wait "
+                                   "for the kernels in front of them to their first store (galois_b200_set_overlap, default on); "
+                                   "extra.config2_batch1_strict_stream_order has the same step with every kernel waiting at entry",
+                       "one_row_kernels_per_step_by_ordering": modes_step,
                        "parallelism": (f"rows/{world} + " + ("packet exchange over NVLink peer memory fused into the mat-mul kernel" if peer_exchange else "nccl all_gather"))
                        if world > 1 else "single gpu"},
             "roofline": {"bound": "hbm", "kernel": "gemv_q4_0_kernel" if B <= 1 else ("mmq_skinny_kernel" if B <= 192 else "mm_q4_0_tc_kernel"), "achieved": achieved, "peak": peak, "unit": UNIT,
                          "frac": achieved / peak, "peak_kind": peak_kind,
                          # DRAM bytes per launch from the ncu capture of this kernel on this workload (profiles/): read + write
                          "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (B == 1 and world == 1) else None,
-                         "traffic_source": "ncu --set full capture summarised in profiles/gemv_q4_0_config2_batch1.md" if (B == 1 and world == 1) else None,
+                         "traffic_source": f"ncu --set full capture summarised in profiles/gemv_q4_0_config2_batch1.md ({NCU_CAPTURE_OF})" if (B == 1 and world == 1) else None,
                          "kernel_us": kernel_ms * 1e3, "algorithmic_bytes_per_launch": local_bytes_call,
                          "timed_launches": calls_step * args.steps, "launches_per_mat_mul": launches_step / calls_step,
                          "isolated_kernel_us": isolated_ms * 1e3, "isolated_launches": cnt.value, "frac_of_8000_nominal": achieved / 8000.0},
@@ -616,6 +767,8 @@ def run_ours(args):
             line["cpu_baseline"] = cpu
         if extra is not None:
             line["extra"] = extra
+        if exchange_check is not None:
+            line["exchange_check"] = exchange_check
         print(json.dumps(line), flush=True)
     if arena is not None:
         dev.synchronize()  # surfaces a device-side wait that ran out
@@ -623,6 +776,8 @@ def run_ours(args):
     if world > 1:
         dist.destroy_process_group()
     dev.close()
+    if exchange_check is not None and not exchange_check["ok"]:
+        raise SystemExit("exchange check failed: the sharded result differs from the unsharded mat-mul")
 
 
 def main():

@@ -47,6 +47,8 @@ SIGNATURES = {
     "galois_b200_launch_count": ([_P], _I64),
     "galois_b200_set_mul_mat_variant": ([_P, _I], _I),
     "galois_b200_set_pdl": ([_P, _I], _I),
+    "galois_b200_set_overlap": ([_P, _I], _I),
+    "galois_b200_overlap_counts": ([_P, C.POINTER(_I64 * 3)], _I),
     "galois_b200_profile_enable": ([_P, _I], _I),
     "galois_b200_profile_read": ([_P, C.POINTER(C.c_double), C.POINTER(_I64)], _I),
     "galois_b200_alloc": ([_P, _SZ, C.POINTER(_P)], _I),
@@ -54,8 +56,12 @@ SIGNATURES = {
     "galois_b200_htod": ([_P, _P, _P, _SZ], _I),
     "galois_b200_dtoh": ([_P, _P, _P, _SZ], _I),
     "galois_b200_synchronize": ([_P], _I),
+    "galois_b200_reserve_scratch": ([_P, _SZ], _I),
+    "galois_b200_mul_mat_q4_0_scratch_bytes": ([_P, _DP, _DP, C.POINTER(_SZ)], _I),
     "galois_b200_quantize_q8_0": ([_P, _P, _I64, _P, _I64, _I64], _I),
     "galois_b200_block_isums_q4_0_q8_0": ([_P, _P, _P, _I64, _P], _I),
+    "galois_b200_block_isums_q4_0_q8_0_ex": ([_P, _P, _P, _I64, _I, _P], _I),
+    "galois_b200_mul_mat_q4_0_tc_block_isums": ([_P, _P, _DP, _P, _DP, _P, _DP, _P], _I),
     "galois_b200_mul_mat_q4_0_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_mul_mat_q4_0_f32_fused": ([_P, _P, _DP, _P, _DP, C.POINTER(GaloisPrologue), _P, _DP, _P, _DP], _I),
     "galois_b200_mul_mat_q4_0_f32_add": ([_P, _P, _DP, _P, _DP, _P, _DP, _P, _DP], _I),

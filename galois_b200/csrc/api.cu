@@ -23,6 +23,28 @@ int gb_fail(galois_b200_ctx* ctx, int code, const char* fmt, ...) {
     return code;
 }
 
+bool gb_hazard_free(const galois_b200_ctx* ctx, const void* p, size_t bytes) {
+    if (ctx->hazard_unknown) return false;
+    const uintptr_t lo = (uintptr_t)p, hi = lo + bytes;
+    for (int i = 0; i < ctx->hazard_n; i++)
+        if (lo < ctx->hazard[i].hi && ctx->hazard[i].lo < hi) return false;
+    return true;
+}
+
+void gb_hazard_note_write(galois_b200_ctx* ctx, const void* p, size_t bytes, bool barrier) {
+    const uintptr_t lo = (uintptr_t)p, hi = lo + bytes;
+    if (barrier) ctx->hazard_unknown = 0, ctx->hazard_n = 0;
+    if (ctx->hazard_unknown) return;
+    for (int i = 0; i < ctx->hazard_n; i++)
+        if (ctx->hazard[i].lo <= lo && hi <= ctx->hazard[i].hi) return;  // already covered
+    if (ctx->hazard_n == GB_HAZARD_MAX) {
+        gb_hazard_reset(ctx);  // too many distinct ranges: the next mat-vec runs in barrier mode and starts a new window
+        return;
+    }
+    ctx->hazard[ctx->hazard_n].lo = lo, ctx->hazard[ctx->hazard_n].hi = hi;
+    ctx->hazard_n++;
+}
+
 int gb_scratch(galois_b200_ctx* ctx, size_t bytes, void** out) {
     if (bytes > ctx->scratch_bytes) {
         // growth: the old arena may still be in use by work already enqueued
@@ -117,18 +139,24 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
     ctx->stream = (cudaStream_t)cu_stream;
     ctx->sm_count = prop.multiProcessorCount;
     ctx->pdl = 1;
-    // optional tuning overrides, e.g. GALOIS_B200_TUNE="warps=16,r=1,stages=2"
+    ctx->hazard_tracking = 1;
+    ctx->hazard_unknown = 1;
+    // optional launch-geometry overrides for experiments, e.g. GALOIS_B200_TUNE="stages=2,smem_kb=56,cps=3":
+    // comma-separated key=value pairs, keys matched whole
     if (const char* t = getenv("GALOIS_B200_TUNE")) {
-        const char* q;
-        if ((q = strstr(t, "warps="))) ctx->tune_warps = atoi(q + 6);
-        if ((q = strstr(t, "r="))) ctx->tune_r = atoi(q + 2);
-        if ((q = strstr(t, "stages="))) ctx->tune_stages = atoi(q + 7);
-        if ((q = strstr(t, "smem_kb="))) ctx->tune_smem_kb = atoi(q + 8);
-        if ((q = strstr(t, "cps="))) ctx->tune_ctas_per_sm = atoi(q + 4);
-        if ((q = strstr(t, "pdl="))) ctx->pdl = atoi(q + 4);
-        if ((q = strstr(t, "cluster="))) ctx->tune_cluster = atoi(q + 8);
-        if ((q = strstr(t, "seg="))) ctx->tune_seg = atoi(q + 4);
-        if ((q = strstr(t, "variant="))) ctx->variant = atoi(q + 8);
+        const struct { const char* key; int* dst; } keys[] = {
+            {"stages", &ctx->tune_stages}, {"smem_kb", &ctx->tune_smem_kb}, {"cps", &ctx->tune_ctas_per_sm}, {"pdl", &ctx->pdl},
+            {"cluster", &ctx->tune_cluster}, {"seg", &ctx->tune_seg}, {"variant", &ctx->variant}, {"overlap", &ctx->hazard_tracking},
+        };
+        while (*t) {
+            const char* end = strchr(t, ',');
+            const size_t len = end ? (size_t)(end - t) : strlen(t);
+            const char* eq = (const char*)memchr(t, '=', len);
+            if (eq)
+                for (const auto& k : keys)
+                    if (strlen(k.key) == (size_t)(eq - t) && strncmp(t, k.key, (size_t)(eq - t)) == 0) *k.dst = atoi(eq + 1);
+            t += len + (end ? 1 : 0);
+        }
     }
 
     // f16 tables of GLOBAL_CPU_DEVICE_CACHE (src/op.rs:227-252): entry i =
@@ -192,9 +220,31 @@ extern "C" int galois_b200_destroy(galois_b200_ctx* ctx) {
     return 0;
 }
 
+extern "C" int galois_b200_reserve_scratch(galois_b200_ctx* ctx, size_t bytes) {
+    GB_CHECK_CTX(ctx);
+    void* p;
+    return gb_scratch(ctx, bytes, &p);
+}
+
+extern "C" int galois_b200_mul_mat_q4_0_scratch_bytes(galois_b200_ctx* ctx, const galois_dim* wd, const galois_dim* xd, size_t* out) {
+    GB_CHECK_CTX(ctx);
+    if (!wd || !xd || !out) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_scratch_bytes: null pointer");
+    if (wd->ne[0] < 0 || wd->ne[0] % GB_QK != 0 || xd->ne[1] < 0 || xd->ne[2] < 0 || xd->ne[3] < 0)
+        return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_scratch_bytes: bad extents");
+    // the largest need of any kernel the dispatcher may pick for these extents
+    size_t need = gb_q8_soa_bytes(wd->ne[0], xd->ne[1] * xd->ne[2] * xd->ne[3]);
+    if (wd->ne[0] % 256 == 0 && xd->ne[1] >= 1) {
+        if (xd->ne[1] <= GB_SKINNY_MAX_BATCH) need = need > gb_mmq_skinny_scratch_bytes(wd, xd) ? need : gb_mmq_skinny_scratch_bytes(wd, xd);
+        need = need > gb_mm_tc_scratch_bytes(wd, xd) ? need : gb_mm_tc_scratch_bytes(wd, xd);
+    }
+    *out = need;
+    return 0;
+}
+
 extern "C" int galois_b200_set_stream(galois_b200_ctx* ctx, void* cu_stream) {
     GB_CHECK_CTX(ctx);
     ctx->stream = (cudaStream_t)cu_stream;
+    gb_hazard_reset(ctx);
     return 0;
 }
 
@@ -231,6 +281,7 @@ extern "C" int galois_b200_htod(galois_b200_ctx* ctx, void* dst_dev, const void*
     if (bytes == 0) return 0;
     if (!dst_dev || !src_host) return gb_fail(ctx, GALOIS_B200_E_BADARG, "htod: null pointer");
     GB_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    gb_hazard_reset(ctx);
     return 0;
 }
 static int check_dev_status(galois_b200_ctx* ctx) {
@@ -248,8 +299,8 @@ extern "C" int galois_b200_dtoh(galois_b200_ctx* ctx, void* dst_host, const void
     if (bytes == 0) return 0;
     if (!dst_host || !src_dev) return gb_fail(ctx, GALOIS_B200_E_BADARG, "dtoh: null pointer");
     GB_CUDA(ctx, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
-    GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    return 0;
+    // synchronises, and reports a bounded device-side wait that ran out in the work the result came from
+    return check_dev_status(ctx);
 }
 extern "C" int galois_b200_synchronize(galois_b200_ctx* ctx) {
     GB_CHECK_CTX(ctx);
@@ -324,6 +375,7 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
         if (!dst) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0: null pointer");
         if (!gb_is_contiguous(dd)) return gb_fail(ctx, GALOIS_B200_E_DST, "mul_mat_q4_0: K == 0 needs a contiguous dst");
         GB_CUDA(ctx, cudaMemsetAsync(dst, 0, (size_t)gb_nelements(dd) * sizeof(float), ctx->stream));
+        gb_hazard_reset(ctx);
         return 0;
     }
     const bool tc_ok = gb_mm_tc_supported(ctx, w, wd, x, xd, dd);
@@ -364,6 +416,34 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
         ctx->prof_n++;
     }
     return rc;
+}
+
+extern "C" int galois_b200_block_isums_q4_0_q8_0_ex(galois_b200_ctx* ctx, const void* w, const void* xq, int64_t nb, int variant,
+                                                    int32_t* out) {
+    GB_CHECK_CTX(ctx);
+    if (variant == 1) return galois_b200_block_isums_q4_0_q8_0(ctx, w, xq, nb, out);
+    if (variant != 2 && variant != 4) return gb_fail(ctx, GALOIS_B200_E_BADARG, "block_isums: variant %d (1, 2 or 4; the tcgen05 path has galois_b200_mul_mat_q4_0_tc_block_isums)", variant);
+    if (nb < 0) return gb_fail(ctx, GALOIS_B200_E_BADARG, "block_isums: negative block count");
+    if (nb == 0) return 0;
+    if (!w || !xq || !out) return gb_fail(ctx, GALOIS_B200_E_BADARG, "block_isums: null pointer");
+    if ((uintptr_t)w % 2 || (uintptr_t)xq % 2) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "block_isums: blocks must be 2-byte aligned");
+    return variant == 2 ? gb_gemv_block_isums(ctx, w, xq, nb, out) : gb_mmq_skinny_block_isums(ctx, w, xq, nb, out);
+}
+
+extern "C" int galois_b200_mul_mat_q4_0_tc_block_isums(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
+                                                       const galois_dim* xd, float* dst, const galois_dim* dd, int32_t* out) {
+    GB_CHECK_CTX(ctx);
+    int rc = gb_validate_mul_mat(ctx, w, wd, x, xd, dst, dd);
+    if (rc) return rc;
+    if (!out) return gb_fail(ctx, GALOIS_B200_E_BADARG, "block_isums_tc: null pointer");
+    if (wd->ne[0] == 0 || wd->ne[1] == 0 || xd->ne[1] == 0) return 0;
+    if (!gb_mm_tc_supported(ctx, w, wd, x, xd, dd)) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "block_isums_tc: shape not supported by the tensor-core kernel");
+    void* scratch = nullptr;
+    galois_dim xpad = *xd;
+    xpad.ne[1] = 64;
+    rc = gb_scratch(ctx, gb_mm_tc_scratch_bytes(wd, &xpad), &scratch);
+    if (rc) return rc;
+    return gb_mm_q4_0_tc_block_isums(ctx, w, wd, x, xd, dst, dd, scratch, out);
 }
 
 // A context-owned buffer for the intermediate of a fused call that has to run as separate ops.
@@ -447,6 +527,21 @@ extern "C" int galois_b200_mul_mat_q4_0_f32_add(galois_b200_ctx* ctx, const void
 extern "C" int galois_b200_set_pdl(galois_b200_ctx* ctx, int on) {
     GB_CHECK_CTX(ctx);
     ctx->pdl = on ? 1 : 0;
+    gb_hazard_reset(ctx);
+    return 0;
+}
+
+extern "C" int galois_b200_overlap_counts(galois_b200_ctx* ctx, int64_t out[3]) {
+    GB_CHECK_CTX(ctx);
+    if (!out) return gb_fail(ctx, GALOIS_B200_E_BADARG, "overlap_counts: null pointer");
+    for (int i = 0; i < 3; i++) out[i] = ctx->sync_counts[i];
+    return 0;
+}
+
+extern "C" int galois_b200_set_overlap(galois_b200_ctx* ctx, int on) {
+    GB_CHECK_CTX(ctx);
+    ctx->hazard_tracking = on ? 1 : 0;
+    gb_hazard_reset(ctx);
     return 0;
 }
 
@@ -514,6 +609,7 @@ extern "C" int galois_b200_mul_mat_q4_0_f32_host(galois_b200_ctx* ctx, const voi
         (void)cudaGetLastError();
     }
     if (xbytes) GB_CUDA(ctx, cudaMemcpyAsync(xdev, x_host, xbytes, cudaMemcpyHostToDevice, ctx->stream));
+    gb_hazard_reset(ctx);
     int rc = galois_b200_mul_mat_q4_0_f32(ctx, w, wd, xdev, xd, ddev, dd);
     if (rc) return rc;
     if (dbytes && !direct) GB_CUDA(ctx, cudaMemcpyAsync(dst_host, ddev, dbytes, cudaMemcpyDeviceToHost, ctx->stream));

@@ -13,6 +13,7 @@
 #define GB_Q4_BYTES 18
 #define GB_Q8_BYTES 34
 #define GB_PROF_MAX 4096
+#define GB_HAZARD_MAX 16
 
 // Context behind the opaque galois_b200_ctx handle.
 struct galois_b200_ctx {
@@ -21,8 +22,15 @@ struct galois_b200_ctx {
     int sm_count;
     int variant;           // forced Q4_0 mat-mul variant (0 = automatic)
     // launch-geometry overrides for the bulk-copy GEMV (0 = automatic), from GALOIS_B200_TUNE
-    int tune_warps, tune_r, tune_stages, tune_smem_kb, tune_ctas_per_sm, tune_cluster, tune_seg;
+    int tune_stages, tune_smem_kb, tune_ctas_per_sm, tune_cluster, tune_seg;
     int pdl;               // launch the streaming kernels with programmatic dependent launch (default on)
+    // Write ranges of the kernels that may still be running when the next kernel of the stream starts
+    // (see gb_hazard_free); hazard_unknown: some kernel in flight may write anywhere.
+    int hazard_tracking;   // 0: every kernel waits for its predecessors at entry (no deferred waits)
+    int hazard_unknown;
+    int hazard_n;
+    int64_t sync_counts[3];  // one-row GEMV launches by ordering mode: wait at entry, deferred wait, barrier
+    struct { uintptr_t lo, hi; } hazard[GB_HAZARD_MAX];
     int64_t launches;      // kernels launched through this context
     // f16 look-up tables (65 536 entries each), device copies
     uint16_t* exp_lut;
@@ -51,6 +59,23 @@ int gb_fail(galois_b200_ctx* ctx, int code, const char* fmt, ...);
 // cudaMalloc when needed; growth synchronises the stream first).
 int gb_scratch(galois_b200_ctx* ctx, size_t bytes, void** out);
 
+// Hazard window of a context.  Kernels launched with programmatic dependent launch start as soon as
+// every CTA of their predecessor has released them, and the kernels of this library do that at
+// entry, before their own wait: when a kernel starts, its predecessor may still be blocked in its
+// wait and the kernels before that may still be running.  Only a kernel that releases its dependents
+// AFTER its wait (the GEMV in barrier mode) guarantees its successor that everything older has
+// completed.  The window therefore lists the write ranges of all kernels launched since the last such
+// barrier; it is "unknown" after any kernel whose writes are not recorded.  Work the library does not
+// launch (the caller's kernels, copies) serialises the stream and only makes the window a superset of
+// the truth.
+//   gb_hazard_free       : the window is known and [p, p + bytes) overlaps none of its ranges
+//   gb_hazard_note_write : a kernel writing [p, p + bytes) was launched; `barrier`: it released its
+//                          dependents after its wait, so the window restarts with this range alone
+//   gb_hazard_reset      : something with unrecorded writes was enqueued (any other kernel, a copy, a new stream)
+bool gb_hazard_free(const galois_b200_ctx* ctx, const void* p, size_t bytes);
+void gb_hazard_note_write(galois_b200_ctx* ctx, const void* p, size_t bytes, bool barrier);
+static inline void gb_hazard_reset(galois_b200_ctx* ctx) { ctx->hazard_unknown = 1, ctx->hazard_n = 0; }
+
 // Argument checks of MatMul::f_q_f32_f32 shared by the mat-mul entry points (0 = valid).
 int gb_validate_mul_mat(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const void* x, const galois_dim* xd,
                         const void* dst, const galois_dim* dd);
@@ -76,6 +101,7 @@ int gb_choose_mul_mat_variant(const galois_b200_ctx* ctx, const void* w, const g
         cudaError_t _e = cudaGetLastError();                                                   \
         if (_e != cudaSuccess) return gb_fail((ctx), (int)_e, "launch of %s: %s", name, cudaGetErrorString(_e)); \
         (ctx)->launches++;                                                                     \
+        gb_hazard_reset(ctx);                                                                  \
     } while (0)
 
 static inline int64_t gb_nelements(const galois_dim* d) { return d->ne[0] * d->ne[1] * d->ne[2] * d->ne[3]; }

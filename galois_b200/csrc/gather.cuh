@@ -4,6 +4,12 @@
 // store into the receiver's inbox, so a packet is its own arrival flag and the sender needs no
 // fence.  A receiver's inbox has two halves used by even and odd epochs; each half has one area
 // of `slots` packets per sender, indexed b * rows_of_the_sender's_band + r.
+//
+// One-wave requirement: a kernel that calls gb_gather_receive from its tail waits for packets that
+// CTAs of the peers' launches send while the peers wait for this launch's packets, so every CTA of
+// such a launch must be resident at the same time (grid <= what the device holds at once).  The
+// launchers clamp their grids with the occupancy calculator; gather_exchange_kernel's grid is
+// bounded by construction.
 #pragma once
 #include "common.cuh"
 

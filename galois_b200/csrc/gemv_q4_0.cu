@@ -15,7 +15,19 @@
 //   * programmatic dependent launch: the kernel releases its dependents at once and prefetches its
 //     first weight stages BEFORE waiting for the kernel in front of it, so launch latency and the
 //     first DRAM round trip hide behind the previous op.  Small CTAs (128 threads, well under half
-//     an SM's shared memory) let CTAs of consecutive kernels share an SM.
+//     an SM's shared memory) let CTAs of consecutive kernels share an SM;
+//   * three ways to order the kernel after its predecessors (`sync_mode`, chosen by the host from
+//     the context's hazard window, common.cuh):
+//       GEMV_SYNC_ENTRY    dependents released at entry, wait before the activations are read;
+//       GEMV_SYNC_DEFERRED no kernel that may still be running writes this call's activations, so
+//                          the kernel quantises, streams and multiplies at once, holds its results
+//                          back in shared memory and waits only before it touches `dst` (and the
+//                          residual): independent mat-muls (gate / up, Q / K / V) stream back to back;
+//       GEMV_SYNC_BARRIER  wait at entry and release the dependents only after the wait, so that
+//                          everything in front of this kernel has completed before its successor
+//                          starts; this is what makes the hazard window known again.
+//     Every warp executes the wait before it exits in all three: the completion of this kernel
+//     implies the completion of everything before it.
 //
 // Numerics: MatMul::f_q_f32_f32::<BlockQ4_0> (src/op.rs:1383-1598) with
 // BlockQ4_0::vec_dot_q8_0 (src/ggml_quants.rs:156-172); only the order of the f32 additions
@@ -33,14 +45,17 @@ namespace {
 constexpr int GEMV_WARPS = GB_GEMV_WARPS;
 constexpr int GEMV_THREADS = GEMV_WARPS * 32;
 constexpr int GEMV_MAX_STAGES = 6;
-constexpr int GEMV_BAR_BYTES = ((GEMV_WARPS * GEMV_MAX_STAGES + 1) * 8 + 16 + 127) & ~127;  // the mbarriers + 4 floats, padded
+enum { GEMV_SYNC_ENTRY = 0, GEMV_SYNC_DEFERRED = 1, GEMV_SYNC_BARRIER = 2 };
+constexpr int GEMV_KEEP = 64;  // results a warp may hold back before its first store (deferred-wait launches)
 constexpr int GEMV_RED_OFFSET = (GEMV_WARPS * GEMV_MAX_STAGES + 1) * 8;  // 4 floats of block-reduction space behind the barriers
+constexpr int GEMV_KEEP_OFFSET = (GEMV_RED_OFFSET + 16 + 15) & ~15;      // GEMV_WARPS * GEMV_KEEP floats of held-back results
+constexpr int GEMV_BAR_BYTES = (GEMV_KEEP_OFFSET + GEMV_WARPS * GEMV_KEEP * 4 + 127) & ~127;  // all of the above, padded
 
 // One 36-byte block pair held as nine aligned words t[0..8] ({d0 | qs0[0:2]}, qs0[2:14],
 // {qs0[14:16] | d1}, qs1[0:16]) against the 64 int8 activations y[0..15] of the same two blocks.
 // ds = {dx0, bits(-8 * sum y0), dx1, bits(-8 * sum y1)}.  High nibbles are used in place
 // (16 * q as an unsigned byte): their dot product is an exact multiple of 16.
-__device__ __forceinline__ float pair_dot(const uint32_t* t, const int* y, const float4 ds, float acc) {
+__device__ __forceinline__ void pair_isums(const uint32_t* t, const int* y, const float4 ds, int& i0, int& i1) {
     int lo0 = 0, hi0 = 0, lo1 = 0, hi1 = 0;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -51,13 +66,43 @@ __device__ __forceinline__ float pair_dot(const uint32_t* t, const int* y, const
         lo1 = dp4a_us(q1 & 0x0F0F0F0Fu, y[8 + i], lo1);
         hi1 = dp4a_us(q1 & 0xF0F0F0F0u, y[12 + i], hi1);
     }
-    const int i0 = lo0 + (hi0 >> 4) + __float_as_int(ds.y);
-    const int i1 = lo1 + (hi1 >> 4) + __float_as_int(ds.w);
+    i0 = lo0 + (hi0 >> 4) + __float_as_int(ds.y);
+    i1 = lo1 + (hi1 >> 4) + __float_as_int(ds.w);
+}
+__device__ __forceinline__ float pair_dot(const uint32_t* t, const int* y, const float4 ds, float acc) {
+    int i0, i1;
+    pair_isums(t, y, ds, i0, i1);
     const float dw0 = __half2float(__ushort_as_half((unsigned short)(t[0] & 0xffffu)));
     const float dw1 = __half2float(__ushort_as_half((unsigned short)(t[4] >> 16)));
     acc = fmaf(dw0 * ds.x, (float)i0, acc);
     acc = fmaf(dw1 * ds.z, (float)i1, acc);
     return acc;
+}
+
+// Test hook: the integer sums of pair_isums for block pairs of one weight row against one
+// activation row given as 34-byte Q8_0 blocks (thread = block pair; w 4-byte aligned).
+__global__ void gemv_pair_isums_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ xq, int64_t npairs, int32_t* __restrict__ out) {
+    const int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= npairs) return;
+    uint32_t t[9];
+#pragma unroll
+    for (int i = 0; i < 9; i++) t[i] = reinterpret_cast<const uint32_t*>(w + p * 36)[i];
+    int y[16], s[2] = {0, 0};
+#pragma unroll
+    for (int blk = 0; blk < 2; blk++) {
+        const int8_t* q = reinterpret_cast<const int8_t*>(xq + (2 * p + blk) * GB_Q8_BYTES + 2);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint32_t v = (uint32_t)(uint8_t)q[4 * i] | ((uint32_t)(uint8_t)q[4 * i + 1] << 8) | ((uint32_t)(uint8_t)q[4 * i + 2] << 16) |
+                               ((uint32_t)(uint8_t)q[4 * i + 3] << 24);
+            y[8 * blk + i] = (int)v;
+            s[blk] += q[4 * i] + q[4 * i + 1] + q[4 * i + 2] + q[4 * i + 3];
+        }
+    }
+    int i0, i1;
+    pair_isums(t, y, make_float4(0.f, __int_as_float(-8 * s[0]), 0.f, __int_as_float(-8 * s[1])), i0, i1);
+    out[2 * p] = i0;
+    out[2 * p + 1] = i1;
 }
 
 // Loads the 36 * SEG bytes of one lane segment into 9 * SEG words with the widest aligned load.
@@ -208,9 +253,10 @@ template <int NB, int SEG, bool SPLIT, int NPASS>
 __global__ void __launch_bounds__(GEMV_THREADS)
     gemv_q4_0_kernel(const uint8_t* __restrict__ w, const float* __restrict__ x, int x_stride, float* __restrict__ dst, int nb1, int K, int N, int nbatch, int stages,
                      int* __restrict__ status, const gb_gather_args G, const float* __restrict__ res, int res_nb1,
-                     int pro_kind, const float* __restrict__ pro_aux, float pro_eps, const uint16_t* __restrict__ silu_lut) {
+                     int pro_kind, const float* __restrict__ pro_aux, float pro_eps, const uint16_t* __restrict__ silu_lut, int sync_mode) {
     extern __shared__ __align__(128) uint8_t smem[];
-    pdl_launch_dependents();
+    const bool late_wait = sync_mode == GEMV_SYNC_DEFERRED;
+    if (sync_mode != GEMV_SYNC_BARRIER) pdl_launch_dependents();
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nblk = K >> 5;
@@ -254,8 +300,9 @@ __global__ void __launch_bounds__(GEMV_THREADS)
     const uint32_t crank = cluster_ctarank(), csize = cluster_nctarank();
     __syncwarp();
     cluster_arrive_relaxed();  // this CTA's shared memory and act_bar exist
-    pdl_wait();                // the activations (and whatever dst aliases) belong to the preceding kernels
-    cluster_wait();            // so do every peer's
+    if (!late_wait) pdl_wait();  // the activations (and whatever dst aliases) belong to the preceding kernels
+    if (sync_mode == GEMV_SYNC_BARRIER) pdl_launch_dependents();
+    cluster_wait();              // every peer's shared memory and act_bar exist
     gemv_prologue pro = {pro_kind, pro_aux, 1.0f, silu_lut};
     if (NB == 1 && GEMV_THREADS == 128 && pro_kind == 1) {
         // rms_norm's scale of the row, every CTA for itself (the row is a few KB and sits in L2), in the
@@ -282,6 +329,23 @@ __global__ void __launch_bounds__(GEMV_THREADS)
             }
         }
     }
+
+    // deferred-wait launches (one activation row): results of chunks [j0, j0 + n) of this warp sit in keep[]
+    float* keep = reinterpret_cast<float*>(smem + GEMV_KEEP_OFFSET) + warp * GEMV_KEEP;
+    int kept = 0, done = 0;
+    auto flush_kept = [&](int j0, int n) {
+        pdl_wait();  // from here on dst and the residual belong to this kernel
+        __syncwarp();
+        for (int i = lane; i < n * rows_per_chunk; i += 32) {
+            const int row = (gw + (j0 + i / rows_per_chunk) * tw) * rows_per_chunk + i % rows_per_chunk;
+            if (row < N) {
+                float v = keep[i];
+                if (res) v = __fadd_rn(res[row], v);
+                dst[row] = v;
+            }
+        }
+        __syncwarp();
+    };
 
     for (int j = 0; j < my_chunks && ok; j++) {
         const int s = j % stages;
@@ -323,7 +387,22 @@ __global__ void __launch_bounds__(GEMV_THREADS)
         __syncwarp();
         if (lane == 0 && j + stages < my_chunks) issue(j + stages, s);
 
-        if (SPLIT) {
+        if (late_wait) {
+            // hold the chunk's results back: nothing of dst is touched before the dependency wait
+            if (SPLIT) {
+                float v = acc[0];
+                for (int o = nsegk >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if ((lane & (nsegk - 1)) == 0) keep[kept * rows_per_chunk + lane / nsegk] = v;
+            } else {
+                const float v = gb_warp_sum(acc[0]);
+                if (lane == 0) keep[kept] = v;
+            }
+            kept++;
+            if ((kept + 1) * rows_per_chunk > GEMV_KEEP) {
+                flush_kept(j + 1 - kept, kept);
+                kept = 0;
+            }
+        } else if (SPLIT) {
             // lanes [r * nsegk, (r + 1) * nsegk) hold row r of the chunk
             const int r = lane / nsegk;
 #pragma unroll
@@ -347,6 +426,11 @@ __global__ void __launch_bounds__(GEMV_THREADS)
                 }
             }
         }
+        done = j + 1;
+    }
+    if (late_wait) {
+        if (kept) flush_kept(done - kept, kept);
+        pdl_wait();  // every warp, also one without rows: this kernel completes after the kernels in front of it
     }
     if (!ok && lane == 0) atomicExch(status, GALOIS_B200_E_TIMEOUT);
     // sharded call: every result went to the peers' inboxes as well; now collect the peers' bands
@@ -431,7 +515,7 @@ cudaError_t gemv_attr() {
 
 template <int NB, int SEG, bool SPLIT, int NPASS>
 int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, const float* x, int x_stride, float* dst, int nb1,
-                int K, int N, int B, const gb_gather_args& gather, const gb_gemv_extra& ex) {
+                int K, int N, int B, const gb_gather_args& gather, const gb_gemv_extra& ex, int sync_mode) {
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute at[2];
     int na = 0;
@@ -451,10 +535,27 @@ int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, cons
     cfg.gridDim = dim3((unsigned)p.grid);
     cfg.blockDim = dim3(GEMV_THREADS);
     cfg.dynamicSmemBytes = p.smem;
+    if (gather.P.nranks > 0) {
+        // The exchange in the kernel's tail polls for packets that other CTAs of the PEER's launch send, and
+        // the peer's CTAs poll for ours: every CTA of the launch must be resident at once, or first-wave CTAs
+        // wait for packets only a second wave would send.  Clamp the grid to what the device holds at the
+        // same time (the kernel deals its chunks round-robin over whatever grid it gets).
+        static int c_dev = -1, c_cluster = 0, c_max = 0;
+        static size_t c_smem = 0;
+        if (c_dev != ctx->ordinal || c_cluster != p.cluster || c_smem != p.smem) {
+            int maxc = 0;
+            GB_CUDA(ctx, cudaOccupancyMaxActiveClusters(&maxc, gemv_q4_0_kernel<NB, SEG, SPLIT, NPASS>, &cfg));
+            c_dev = ctx->ordinal, c_cluster = p.cluster, c_smem = p.smem, c_max = maxc;
+        }
+        if (c_max < 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: no cluster of the sharded GEMV fits on the device");
+        if ((int)cfg.gridDim.x > c_max * p.cluster) cfg.gridDim.x = (unsigned)(c_max * p.cluster);
+    }
     GB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_0_kernel<NB, SEG, SPLIT, NPASS>, w, x, x_stride, dst, nb1, K, N, B, p.stages,
                                     ctx->dev_status, gather, ex.res, (int)ex.res_nb1, ex.pro_kind, ex.pro_aux, ex.pro_eps,
-                                    ctx->silu_lut));
+                                    ctx->silu_lut, sync_mode));
     ctx->launches++;
+    ctx->sync_counts[sync_mode]++;
+    gb_hazard_note_write(ctx, dst, (size_t)N * sizeof(float), sync_mode == GEMV_SYNC_BARRIER);
     return 0;
 }
 
@@ -468,6 +569,13 @@ int gb_gemv_init(galois_b200_ctx* ctx) {
 }
 
 bool gb_gemv_has_prologue() { return GEMV_THREADS == 128; }
+
+int gb_gemv_block_isums(galois_b200_ctx* ctx, const void* w, const void* xq, int64_t nb, int32_t* out) {
+    if (nb % 2 != 0 || (uintptr_t)w % 4 != 0) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "block_isums: the GEMV path takes block pairs from a 4-byte aligned row");
+    gemv_pair_isums_kernel<<<(unsigned)((nb / 2 + 127) / 128), 128, 0, ctx->stream>>>((const uint8_t*)w, (const uint8_t*)xq, nb / 2, out);
+    GB_LAUNCHED(ctx, "gemv_pair_isums");
+    return 0;
+}
 
 bool gb_gemv_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
                        const galois_dim* dd) {
@@ -497,9 +605,22 @@ int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* w
     if (!p.ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: shape not supported by the streaming GEMV");
     const uint8_t* wb = (const uint8_t*)w;
     const int nb1 = (int)dd->nb[1], xs = (int)xd->nb[1];
+    // How this launch orders itself after the kernels in front of it (see the header comment).  A deferred
+    // wait reads x (and the prologue's second operand) before any wait, which is safe only when no kernel
+    // that may still be running writes those ranges; the residual and dst are touched after the wait and
+    // need no check.  Sharded calls keep the wait at entry.
+    int sync_mode = GEMV_SYNC_ENTRY;
+    if (ctx->pdl && ctx->hazard_tracking && gather->P.nranks == 0 && B == 1) {
+        if (ctx->hazard_unknown)
+            sync_mode = GEMV_SYNC_BARRIER;
+        else if (gb_hazard_free(ctx, x, (size_t)K * sizeof(float)) && (ex.pro_kind == 0 || gb_hazard_free(ctx, ex.pro_aux, (size_t)K * sizeof(float))))
+            sync_mode = GEMV_SYNC_DEFERRED;
+    } else {
+        gb_hazard_reset(ctx);
+    }
 #define X(NB_, SEG_, SPLIT_, NP_)                                                   \
     if (p.nbt == NB_ && p.seg == SEG_ && p.split == SPLIT_ && p.npass == NP_)       \
-        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, x, xs, dst, nb1, K, N, B, *gather, ex);
+        return launch_gemv<NB_, SEG_, SPLIT_, NP_>(ctx, p, wb, x, xs, dst, nb1, K, N, B, *gather, ex, sync_mode);
     GB_GEMV_INSTANCES(X)
 #undef X
     return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: no streaming-GEMV instance for this shape");

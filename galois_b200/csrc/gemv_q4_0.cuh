@@ -31,3 +31,6 @@ int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* w
                         const galois_dim* dd, const gb_gather_args* gather, const gb_gemv_extra* extra);
 // True when the GEMV was built with the 128-thread CTAs the in-kernel rms_norm needs.
 bool gb_gemv_has_prologue();
+// Test hook: per-block integer sums as the GEMV's dp4a sequence forms them (nb even, w 4-byte aligned;
+// xq in the 34-byte Q8_0 format).
+int gb_gemv_block_isums(galois_b200_ctx* ctx, const void* w, const void* xq, int64_t nb, int32_t* out);

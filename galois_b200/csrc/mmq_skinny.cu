@@ -86,28 +86,55 @@ __global__ void __launch_bounds__(256) quantize_q8_frag_kernel(const float* __re
     }
 }
 
-// One block of 16 weight rows (fragment words qa for row g, qb for row g + 8; scales dwa, dwb)
-// against NT n-tiles of activations (fragments bf, {d, m} pairs sc of activation rows 2t, 2t + 1).
+// One block of 16 weight rows (fragment words qa for row g, qb for row g + 8) against one n-tile of
+// activations (fragment bf, {d, m} pairs s of activation rows 2t, 2t + 1): the four integer sums of this
+// lane as exact floats.
+__device__ __forceinline__ void block_isums_f(uint32_t qa, uint32_t qb, const uint2 bf, const float4 s, float (&f)[4]) {
+    const uint32_t a0 = qa & 0x0F0F0F0Fu, a2 = (qa >> 4) & 0x0F0F0F0Fu;
+    const uint32_t a1 = qb & 0x0F0F0F0Fu, a3 = (qb >> 4) & 0x0F0F0F0Fu;
+    int c[4];
+    mma_u8s8(c, a0, a1, a2, a3, bf.x, bf.y);
+    // float(isum) = float(c - 8 * sum q) through the 1.5 * 2^23 trick: exact for |isum| < 2^22
+    f[0] = __int_as_float(c[0] + __float_as_int(s.y)) - SK_MAGIC;
+    f[1] = __int_as_float(c[1] + __float_as_int(s.w)) - SK_MAGIC;
+    f[2] = __int_as_float(c[2] + __float_as_int(s.y)) - SK_MAGIC;
+    f[3] = __int_as_float(c[3] + __float_as_int(s.w)) - SK_MAGIC;
+}
+
+// The same block against NT n-tiles, scaled (dwa, dwb: the weight rows' f16 scales) and accumulated.
 template <int NT>
 __device__ __forceinline__ void block_mma(uint32_t qa, uint32_t qb, float dwa, float dwb, const uint2 (&bf)[NT], const float4 (&sc)[NT],
                                           float (&acc)[NT][4]) {
-    const uint32_t a0 = qa & 0x0F0F0F0Fu, a2 = (qa >> 4) & 0x0F0F0F0Fu;
-    const uint32_t a1 = qb & 0x0F0F0F0Fu, a3 = (qb >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
         const float4 s = sc[nt];
-        int c[4];
-        mma_u8s8(c, a0, a1, a2, a3, bf[nt].x, bf[nt].y);
-        // float(isum) = float(c - 8 * sum q) through the 1.5 * 2^23 trick: exact for |isum| < 2^22
-        const float f0 = __int_as_float(c[0] + __float_as_int(s.y)) - SK_MAGIC;
-        const float f1 = __int_as_float(c[1] + __float_as_int(s.w)) - SK_MAGIC;
-        const float f2 = __int_as_float(c[2] + __float_as_int(s.y)) - SK_MAGIC;
-        const float f3 = __int_as_float(c[3] + __float_as_int(s.w)) - SK_MAGIC;
-        acc[nt][0] = fmaf(dwa * s.x, f0, acc[nt][0]);
-        acc[nt][1] = fmaf(dwa * s.z, f1, acc[nt][1]);
-        acc[nt][2] = fmaf(dwb * s.x, f2, acc[nt][2]);
-        acc[nt][3] = fmaf(dwb * s.z, f3, acc[nt][3]);
+        float f[4];
+        block_isums_f(qa, qb, bf[nt], s, f);
+        acc[nt][0] = fmaf(dwa * s.x, f[0], acc[nt][0]);
+        acc[nt][1] = fmaf(dwa * s.z, f[1], acc[nt][1]);
+        acc[nt][2] = fmaf(dwb * s.x, f[2], acc[nt][2]);
+        acc[nt][3] = fmaf(dwb * s.z, f[3], acc[nt][3]);
     }
+}
+
+// Test hook: the sums of block_isums_f for the blocks of one weight row against one activation row
+// given as 34-byte Q8_0 blocks.  One warp per block; every row of the 16 x 8 tile holds the same data.
+__global__ void skinny_block_isums_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ xq, int64_t nb, int32_t* __restrict__ out) {
+    const int64_t ib = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (ib >= nb) return;
+    const int lane = threadIdx.x & 31, t = lane & 3;
+    const uint8_t* wq = w + ib * GB_Q4_BYTES + 2;
+    const int8_t* q = reinterpret_cast<const int8_t*>(xq + ib * GB_Q8_BYTES + 2);
+    const uint32_t qa = (uint32_t)wq[4 * t] | ((uint32_t)wq[4 * t + 1] << 8) | ((uint32_t)wq[4 * t + 2] << 16) | ((uint32_t)wq[4 * t + 3] << 24);
+    uint2 bf;
+    bf.x = (uint32_t)(uint8_t)q[4 * t] | ((uint32_t)(uint8_t)q[4 * t + 1] << 8) | ((uint32_t)(uint8_t)q[4 * t + 2] << 16) | ((uint32_t)(uint8_t)q[4 * t + 3] << 24);
+    bf.y = (uint32_t)(uint8_t)q[16 + 4 * t] | ((uint32_t)(uint8_t)q[17 + 4 * t] << 8) | ((uint32_t)(uint8_t)q[18 + 4 * t] << 16) | ((uint32_t)(uint8_t)q[19 + 4 * t] << 24);
+    int sum = 0;
+    for (int i = 0; i < 32; i++) sum += q[i];
+    const float m = __int_as_float(SK_MAGIC_INT - 8 * sum);
+    float f[4];
+    block_isums_f(qa, qa, bf, make_float4(0.f, m, 0.f, m), f);
+    if (lane == 0) out[ib] = (int)f[0];
 }
 
 // NP block pairs of one stage: rows g and g + 8 of the tile (ra, rb) against the activations of
@@ -298,6 +325,12 @@ int gb_mmq_skinny_init(galois_b200_ctx* ctx) {
     return 0;
 }
 
+int gb_mmq_skinny_block_isums(galois_b200_ctx* ctx, const void* w, const void* xq, int64_t nb, int32_t* out) {
+    skinny_block_isums_kernel<<<(unsigned)((nb + 3) / 4), 128, 0, ctx->stream>>>((const uint8_t*)w, (const uint8_t*)xq, nb, out);
+    GB_LAUNCHED(ctx, "skinny_block_isums");
+    return 0;
+}
+
 bool gb_mmq_skinny_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
                              const galois_dim* dd) {
     (void)ctx;
@@ -331,7 +364,18 @@ int gb_mmq_skinny(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, con
     // shapes this path takes stay in L2 between passes)
     for (int b0 = 0; b0 < B; b0 += 16) {
         const int bc = B - b0 < 16 ? B - b0 : 16;
-        const skinny_plan p = plan_skinny(ctx, N, bc);
+        skinny_plan p = plan_skinny(ctx, N, bc);
+        if (G.P.nranks > 0) {
+            // a sharded pass exchanges results in the kernel's tail: all of its CTAs must be resident at once
+            // (see the streaming GEMV); the kernel deals its tiles round-robin over whatever grid it gets
+            int per_sm = 0;
+            if (p.nt == 1)
+                GB_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mmq_skinny_kernel<1>, SK_THREADS, p.smem));
+            else
+                GB_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, mmq_skinny_kernel<2>, SK_THREADS, p.smem));
+            if (per_sm < 1) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: the sharded skinny kernel does not fit on the device");
+            if (p.grid > per_sm * ctx->sm_count) p.grid = per_sm * ctx->sm_count;
+        }
         uint8_t* base = reinterpret_cast<uint8_t*>(scratch) + (size_t)(b0 / 16) * pass_scratch_bytes((size_t)nblk);
         uint32_t* qfrag = reinterpret_cast<uint32_t*>(base);
         float2* ds = reinterpret_cast<float2*>(base + (((size_t)nblk * p.nt * 256 + 255) & ~(size_t)255));

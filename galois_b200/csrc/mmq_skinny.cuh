@@ -23,3 +23,6 @@ size_t gb_mmq_skinny_scratch_bytes(const galois_dim* wd, const galois_dim* xd);
 // each pass's tail receives the peers' rows (protocol of gather.cuh).
 int gb_mmq_skinny(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
                   const galois_dim* dd, void* scratch, const gb_gather_args* gather = nullptr);
+// Test hook: per-block integer sums as the kernel's mma.sync + magic-number conversion forms them
+// (xq in the 34-byte Q8_0 format).
+int gb_mmq_skinny_block_isums(galois_b200_ctx* ctx, const void* w, const void* xq, int64_t nb, int32_t* out);

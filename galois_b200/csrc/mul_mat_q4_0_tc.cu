@@ -138,10 +138,12 @@ __global__ void __launch_bounds__(256) quantize_q8_tc_kernel(const float* __rest
     }
 }
 
-template <int BN>
+// DBG (test hook): the epilogue also stores every per-block integer sum of the tile it owns,
+// dbg[(block * 128 + row in tile) * BN + column in tile], exactly as it is about to scale it.
+template <int BN, bool DBG>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     mm_q4_0_tc_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ qs, const uint8_t* __restrict__ xs,
-                      float* __restrict__ dst, int64_t nb1, int K, int N, int B, int* __restrict__ status) {
+                      float* __restrict__ dst, int64_t nb1, int K, int N, int B, int* __restrict__ status, int32_t* __restrict__ dbg) {
     using L = tc_smem<BN>;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -212,8 +214,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     const int4 sc = xsp[(c0 + c) >> 1];  // {d_x, magic - 8 sum} of two columns (same for all lanes)
                     const float f0 = __int_as_float((int)r[c] + sc.y) - 12582912.0f;
                     const float f1 = __int_as_float((int)r[c + 1] + sc.w) - 12582912.0f;
-                    acc[c0 + c] = fmaf(dw, __int_as_float(sc.x) * f0, acc[c0 + c]);
-                    acc[c0 + c + 1] = fmaf(dw, __int_as_float(sc.z) * f1, acc[c0 + c + 1]);
+                    if (DBG) {
+                        int32_t* o = dbg + ((size_t)g * TC_M + row_in_tile) * BN + half * NC + c0 + c;
+                        o[0] = (int)f0, o[1] = (int)f1;
+                    }
+                    // (d_w * d_x) is exact in f32 (two f16 values), so this is the term of vec_dot_q8_0 with one rounding
+                    acc[c0 + c] = fmaf(dw * __int_as_float(sc.x), f0, acc[c0 + c]);
+                    acc[c0 + c + 1] = fmaf(dw * __int_as_float(sc.z), f1, acc[c0 + c + 1]);
                 }
             }
             if (kb == TC_KC - 1) {
@@ -330,7 +337,7 @@ template <int BN>
 int launch_tc(galois_b200_ctx* ctx, const uint8_t* w, const uint8_t* qs, const uint8_t* xs, float* dst, int64_t nb1, int K, int N,
               int B) {
     dim3 grid((unsigned)((N + TC_M - 1) / TC_M), (unsigned)((B + BN - 1) / BN));
-    mm_q4_0_tc_kernel<BN><<<grid, TC_THREADS, tc_smem<BN>::TOTAL, ctx->stream>>>(w, qs, xs, dst, nb1, K, N, B, ctx->dev_status);
+    mm_q4_0_tc_kernel<BN, false><<<grid, TC_THREADS, tc_smem<BN>::TOTAL, ctx->stream>>>(w, qs, xs, dst, nb1, K, N, B, ctx->dev_status, nullptr);
     GB_LAUNCHED(ctx, "mm_q4_0_tc");
     return 0;
 }
@@ -338,8 +345,9 @@ int launch_tc(galois_b200_ctx* ctx, const uint8_t* w, const uint8_t* qs, const u
 }  // namespace
 
 int gb_mm_tc_init(galois_b200_ctx* ctx) {
-    GB_CUDA(ctx, cudaFuncSetAttribute(mm_q4_0_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem<64>::TOTAL));
-    GB_CUDA(ctx, cudaFuncSetAttribute(mm_q4_0_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem<128>::TOTAL));
+    GB_CUDA(ctx, cudaFuncSetAttribute(mm_q4_0_tc_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem<64>::TOTAL));
+    GB_CUDA(ctx, cudaFuncSetAttribute(mm_q4_0_tc_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem<128>::TOTAL));
+    GB_CUDA(ctx, cudaFuncSetAttribute(mm_q4_0_tc_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem<64>::TOTAL));
     return 0;
 }
 
@@ -377,4 +385,20 @@ int gb_mm_q4_0_tc(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, con
     const uint8_t* wb = (const uint8_t*)w;
     if (BN == 64) return launch_tc<64>(ctx, wb, qs, xs, dst, dd->nb[1], K, N, B);
     return launch_tc<128>(ctx, wb, qs, xs, dst, dd->nb[1], K, N, B);
+}
+
+int gb_mm_q4_0_tc_block_isums(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
+                              const galois_dim* dd, void* scratch, int32_t* out) {
+    const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
+    if (N > TC_M || B > 64) return gb_fail(ctx, GALOIS_B200_E_SHAPE, "block_isums_tc: one tile only (N <= 128, B <= 64)");
+    constexpr int BN = 64;
+    uint8_t* qs = (uint8_t*)scratch;
+    uint8_t* xs = qs + (((size_t)BN * K + 255) & ~(size_t)255);
+    dim3 qgrid((unsigned)((K / 32 * 8 + 255) / 256), (unsigned)BN);
+    quantize_q8_tc_kernel<<<qgrid, 256, 0, ctx->stream>>>(x, xd->nb[1], K, B, BN, qs, (int2*)xs);
+    GB_LAUNCHED(ctx, "quantize_q8_tc");
+    mm_q4_0_tc_kernel<BN, true><<<dim3(1, 1), TC_THREADS, tc_smem<BN>::TOTAL, ctx->stream>>>((const uint8_t*)w, qs, xs, dst, dd->nb[1], K, N, B,
+                                                                                       ctx->dev_status, out);
+    GB_LAUNCHED(ctx, "mm_q4_0_tc (block sums)");
+    return 0;
 }

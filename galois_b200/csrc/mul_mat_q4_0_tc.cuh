@@ -15,3 +15,7 @@ size_t gb_mm_tc_scratch_bytes(const galois_dim* wd, const galois_dim* xd);
 // Quantises x into `scratch` and runs the GEMM (two launches).
 int gb_mm_q4_0_tc(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
                   const galois_dim* dd, void* scratch);
+// Test hook: the same two launches on ONE 128 x 64 tile (N <= 128, B <= 64); the epilogue also stores
+// every per-block integer sum it scales: out[(block * 128 + row) * 64 + column], int32.
+int gb_mm_q4_0_tc_block_isums(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
+                              const galois_dim* dd, void* scratch, int32_t* out);

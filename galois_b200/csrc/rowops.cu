@@ -103,7 +103,8 @@ __global__ void rope_kernel(const float* __restrict__ x, int64_t xb1, int64_t xb
 template <bool EXT>
 __global__ void soft_max_kernel(const float* __restrict__ x, int64_t xb1, int64_t xb2, int64_t xb3, float* __restrict__ y,
                                 int64_t yb1, int64_t yb2, int64_t yb3, int64_t nc, int64_t ne1, int64_t ne2,
-                                const uint16_t* __restrict__ exp_lut, float scale, const int32_t* __restrict__ pos) {
+                                const uint16_t* __restrict__ exp_lut, float scale, const int32_t* __restrict__ pos,
+                                int* __restrict__ status) {
     gb_pdl_entry();
     __shared__ float red[33];
     const int64_t r = blockIdx.x;
@@ -135,6 +136,13 @@ __global__ void soft_max_kernel(const float* __restrict__ x, int64_t xb1, int64_
         yr[i] = val;
     }
     sum = block_sum(sum, red);
+    if (!(sum > 0.0f)) {
+        // every column masked or -inf: the reference asserts sum > 0.0 (src/lib.rs:586); here the row
+        // becomes zeros and the next synchronising call reports GALOIS_B200_E_BADARG
+        for (int64_t i = threadIdx.x; i < nc; i += blockDim.x) yr[i] = 0.0f;
+        if (threadIdx.x == 0) atomicExch(status, GALOIS_B200_E_BADARG);
+        return;
+    }
     const float inv = __fdiv_rn(1.0f, sum);
     for (int64_t i = threadIdx.x; i < nc; i += blockDim.x) yr[i] = __fmul_rn(yr[i], inv);
 }
@@ -313,10 +321,10 @@ static int soft_max_impl(galois_b200_ctx* ctx, const float* x, const galois_dim*
     const int threads = row_threads(nc);
     if (ext)
         gb_launch(ctx, soft_max_kernel<true>, dim3((unsigned)nr), dim3(threads), 0, x, xb1, xb2, xb3, y, yb1, yb2, yb3, nc, ne1, ne2,
-                                                                         ctx->exp_lut, scale, pos);
+                                                                         ctx->exp_lut, scale, pos, ctx->dev_status);
     else
         gb_launch(ctx, soft_max_kernel<false>, dim3((unsigned)nr), dim3(threads), 0, x, xb1, xb2, xb3, y, yb1, yb2, yb3, nc, ne1, ne2,
-                                                                          ctx->exp_lut, 1.0f, nullptr);
+                                                                          ctx->exp_lut, 1.0f, nullptr, ctx->dev_status);
     GB_LAUNCHED(ctx, "soft_max");
     return 0;
 }

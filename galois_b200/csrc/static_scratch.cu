@@ -24,6 +24,8 @@ namespace {
 constexpr int MAX_DEVICES = 64;
 // Per device: the device address of g_static_scratch (the symbol's name is only a host-side
 // handle, never a pointer a kernel may be given) and the SM count, looked up on first use.
+// The first call on a device fills both without any locking: it must not run concurrently with
+// another host thread's call on the same device (later calls only read them).
 void* g_scratch_addr[MAX_DEVICES];
 int g_sm_count[MAX_DEVICES];
 
@@ -52,7 +54,15 @@ extern "C" int galois_b200_mul_mat_q4_0_f32_static(void* cu_stream, const void* 
     if (!(dd->ne[0] == N && dd->ne[1] == xd->ne[1] && dd->ne[2] == xd->ne[2] && dd->ne[3] == xd->ne[3]))
         return fail(errbuf, errbuf_len, GALOIS_B200_E_SHAPE, "mul_mat_q4_0_static: dst shape does not match");
     const int64_t nrows = xd->ne[1] * xd->ne[2] * xd->ne[3];
-    if (N == 0 || K == 0 || nrows == 0) return 0;  // nothing to compute; K == 0 with a non-empty dst is the caller's memset
+    if (N == 0 || nrows == 0) return 0;  // nothing to compute
+    if (K == 0) {
+        // an empty contraction is 0.0 everywhere, as in the regular entry point (a memset allocates nothing)
+        if (!dst) return fail(errbuf, errbuf_len, GALOIS_B200_E_BADARG, "mul_mat_q4_0_static: null pointer");
+        if (!gb_is_contiguous(dd)) return fail(errbuf, errbuf_len, GALOIS_B200_E_DST, "mul_mat_q4_0_static: K == 0 needs a contiguous dst");
+        const cudaError_t me = cudaMemsetAsync(dst, 0, (size_t)gb_nelements(dd) * sizeof(float), (cudaStream_t)cu_stream);
+        if (me != cudaSuccess) return fail(errbuf, errbuf_len, (int)me, "mul_mat_q4_0_static: cudaMemsetAsync: %s", cudaGetErrorString(me));
+        return 0;
+    }
     if (wd->nb[0] != 1 || xd->nb[0] != 1) return fail(errbuf, errbuf_len, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0_static: permuted src0 or src1 not supported");
     if (!(dd->nb[0] == 1 && dd->nb[0] <= dd->nb[1] && dd->nb[1] <= dd->nb[2] && dd->nb[2] <= dd->nb[3]))
         return fail(errbuf, errbuf_len, GALOIS_B200_E_DST, "mul_mat_q4_0_static: dst cannot be transposed or permuted");

@@ -2,7 +2,7 @@
 
 galois itself holds no model code: a caller crate composes a layer from the free functions
 ``galois_rms_norm / mul / matmul / rope_custom / cpy / soft_max / unary / add``
-(src/op.rs:3034-3341).  This module is that caller for BASELINE config 4: hidden 4096,
+(src/op.rs:3034-3341).  This module is that caller for the decode-layer configuration of the benchmark (config 4): hidden 4096,
 32 heads x 128, FFN 11008, Q4_0 projections, f16 KV cache, batch 1.
 
 KV-cache layout (both present the contraction dimension contiguously, as

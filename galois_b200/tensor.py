@@ -76,10 +76,11 @@ class Dim:
     def nrows(self) -> int:
         return self.shape[1] * self.shape[2] * self.shape[3]
 
-    def ggml_is_contiguous(self) -> bool:
-        """src/shape.rs:254-259 (strides are already in blocks)."""
+    def ggml_is_contiguous(self, block: int = 1) -> bool:
+        """src/shape.rs:254-259; strides are in blocks of `block` elements (32 for Q4_0), so a row
+        of shape[0] elements is contiguous with the next one when stride[1] == shape[0] / block."""
         s, n = self.stride, self.shape
-        return s[0] == 1 and s[2] == s[1] * n[1] and s[3] == s[2] * n[2]
+        return s[0] == 1 and s[1] == n[0] // block and s[2] == s[1] * n[1] and s[3] == s[2] * n[2]
 
     def c_struct(self) -> GaloisDim:
         d = GaloisDim()
@@ -126,6 +127,16 @@ class CudaDevice:
 
     def set_mul_mat_variant(self, variant: int):
         _check(self.ctx, lib.galois_b200_set_mul_mat_variant(self.ctx, variant), "set_mul_mat_variant")
+
+    def set_overlap(self, on: bool):
+        """Overlap of independent one-row mat-muls (galois_b200_set_overlap; default on)."""
+        _check(self.ctx, lib.galois_b200_set_overlap(self.ctx, 1 if on else 0), "set_overlap")
+
+    def overlap_counts(self):
+        """(waited at entry, deferred wait, barrier) counts of one-row mat-vec launches so far."""
+        out = (C.c_int64 * 3)()
+        _check(self.ctx, lib.galois_b200_overlap_counts(self.ctx, C.byref(out)), "overlap_counts")
+        return tuple(int(v) for v in out)
 
     def launch_count(self) -> int:
         return int(lib.galois_b200_launch_count(self.ctx))
@@ -264,7 +275,7 @@ class Tensor:
     def to_numpy(self) -> np.ndarray:
         """Contiguous tensors only: numpy array of shape (n3, n2, n1, n0) trimmed to n_dims."""
         t = self.to_cpu_tensor()
-        if not t._dim.ggml_is_contiguous():
+        if not t._dim.ggml_is_contiguous(BLCK_SIZE[t.dtype]):
             raise GError("to_numpy: tensor is not contiguous")
         n = t._dim.elem_count() // BLCK_SIZE[t.dtype]
         if t.dtype == GGmlType.Q4_0:

@@ -86,6 +86,27 @@ int galois_b200_set_mul_mat_variant(galois_b200_ctx* ctx, int variant);
  * are always safe). */
 int galois_b200_set_pdl(galois_b200_ctx* ctx, int on);
 
+/* Overlap of independent mat-vec calls (default on; needs programmatic dependent launch).  The
+ * reference API orders every op after the one before it (one stream, src/cuda.rs:340), although
+ * the projections of one input (Q / K / V, gate / up) do not depend on each other.  The context
+ * keeps the address ranges written by the kernels that may still be running; a one-row
+ * galois_b200_mul_mat_q4_0_f32 (or its fused form) whose activations (and prologue operand) lie
+ * outside all of them starts reading, quantising and multiplying at once and waits for the kernels
+ * in front of it only before its first store to `dst`, so that it streams weights while its
+ * predecessor still runs.  Results are those of strict stream order: a mat-vec that reads what an
+ * unfinished kernel writes waits at entry as before, and so does every other op.  Only work
+ * enqueued through this context is tracked; work the caller puts on the stream itself (its own
+ * kernels, copies) must be ordinary stream-ordered work: a kernel the caller launches with
+ * programmatic stream serialization has to call cudaGridDependencySynchronize before it exits.
+ * 0 turns the overlap off (every kernel waits at entry). */
+int galois_b200_set_overlap(galois_b200_ctx* ctx, int on);
+/* How many one-row mat-vec kernels this context has launched in each ordering mode so far:
+ * out[0] waited at entry (its input may be written by a kernel in flight, or overlap is off),
+ * out[1] deferred its wait to its first store (independent input), out[2] waited at entry and released
+ * its successor only afterwards (taken when the kernels in flight are not known, e.g. after any op
+ * other than a one-row mat-vec; it makes them known again).  For benches and tests. */
+int galois_b200_overlap_counts(galois_b200_ctx* ctx, int64_t out[3]);
+
 /* Kernel timing for benches.  While enabled, every galois_b200_mul_mat_q4_0_f32
  * call brackets its mat-mul kernel (not the activation quantiser) with CUDA
  * events on the context's stream; galois_b200_profile_read synchronises, adds
@@ -103,6 +124,17 @@ int galois_b200_free(galois_b200_ctx* ctx, void* dev);
 int galois_b200_htod(galois_b200_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
 int galois_b200_dtoh(galois_b200_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
 int galois_b200_synchronize(galois_b200_ctx* ctx);
+/* galois_b200_dtoh and galois_b200_synchronize also report a bounded device-side wait that ran out
+ * in the work they waited for (GALOIS_B200_E_TIMEOUT, a bad get_rows index as GALOIS_B200_E_BADARG):
+ * the status is returned once and cleared. */
+
+/* The scratch arena that holds quantised activations (the reference allocates such temporaries with
+ * alloc_zeros on every call, src/cuda.rs:1052-1068).  galois_b200_init creates 16 MiB; a mat-mul that
+ * needs more grows it, which synchronises the stream and calls cudaFree / cudaMalloc.  To keep every
+ * later call free of that, reserve once up front: galois_b200_mul_mat_q4_0_scratch_bytes gives the need
+ * of a mat-mul with the extents of wd (K, N, ..) and xd (K, B, ne12, ne13), whichever kernel is chosen. */
+int galois_b200_reserve_scratch(galois_b200_ctx* ctx, size_t bytes);
+int galois_b200_mul_mat_q4_0_scratch_bytes(galois_b200_ctx* ctx, const galois_dim* wd, const galois_dim* xd, size_t* out_bytes);
 
 /* ---- quantisation ------------------------------------------------------ */
 
@@ -121,6 +153,19 @@ int galois_b200_quantize_q8_0(galois_b200_ctx* ctx, const float* x, int64_t x_ro
  * 34-byte format; out: nb int32. */
 int galois_b200_block_isums_q4_0_q8_0(galois_b200_ctx* ctx, const void* w, const void* xq, int64_t nb,
                                       int32_t* out);
+/* The same sums out of the integer path of each of the other mat-mul kernels (same quantity, same
+ * reference lines): variant 1 = general kernel (dp4a on whole words; the call above), 2 = streaming
+ * GEMV (dp4a with the high nibbles used in place), 4 = skinny kernel (mma.sync m16n8k32 u8 x s8 and its
+ * magic-number int -> float conversion).  Variants 2 and 4 take an even `nb` and a 4-byte aligned w. */
+int galois_b200_block_isums_q4_0_q8_0_ex(galois_b200_ctx* ctx, const void* w, const void* xq, int64_t nb, int variant,
+                                         int32_t* out);
+/* ... and out of the tcgen05 kernel: runs galois_b200_mul_mat_q4_0_f32's tensor-core path on ONE tile
+ * (N <= 128 weight rows, B <= 64 activation rows, K % 256 == 0; arguments as for the mat-mul, dst is
+ * written as usual) and also stores every per-block integer sum its epilogue scales:
+ * out[(block * 128 + n) * 64 + b], int32, K/32 * 128 * 64 values (entries with n >= N or b >= B are
+ * padding). */
+int galois_b200_mul_mat_q4_0_tc_block_isums(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
+                                            const galois_dim* xd, float* dst, const galois_dim* dd, int32_t* out);
 
 /* ---- mat-mul ----------------------------------------------------------- */
 
@@ -180,7 +225,9 @@ int galois_b200_mul_mat_q4_0_f32_host(galois_b200_ctx* ctx, const void* w, const
  * The first call on each device resolves the array's device address (that device must be
  * current) and should come before any stream capture; later calls only enqueue two kernels on
  * `cu_stream`.  All calls on one device share the array: calls whose kernels could overlap on
- * the GPU (different streams, no dependency) race on it and must be ordered by the caller.
+ * the GPU (different streams, no dependency) race on it and must be ordered by the caller; the
+ * first call on a device must not run concurrently with another host thread's call on it.
+ * K == 0 zero-fills a contiguous dst (a memset; still no allocation), like the regular entry point.
  * `errbuf` (may be NULL) receives the text of a non-zero status. */
 int galois_b200_mul_mat_q4_0_f32_static(void* cu_stream, const void* w, const galois_dim* wd, const float* x,
                                         const galois_dim* xd, float* dst, const galois_dim* dd, char* errbuf,

@@ -69,6 +69,26 @@ def build(force: bool = False) -> str:
     return _SO
 
 
+def use_native_build() -> str:
+    """For TIMING the CPU baseline only: rebuild the oracle with -march=native on the host this runs on
+    (the analogue of the reference README's -Ctarget-cpu=native, README.md:33) and switch this module to it.
+    Returns "native", or "portable" when that build fails and the portable library stays in use."""
+    global _lib, _SO
+    try:
+        subprocess.run(["make", "-C", _HERE, "-B", "libgalois_oracle_native.so"], check=True, capture_output=True)
+    except Exception:
+        return "portable"
+    _SO = os.path.join(_HERE, "libgalois_oracle_native.so")
+    _lib = None
+    try:
+        lib()
+    except Exception:
+        _SO = os.path.join(_HERE, "libgalois_oracle.so")
+        _lib = None
+        return "portable"
+    return "native"
+
+
 _lib = None
 
 

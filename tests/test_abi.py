@@ -80,6 +80,21 @@ def test_dim_mirror():
 
     d = gb.Dim.ggml((4096, 11008), gb.GGmlType.Q4_0)
     assert d.stride == (1, 128, 128 * 11008, 128 * 11008) and d.shape == (4096, 11008, 1, 1)
-    assert d.ggml_is_contiguous()
+    assert d.ggml_is_contiguous(32) and not d.ggml_is_contiguous()
     d = gb.Dim.ggml((128, 32, 1), gb.GGmlType.F32)
-    assert d.stride == (1, 128, 4096, 4096) and d.n_dims == 3
+    assert d.stride == (1, 128, 4096, 4096) and d.n_dims == 3 and d.ggml_is_contiguous()
+
+
+def test_to_numpy_rejects_row_padded_view():
+    """A window whose rows are further apart than their length (the band of a sharded result) is not
+    contiguous (src/shape.rs:254-259): to_numpy must refuse it instead of returning the wrong elements."""
+    import numpy as np
+
+    import galois_b200 as gb
+
+    t = gb.Tensor.from_numpy(np.arange(4 * 16, dtype=np.float32).reshape(4, 16), gb.GGmlType.F32, gb.Device.Cpu())
+    band = t.view((8, 4), (1, 16, 64, 64))
+    assert not band.dim().ggml_is_contiguous()
+    with pytest.raises(gb.GError):
+        band.to_numpy()
+    assert np.array_equal(t.view((16, 2), (1, 16, 32, 32), offset=16).to_numpy(), np.arange(16, 48, dtype=np.float32).reshape(2, 16))

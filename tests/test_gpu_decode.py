@@ -1,5 +1,7 @@
-"""GPU parity of one decoder-layer decode step (BASELINE config 4) built from galois ops,
-against the same op sequence evaluated by the CPU oracle."""
+"""GPU parity of one decoder-layer decode step (hidden 4096, 32 heads x 128, FFN 11008, f16 KV cache of
+2048, batch 1, and a small sibling) built from galois ops, against the same op sequence evaluated by
+the CPU oracle (oracle/layer.py): the whole layer free-running, and every op fed the oracle's
+own input for that op."""
 import math
 
 import numpy as np
@@ -9,31 +11,7 @@ from conftest import assert_close
 
 pytestmark = pytest.mark.gpu
 
-
-def oracle_layer_step(O, s, wq4, attn_norm, ffn_norm, k_cache, v_cache, x, position):
-    """The op sequence of galois_b200.decode.DecodeLayer.step on the CPU oracle.  Caches are f16
-    bit patterns (uint16) and are updated in place."""
-    hd, nh, ctx = s.head_dim, s.heads, s.ctx
-    pos = np.array([position], np.int32)
-    h = O.mul(O.rms_norm(x, s.eps), attn_norm[None])
-    q = O.mul_mat_q4_0(wq4["wq"], h)
-    k = O.mul_mat_q4_0(wq4["wk"], h)
-    v = O.mul_mat_q4_0(wq4["wv"], h)
-    qr = O.rope(q.reshape(1, nh, hd), pos, hd, freq_base=s.rope_theta)
-    kr = O.rope(k.reshape(1, nh, hd), pos, hd, freq_base=s.rope_theta)
-    k_cache[:, position, :] = O.f32_to_f16(kr[0])
-    v_cache[:, :, position] = O.f32_to_f16(v.reshape(nh, hd))
-    scores = O.mul_mat_f16(k_cache, qr.reshape(nh, 1, hd))            # [nh, 1, ctx]
-    probs = O.soft_max_ext(scores.reshape(1, nh, ctx), 1.0 / math.sqrt(hd), pos)
-    ctxv = O.mul_mat_f16(v_cache, probs.reshape(nh, 1, ctx))          # [nh, 1, hd]
-    o = O.mul_mat_q4_0(wq4["wo"], ctxv.reshape(1, nh * hd))
-    x2 = O.add(x, o)
-    h2 = O.mul(O.rms_norm(x2, s.eps), ffn_norm[None])
-    g = O.mul_mat_q4_0(wq4["w_gate"], h2)
-    u = O.mul_mat_q4_0(wq4["w_up"], h2)
-    a = O.mul(O.silu(g), u)
-    d = O.mul_mat_q4_0(wq4["w_down"], a)
-    return O.add(x2, d)
+from oracle.layer import disagreement, make_layer_inputs, oracle_layer_step, oracle_layer_trace  # noqa: E402
 
 
 @pytest.mark.parametrize("hidden,heads,ffn,ctx,position", [(512, 4, 1024, 256, 255), (4096, 32, 11008, 2048, 2047),
@@ -66,10 +44,17 @@ def test_decode_layer_step(dev, oracle, hidden, heads, ffn, ctx, position):
     assert_close(layer.q.to_numpy(), O.mul_mat_q4_0(wq4["wq"], h))
     # The whole layer does not: the reference's soft_max and silu round their ARGUMENT to f16 before a
     # table look-up (src/lib.rs:543-549, 578-582), so a last-bit difference in a score or a gate value
-    # (rope's sin/cos, the order of f32 sums) can move a probability by an f16 step (up to ~0.8 %).  The
-    # CPU reference run twice with inputs one ulp apart differs from itself by as much; per-op parity
-    # on identical inputs is what the 1e-4 bar is checked on (tests/test_gpu_parity.py).
-    assert_close(got, want, rel_l2=2e-2, max_abs=5e-2)
+    # (rope's sin/cos, the order of f32 sums) moves an output by an f16 step (up to ~0.8 %).  The bar is
+    # therefore MEASURED, not picked: the reference's two own builds of the block dot (AVX2 and scalar,
+    # src/ggml_quants.rs:202-207) are run on the same inputs, and the GPU may differ from the AVX2 build by
+    # at most twice what the scalar build differs from it (config 4: 3e-3..6e-3 relative L2, 0.02..0.05 max
+    # abs).  Per-op parity on identical inputs at the 1e-4 / 1e-3 bar is test_layer_ops_teacher_forced.
+    scalar = oracle_layer_step(O, s, wq4, attn_norm, ffn_norm, k_cache.copy(), v_cache.copy(), x, position, avx=False)
+    self_rel, self_abs = disagreement(scalar, want)
+    # the small sibling has so few table look-ups that the two CPU builds usually agree exactly while a
+    # single f16 step on the GPU side is still possible: one step there is at most 2e-3 / 1e-2
+    floor_rel, floor_abs = (1e-4, 1e-3) if hidden >= 4096 else (2e-3, 1e-2)
+    assert_close(got, want, rel_l2=max(2 * self_rel, floor_rel), max_abs=max(2 * self_abs, floor_abs))
     # the caches were appended bit-exactly ... almost: rope's sin/cos differ in the last bit between
     # the GPU and libm, so K rows are compared as numbers, V (a plain f32 -> f16 copy of a mat-mul) too
     gk = layer.k_cache.to_numpy().view(np.uint16)
@@ -112,3 +97,109 @@ def test_fused_layer_equals_op_by_op_layer(dev, oracle, hidden, heads, ffn, ctx,
     assert np.array_equal(plain.k_cache.to_numpy().view(np.uint16), fused.k_cache.to_numpy().view(np.uint16))
     assert np.array_equal(plain.v_cache.to_numpy().view(np.uint16), fused.v_cache.to_numpy().view(np.uint16))
     assert (l1 - l0, l2 - l1) == (22, 9)
+
+
+def _bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+@pytest.mark.parametrize("position", [2047, 100])
+def test_layer_ops_teacher_forced(dev, oracle, position):
+    """Config 4 at full size, op by op: every GPU op (the 22 of the op-by-op layer, then the fused
+    forms of the 9-kernel layer) is fed the ORACLE's input for that op and its output is held to the
+    stated bar: 1e-4 relative L2 / 1e-3 max abs for mat-muls and rms_norm, 1e-5 for rope and soft_max,
+    identical bits for mul, add, silu and the f32 -> f16 cache appends."""
+    import galois_b200 as gb
+    from galois_b200.decode import LayerShape
+    from galois_b200.op import (RopeCustomOption, UnaryOp, galois_add, galois_cpy, galois_cpy_pair, galois_matmul, galois_matmul_add,
+                                galois_matmul_fused, galois_mul, galois_rms_norm, galois_rope_custom, galois_soft_max_ext, galois_unary)
+
+    O = oracle
+    s = LayerShape()
+    hd, nh, ctx, H, F = s.head_dim, s.heads, s.ctx, s.hidden, s.ffn
+    wq4, attn_norm, ffn_norm, k_cache, v_cache, x = make_layer_inputs(O, s, 4700)
+    kc, vc = k_cache.copy(), v_cache.copy()
+    t = oracle_layer_trace(O, s, wq4, attn_norm, ffn_norm, kc, vc, x, position)  # kc, vc: caches after the append
+    G = gb.Device.Gpu(dev)
+    up = lambda a: gb.Tensor.from_numpy(np.ascontiguousarray(a, np.float32), gb.GGmlType.F32, G)
+    z = lambda *ne: gb.Tensor.zeros(ne, gb.GGmlType.F32, G)
+    W = {name: gb.Tensor.from_raw(w, (w.shape[1] // 18 * 32, w.shape[0]), gb.GGmlType.Q4_0, G) for name, w in wq4.items()}
+    pos = gb.Tensor.from_numpy(np.array([position], np.int32), gb.GGmlType.I32, G)
+    rope = RopeCustomOption(n_dims=hd, mode=0, n_ctx=ctx, freq_base=s.rope_theta, freq_scale=1.0)
+
+    def exact(got, want, what):
+        assert np.array_equal(_bits(got), _bits(want)), what
+
+    # ---- the op-by-op layer
+    o = z(H, 1)
+    galois_rms_norm(up(x), o, s.eps)
+    assert_close(o.to_numpy(), t["h_norm"])
+    galois_mul(up(t["h_norm"]), up(attn_norm[None]), o)
+    exact(o.to_numpy(), t["h"], "mul by the attention gain")
+    for name, key in (("wq", "q"), ("wk", "k"), ("wv", "v")):
+        galois_matmul(W[name], up(t["h"]), o)
+        assert_close(o.to_numpy(), t[key])
+    r = z(hd, nh, 1)
+    for key, rk in (("q", "qr"), ("k", "kr")):
+        galois_rope_custom(rope, up(t[key].reshape(1, nh, hd)), pos, r)
+        assert_close(r.to_numpy(), t[rk], rel_l2=1e-5, max_abs=1e-5)
+    # cache appends from the oracle's rope / v outputs: identical f16 bits everywhere
+    kct = gb.Tensor.from_numpy(k_cache.view(np.float16), gb.GGmlType.F16, G)
+    vct = gb.Tensor.from_numpy(v_cache.view(np.float16), gb.GGmlType.F16, G)
+    krt, vt = up(t["kr"]), up(t["v"])
+    galois_cpy(krt.view((hd, 1, nh), (1, hd, hd, hd * nh)), kct.view((hd, 1, nh), (1, hd, hd * ctx, hd * ctx * nh), offset=position * hd))
+    galois_cpy(vt.view((1, hd, nh), (1, 1, hd, hd * nh)), vct.view((1, hd, nh), (1, ctx, hd * ctx, hd * ctx * nh), offset=position))
+    assert np.array_equal(kct.to_numpy().view(np.uint16), kc)
+    assert np.array_equal(vct.to_numpy().view(np.uint16), vc)
+    sc = z(ctx, 1, nh)
+    galois_matmul(kct, up(t["qr"]).view((hd, 1, nh), (1, hd, hd, hd * nh)), sc)
+    assert_close(sc.to_numpy(), t["scores"])
+    pr = z(ctx, nh, 1)
+    galois_soft_max_ext(up(t["scores"].reshape(1, nh, ctx)), pr, 1.0 / math.sqrt(hd), pos)
+    assert_close(pr.to_numpy(), t["probs"], rel_l2=1e-5, max_abs=1e-5)
+    cv = z(hd, 1, nh)
+    galois_matmul(vct, up(t["probs"].reshape(nh, 1, ctx)), cv)
+    assert_close(cv.to_numpy(), t["ctxv"])
+    galois_matmul(W["wo"], up(t["ctxv"].reshape(1, H)), o)
+    assert_close(o.to_numpy(), t["o"])
+    galois_add(up(x), up(t["o"]), o)
+    exact(o.to_numpy(), t["x2"], "first residual")
+    galois_rms_norm(up(t["x2"]), o, s.eps)
+    assert_close(o.to_numpy(), t["h2_norm"])
+    galois_mul(up(t["h2_norm"]), up(ffn_norm[None]), o)
+    exact(o.to_numpy(), t["h2"], "mul by the FFN gain")
+    f = z(F, 1)
+    for name, key in (("w_gate", "g"), ("w_up", "u")):
+        galois_matmul(W[name], up(t["h2"]), f)
+        assert_close(f.to_numpy(), t[key])
+    galois_unary(up(t["g"]), f, UnaryOp.Silu)
+    exact(f.to_numpy(), t["a_silu"], "silu")
+    galois_mul(up(t["a_silu"]), up(t["u"]), f)
+    exact(f.to_numpy(), t["a"], "silu(g) * u")
+    galois_matmul(W["w_down"], up(t["a"]), o)
+    assert_close(o.to_numpy(), t["d"])
+    galois_add(up(t["x2"]), up(t["d"]), o)
+    exact(o.to_numpy(), t["out"], "second residual")
+
+    # ---- the fused forms of the 9-kernel layer, each on the oracle's inputs
+    raw = lambda name: np.ascontiguousarray(wq4[name]).view(np.uint8).reshape(-1)
+    wqkv = gb.Tensor.from_raw(np.concatenate([raw("wq"), raw("wk"), raw("wv")]), (H, 3 * H), gb.GGmlType.Q4_0, G)
+    wgu = gb.Tensor.from_raw(np.concatenate([raw("w_gate"), raw("w_up")]), (H, 2 * F), gb.GGmlType.Q4_0, G)
+    qkv = z(3 * H, 1)
+    galois_matmul_fused(wqkv, up(x), qkv, rms_gain=up(attn_norm[None]), eps=s.eps)
+    assert_close(qkv.to_numpy(), np.concatenate([t["q"], t["k"], t["v"]], axis=1))
+    qkr = z(hd, 2 * nh, 1)
+    galois_rope_custom(rope, up(np.concatenate([t["q"], t["k"]], axis=1).reshape(1, 2 * nh, hd)), pos, qkr)
+    assert_close(qkr.to_numpy(), np.concatenate([t["qr"], t["kr"]], axis=1), rel_l2=1e-5, max_abs=1e-5)
+    kct2 = gb.Tensor.from_numpy(k_cache.view(np.float16), gb.GGmlType.F16, G)
+    vct2 = gb.Tensor.from_numpy(v_cache.view(np.float16), gb.GGmlType.F16, G)
+    galois_cpy_pair(krt.view((hd, 1, nh), (1, hd, hd, hd * nh)), kct2.view((hd, 1, nh), (1, hd, hd * ctx, hd * ctx * nh), offset=position * hd),
+                    vt.view((1, hd, nh), (1, 1, hd, hd * nh)), vct2.view((1, hd, nh), (1, ctx, hd * ctx, hd * ctx * nh), offset=position))
+    assert np.array_equal(kct2.to_numpy().view(np.uint16), kc) and np.array_equal(vct2.to_numpy().view(np.uint16), vc)
+    galois_matmul_add(W["wo"], up(t["ctxv"].reshape(1, H)), up(x), o)
+    assert_close(o.to_numpy(), t["x2"])
+    gu = z(2 * F, 1)
+    galois_matmul_fused(wgu, up(t["x2"]), gu, rms_gain=up(ffn_norm[None]), eps=s.eps)
+    assert_close(gu.to_numpy(), np.concatenate([t["g"], t["u"]], axis=1))
+    galois_matmul_fused(W["w_down"], up(t["g"]), o, silu_mul=up(t["u"]), res=up(t["x2"]))
+    assert_close(o.to_numpy(), t["out"])

@@ -118,7 +118,7 @@ def _mul_mat_case(gb, dev, oracle, n, k, b, seed, variant):
     assert_close(got, want)
 
 
-# BASELINE config 1 (4096x4096, B=1) and odd shapes; variant 1 = direct kernel
+# config 1 of the benchmark (4096x4096, B=1) and odd shapes; variant 1 = direct kernel
 @pytest.mark.parametrize("n,k,b", [(4096, 4096, 1), (70, 96, 5), (1, 32, 1), (33, 4096 + 32, 3), (257, 352, 8),
                                    (100, 256, 16), (64, 64, 33), (5, 11008, 2)])
 def test_mul_mat_q4_0_direct(gb, dev, oracle, n, k, b):
@@ -159,7 +159,7 @@ def test_mul_mat_q4_0_dependent_launch_ordering(gb, dev, oracle):
     gb.lib.galois_b200_set_pdl(dev.ctx, 1)
 
 
-# variant 3 = tcgen05 int8 tensor-core GEMM (K % 256 == 0); BASELINE config 3 is 4096 x 4096 x 512
+# variant 3 = tcgen05 int8 tensor-core GEMM (K % 256 == 0); config 3 of the benchmark is 4096 x 4096 x 512
 @pytest.mark.parametrize("n,k,b", [(128, 256, 64), (128, 512, 1), (200, 768, 33), (77, 256, 130), (4096, 4096, 512),
                                    (300, 4096, 37), (4096, 4096, 100), (1000, 11008, 65)])
 def test_mul_mat_q4_0_tensor_core(gb, dev, oracle, n, k, b):
@@ -176,7 +176,7 @@ def test_mul_mat_q4_0_skinny(gb, dev, oracle, n, k, b):
     _mul_mat_case(gb, dev, oracle, n, k, b, 9700 + n + k + b, 4)
 
 
-# automatic dispatch over the BASELINE shapes (configs 2, 3, 5) incl. large batches
+# automatic dispatch over the shapes of the benchmark (configs 2, 3, 5) incl. large batches
 @pytest.mark.parametrize("n,k,b", [(11008, 4096, 8), (4096, 11008, 8), (4096, 4096, 512), (32000, 4096, 16), (28672, 8192, 16),
                                    (4096, 4096, 100), (300, 4096, 37)])
 def test_mul_mat_q4_0_auto(gb, dev, oracle, n, k, b):

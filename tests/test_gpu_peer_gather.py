@@ -94,6 +94,28 @@ def test_band_goes_out_and_peers_bands_come_in(dev, n, k, b, world, rank, epoch)
         assert not got.any(), "packets outside this rank's area of the inbox"
 
 
+def test_long_rows_and_a_large_band_stay_one_wave(dev):
+    """K = 20480 needs so much shared memory per CTA that only one CTA fits per SM; the sharded launch
+    must then shrink to one wave of CTAs, or first-wave CTAs would poll for packets that only a second
+    wave sends.  A band of 20480 rows gives every CTA of the first wave receive work."""
+    import torch
+
+    from galois_b200 import lib
+    from galois_b200.shard import shard_rows
+
+    n, k, b, world, rank, epoch = 40960, 20480, 1, 2, 1, 3
+    w_band, x, ref, full, inboxes, peers, dd, r0, nr, slots = _setup(dev, n, k, b, world, rank, 4242)
+    want = ref.to_numpy()
+    p0, pn = shard_rows(n, world, 0)
+    pk = torch.from_numpy(_packets(want[:, p0 : p0 + pn], epoch)).to(dev.torch_device)
+    start = ((epoch & 1) * world + 0) * slots
+    inboxes[rank][start : start + pk.numel()] = pk
+    torch.cuda.synchronize()
+    assert _call(dev, w_band, x, full, dd, r0, peers, epoch) == 0, lib.galois_b200_last_error(dev.ctx)
+    dev.synchronize()
+    assert np.array_equal(full.cpu().numpy().reshape(b, n), want)
+
+
 def test_wait_runs_out_and_context_survives(dev):
     """Nothing ever fills the inbox: the bounded device wait gives up, the next synchronize
     reports the time-out, and the context keeps working."""
