@@ -146,7 +146,7 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
     if (const char* t = getenv("GALOIS_B200_TUNE")) {
         const struct { const char* key; int* dst; } keys[] = {
             {"stages", &ctx->tune_stages}, {"smem_kb", &ctx->tune_smem_kb}, {"cps", &ctx->tune_ctas_per_sm}, {"pdl", &ctx->pdl},
-            {"cluster", &ctx->tune_cluster}, {"seg", &ctx->tune_seg}, {"variant", &ctx->variant}, {"overlap", &ctx->hazard_tracking},
+            {"cluster", &ctx->tune_cluster}, {"dcps", &ctx->tune_dcps}, {"dsmem_kb", &ctx->tune_dsmem_kb}, {"seg", &ctx->tune_seg}, {"variant", &ctx->variant}, {"overlap", &ctx->hazard_tracking},
         };
         while (*t) {
             const char* end = strchr(t, ',');

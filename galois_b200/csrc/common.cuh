@@ -23,6 +23,7 @@ struct galois_b200_ctx {
     int variant;           // forced Q4_0 mat-mul variant (0 = automatic)
     // launch-geometry overrides for the bulk-copy GEMV (0 = automatic), from GALOIS_B200_TUNE
     int tune_stages, tune_smem_kb, tune_ctas_per_sm, tune_cluster, tune_seg;
+    int tune_dcps, tune_dsmem_kb;  // the same two for launches with a deferred wait
     int pdl;               // launch the streaming kernels with programmatic dependent launch (default on)
     // Write ranges of the kernels that may still be running when the next kernel of the stream starts
     // (see gb_hazard_free); hazard_unknown: some kernel in flight may write anywhere.

@@ -101,10 +101,11 @@ int galois_b200_set_pdl(galois_b200_ctx* ctx, int on);
  * 0 turns the overlap off (every kernel waits at entry). */
 int galois_b200_set_overlap(galois_b200_ctx* ctx, int on);
 /* How many one-row mat-vec kernels this context has launched in each ordering mode so far:
- * out[0] waited at entry (its input may be written by a kernel in flight, or overlap is off),
+ * out[0] waited at entry and released its successor at once (overlap off, or a sharded call),
  * out[1] deferred its wait to its first store (independent input), out[2] waited at entry and released
- * its successor only afterwards (taken when the kernels in flight are not known, e.g. after any op
- * other than a one-row mat-vec; it makes them known again).  For benches and tests. */
+ * its successor only afterwards (its input may be written by a kernel in flight, or the kernels in
+ * flight are not known, e.g. after any op other than a one-row mat-vec; this makes them known again).
+ * For benches and tests. */
 int galois_b200_overlap_counts(galois_b200_ctx* ctx, int64_t out[3]);
 
 /* Kernel timing for benches.  While enabled, every galois_b200_mul_mat_q4_0_f32

@@ -63,7 +63,7 @@ def test_independent_mat_vecs_defer_their_wait_and_match_serial_results(gb, dev,
     assert deferred >= 3 * len(shapes) - 2 and entry == 0 and barrier <= 2, (entry, deferred, barrier)
 
 
-def test_read_after_write_chain_waits_at_entry(gb, dev, oracle):
+def test_read_after_write_chain_waits_before_it_reads(gb, dev, oracle):
     """y1 = W1 x; y2 = W2 y1; y3 = W3 y2: each input is the output of the kernel in front of it."""
     G = gb.Device.Gpu(dev)
     (r1, w1), (r2, w2), (r3, w3) = _weights(gb, dev, oracle, [(4096, 4096), (11008, 4096), (4096, 11008)], 9300)
@@ -77,7 +77,7 @@ def test_read_after_write_chain_waits_at_entry(gb, dev, oracle):
         gb.galois_matmul(w3, y2, y3)
     got = [t.to_numpy() for t in (y1, y2, y3)]
     entry, deferred, barrier = _counts_delta(dev, c0)
-    assert entry >= 38, (entry, deferred, barrier)  # W2 and W3 always read what is being written
+    assert barrier >= 38 and entry == 0, (entry, deferred, barrier)  # W2 and W3 always read what is being written
     # the same chain, synchronised after every op
     dev.set_overlap(False)
     try:
