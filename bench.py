@@ -536,6 +536,39 @@ def run_ours(args):
 
         extra["decode_layer"] = measure_layer(False)       # the op-by-op sequence a galois caller writes
         extra["decode_layer_fused"] = measure_layer(True)  # stacked QKV / gate-up weights + two-op fusions, same numbers
+        # the same 22-op layers as ONE persistent cooperative kernel per token (galois_b200_decode_layers_f32)
+        def measure_stack(nl):
+            from galois_b200.decode import DecodeStack
+            layers = []
+            for li in range(nl):
+                wq4 = {name: make_q4_0(n, k, 31000 + 100 * li + i, device).cpu().numpy()
+                       for i, (name, (n, k)) in enumerate(weight_shapes(shp).items())}
+                gk = torch.Generator(device=device)
+                gk.manual_seed(32000 + li)
+                kc = torch.randn(shp.heads, shp.ctx, shp.head_dim, generator=gk, device=device).to(torch.float16).cpu().numpy()
+                vc = torch.randn(shp.heads, shp.head_dim, shp.ctx, generator=gk, device=device).to(torch.float16).cpu().numpy()
+                layers.append(DecodeLayer(dev, shp, wq4, np.ones(shp.hidden, np.float32), np.ones(shp.hidden, np.float32), kc, vc))
+            stack = DecodeStack(layers)
+            G = gb.Device.Gpu(dev)
+            xin = gb.Tensor.from_numpy(xs[HIDDEN][:1].cpu().numpy(), gb.GGmlType.F32, G)
+            post = gb.Tensor.from_numpy(np.array([shp.ctx - 1], np.int32), gb.GGmlType.I32, G)
+            for _ in range(3):
+                stack.step(xin, post)
+            dev.synchronize()
+            reps = max(20, args.steps // 4)
+            e0.record(stream)
+            for _ in range(reps):
+                stack.step(xin, post)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            us_layer = e0.elapsed_time(e1) * 1e3 / (reps * nl)
+            lbytes = layers[0].algorithmic_bytes()
+            return {"config": f"config4 shapes, {nl} distinct layers per launch, stream launches", "layers_per_launch": nl,
+                    "layer_steps_per_s": 1e6 / us_layer, "us_per_layer": us_layer, "kernels_per_layer": 1.0 / nl, "algorithmic_bytes": lbytes,
+                    "hbm_gbs": lbytes / us_layer / 1e3, "frac_of_measured_hbm": lbytes / us_layer / 1e3 / peak}
+
+        extra["decode_layer_persistent"] = measure_stack(8)
+        extra["decode_layer_persistent_1_layer_per_launch"] = measure_stack(1)
         if not args.no_cpu:
             # the same layer step on the CPU oracle (the reference's op sequence, mat-muls on its 4 fixed tasks)
             import oracle as O2
@@ -550,7 +583,7 @@ def run_ours(args):
                 oracle_layer_step(O2, shp, *li, shp.ctx - 1)
                 reps += 1
             cpu_layer_us = (time.perf_counter() - t0) / reps * 1e6
-            for key in ("decode_layer", "decode_layer_fused"):
+            for key in ("decode_layer", "decode_layer_fused", "decode_layer_persistent"):
                 extra[key]["cpu_us_4thr"] = cpu_layer_us
                 extra[key]["host_cpus"] = os.cpu_count()
         # config 3: prefill 4096 x 4096 x 512 tokens on the tcgen05 int8 path; config 2 at batch 4 and 8

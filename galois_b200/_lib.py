@@ -35,6 +35,19 @@ class GaloisPrologue(C.Structure):
     _fields_ = [("kind", C.c_int32), ("aux", C.c_void_p), ("eps", C.c_float)]
 
 
+class GaloisDecodeLayer(C.Structure):
+    """``galois_b200_decode_layer``: device pointers of one decoder layer for the persistent decode kernel."""
+
+    _fields_ = [(n, C.c_void_p) for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down", "attn_norm", "ffn_norm", "k_cache", "v_cache")]
+
+
+class GaloisDecodeShape(C.Structure):
+    """``galois_b200_decode_shape``."""
+
+    _fields_ = [("hidden", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32), ("ffn", C.c_int32), ("ctx", C.c_int32),
+                ("eps", C.c_float), ("rope_freq_base", C.c_float), ("rope_freq_scale", C.c_float)]
+
+
 _P, _F, _I, _I64, _SZ = C.c_void_p, C.c_float, C.c_int, C.c_int64, C.c_size_t
 _DP = C.POINTER(GaloisDim)
 
@@ -82,6 +95,8 @@ SIGNATURES = {
     "galois_b200_cpy_f32_f16": ([_P, _P, _DP, _P, _DP], _I),
     "galois_b200_cpy_f32_f16_pair": ([_P, _P, _DP, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_get_rows_q4_0_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
+    "galois_b200_decode_workspace_bytes": ([_P, C.POINTER(GaloisDecodeShape), C.POINTER(_SZ)], _I),
+    "galois_b200_decode_layers_f32": ([_P, C.POINTER(GaloisDecodeShape), C.POINTER(GaloisDecodeLayer), _I, _P, _P, _P, _P, _SZ], _I),
     "galois_b200_shard_rows": ([_I64, _I, _I, C.POINTER(_I64), C.POINTER(_I64)], _I),
     "galois_b200_ipc_export": ([_P, _P, C.c_char_p], _I),
     "galois_b200_ipc_import": ([_P, C.c_char_p, C.POINTER(_P)], _I),

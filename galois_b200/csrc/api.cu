@@ -10,6 +10,7 @@
 #include "mul_mat_q4_0_tc.cuh"
 #include "mmq_skinny.cuh"
 #include "gather.cuh"
+#include "decode_layer.cuh"
 #include "quantize.cuh"
 
 static char g_init_err[512] = "";
@@ -190,6 +191,7 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
         if (rc == 0) rc = gb_gemv_init(ctx);
         if (rc == 0) rc = gb_mmq_skinny_init(ctx);
         if (rc == 0) rc = gb_mm_tc_init(ctx);
+        if (rc == 0) rc = gb_decode_init(ctx);
         if (rc != 0) snprintf(g_init_err, sizeof(g_init_err), "%s", ctx->err);
     }
     if (rc != 0) {
@@ -289,7 +291,7 @@ static int check_dev_status(galois_b200_ctx* ctx) {
     GB_CUDA(ctx, cudaMemcpyAsync(&st, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (st != 0) {
-        GB_CUDA(ctx, cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream));
+        GB_CUDA(ctx, cudaMemsetAsync(ctx->dev_status, 0, 256, ctx->stream));  // the status and the grid-barrier words behind it
         return gb_fail(ctx, st, "a bounded device-side wait ran out (status %d)", st);
     }
     return 0;

@@ -1,0 +1,779 @@
+// One decode step (one token) of a stack of LLaMA-shaped decoder layers as ONE persistent cooperative
+// kernel: the op sequence a galois caller writes per layer (src/op.rs:3034-3341),
+//   rms_norm, mul, 3 x matmul(Q4_0), 2 x rope_custom, 2 x cpy (KV append), matmul(F16), soft_max (scaled,
+//   causal), matmul(F16), matmul(Q4_0), add, rms_norm, mul, 2 x matmul(Q4_0), unary(Silu), mul,
+//   matmul(Q4_0), add
+// walked by one CTA per SM with bounded grid barriers where a kernel boundary would be.  Every number is
+// formed exactly as the one-op kernels of this library form it (same lane decomposition of every dot
+// product, same order of every sum, the same f16 tables), so the result is bit-identical to running the
+// 22 ops one after the other; what changes is that nothing waits for a launch, and that every warp asks
+// for the weights of the NEXT phase before it arrives at a barrier, so HBM keeps streaming across it.
+//
+// Phases per layer (a grid barrier after each):
+//   1  x -> rms_norm * gain -> Q8_0 (every CTA for itself, in shared memory) -> rows of Wq, Wk, Wv
+//   2  rope(q) (every CTA, all heads, in shared memory); rope(k) + both cache appends (one CTA per head);
+//      scores = K cache . f16(q) (16 cache rows per chunk)
+//   3  per chunk of 8 V rows: soft_max of that head's scores (scaled, causal) in shared memory, then
+//      context = V cache . f16(probs)
+//   4  context -> Q8_0 -> rows of Wo, + x                         -> x2
+//   5  x2 -> rms_norm * gain -> Q8_0 -> rows of W_gate, W_up
+//   6  silu(gate) * up -> Q8_0 -> rows of W_down, + x2            -> the layer's output
+// Weights and cache rows travel HBM -> shared memory through per-warp rings of 1-D bulk copies
+// (cp.async.bulk completing on mbarriers, no multicast).  The cache row / column being appended in this
+// step is never taken from the ring: the value just computed is used in its place, so a ring copy may run
+// ahead of the append.
+//
+// Every wait is bounded: a barrier or a ring wait that runs out sets GALOIS_B200_E_TIMEOUT and an abort
+// word that makes all CTAs leave; nothing spins forever.
+#include "decode_layer.cuh"
+
+#include "gemv_q4_0.cuh"
+#include "gemv_q4_0_dev.cuh"
+#include "ptx.cuh"
+
+namespace {
+
+constexpr int DL_WARPS = 8;
+constexpr int DL_THREADS = DL_WARPS * 32;
+constexpr int DL_NSLOT = 3;                   // ring slots per warp
+constexpr int DL_SLOT = 6400;                 // bytes per slot (a 6192-byte row of K = 11008 fits)
+constexpr int DL_MAX_K = 16384;               // longest row the activation area holds
+constexpr int DL_MAX_VEC = 8192;              // hidden and ctx may not exceed this (floats of shared memory)
+constexpr int DL_MAX_PAIRS = 64;              // head_dim / 2 (head_dim is 128: sixteen lanes of eight halves per cache row)
+constexpr unsigned long long DL_WAIT_NS = 2000000000ull;
+
+// dev_status words used by this kernel (the buffer is 256 bytes, zeroed at init and after a time-out)
+constexpr int DL_W_COUNT = 16, DL_W_EXIT = 17, DL_W_ABORT = 18;
+
+struct dl_params {
+    int hidden, heads, head_dim, ffn, ctx, n_layers;
+    int plan_h, plan_f;   // row plan of K = hidden / K = ffn: 0 = 32 segments of 4 block pairs per pass (split), 1 = 3 passes of 2 pairs
+    float eps, theta_scale, freq_scale, kq_scale;
+    const float* x;       // [hidden]
+    const int32_t* pos;   // the token's position (one value)
+    float* out;           // [hidden]
+    float* ws;            // workspace, see dl_ws
+    int* status;          // the context's status words
+    const uint16_t* exp_lut;
+    const uint16_t* silu_lut;
+    galois_b200_decode_layer layers[GALOIS_B200_DECODE_MAX_LAYERS];
+};
+
+// workspace (floats): qkv[3H] | scores[heads * ctx] | ctxv[H] | x2[H] | gu[2F] | xa[H] | xb[H]
+struct dl_ws {
+    float *qkv, *scores, *ctxv, *x2, *gu, *xa, *xb;
+};
+__host__ __device__ inline dl_ws dl_carve(float* ws, int H, int heads, int ctx, int F) {
+    dl_ws w;
+    w.qkv = ws;
+    w.scores = w.qkv + 3 * (size_t)H;
+    w.ctxv = w.scores + (size_t)heads * ctx;
+    w.x2 = w.ctxv + H;
+    w.gu = w.x2 + H;
+    w.xa = w.gu + 2 * (size_t)F;
+    w.xb = w.xa + H;
+    return w;
+}
+inline size_t dl_ws_floats(int H, int heads, int ctx, int F) { return 3 * (size_t)H + (size_t)heads * ctx + 4 * (size_t)H + 2 * (size_t)F; }
+
+__device__ __forceinline__ unsigned long long dl_now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ unsigned dl_ld_acquire(const int* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ldcg_f(const float* p) { return __ldcg(p); }
+
+struct dl_geom {
+    int rpc_h, rpc_f;                 // rows per chunk of a K = hidden / K = ffn weight
+    uint32_t row_bytes_h, row_bytes_f;
+    int nchunks[6];
+    uint32_t chunk_bytes[6];
+};
+
+// Shared-memory map of a CTA.
+struct dl_smem {
+    dl_geom geom;
+    alignas(16) uint64_t bars[DL_WARPS * DL_NSLOT];
+    float red[40];
+    int flag;                           // this CTA has seen the abort word / a time-out
+    float cs[DL_MAX_PAIRS * 2];         // rope: {cos, sin} per pair
+    alignas(128) uint8_t act_qs[DL_MAX_K];  // Q8_0 quants of the current activation row, piece-major
+    alignas(128) uint8_t act_ds[DL_MAX_K / 32 * 8];  // {d, bits(-8 * sum)} per block, piece-major
+    alignas(128) float vec[DL_MAX_VEC];  // phase 2: rope(q) of all heads, rounded to f16; phase 3: the probabilities of one head
+};
+
+// Grid barrier number `index` (0, 1, 2, ... in the order every CTA meets them).  Returns false when the
+// kernel is being abandoned.
+__device__ bool dl_grid_barrier(int* words, unsigned index, dl_smem* S) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        bool ok = S->flag == 0;
+        if (ok) {
+            __threadfence();
+            atomicAdd(reinterpret_cast<unsigned*>(words + DL_W_COUNT), 1u);
+            const unsigned target = (index + 1u) * gridDim.x;
+            unsigned long long t0 = 0;
+            unsigned spins = 0;
+            while (dl_ld_acquire(words + DL_W_COUNT) < target) {
+                if ((++spins & 63u) == 0) {
+                    if (dl_ld_acquire(words + DL_W_ABORT) != 0) {
+                        ok = false;
+                        break;
+                    }
+                    const unsigned long long now = dl_now_ns();
+                    if (t0 == 0) t0 = now;
+                    if (now - t0 > DL_WAIT_NS) {
+                        atomicExch(words, GALOIS_B200_E_TIMEOUT);
+                        atomicExch(words + DL_W_ABORT, 1);
+                        ok = false;
+                        break;
+                    }
+                }
+            }
+        }
+        if (!ok) S->flag = 1;
+    }
+    __syncthreads();
+    return S->flag == 0;
+}
+
+// ---------------------------------------------------------------- the per-warp stream of chunks
+// What each phase streams through the rings.  A chunk is one bulk copy into one ring slot:
+//   phase 0  Wq | Wk | Wv rows   (rpc_h rows of K = hidden)      phase 3  Wo rows
+//   phase 1  K cache rows        (16 rows of head_dim halves)     phase 4  W_gate | W_up rows
+//   phase 2  V cache rows        (1 row of ctx halves)            phase 5  W_down rows (rpc_f rows of K = ffn)
+// Chunks of a phase are dealt round-robin over all warps of the grid: warp gw takes gw, gw + tw, ...
+__device__ __forceinline__ void dl_make_geom(const dl_params& P, dl_geom& g) {
+    const int nsegk_h = P.hidden / 256, nsegk_f = P.ffn / 256;  // split plans: segments of 4 block pairs
+    g.rpc_h = P.plan_h == 0 ? 32 / nsegk_h : 1;
+    g.rpc_f = P.plan_f == 0 ? 32 / nsegk_f : 1;
+    g.row_bytes_h = (uint32_t)(P.hidden / 32) * GB_Q4_BYTES;
+    g.row_bytes_f = (uint32_t)(P.ffn / 32) * GB_Q4_BYTES;
+    g.nchunks[0] = 3 * P.hidden / g.rpc_h;
+    g.nchunks[1] = P.heads * P.ctx / 16;
+    g.nchunks[2] = P.heads * P.head_dim;
+    g.nchunks[3] = P.hidden / g.rpc_h;
+    g.nchunks[4] = 2 * P.ffn / g.rpc_h;
+    g.nchunks[5] = P.hidden / g.rpc_f;
+    g.chunk_bytes[0] = g.chunk_bytes[3] = g.chunk_bytes[4] = g.rpc_h * g.row_bytes_h;
+    g.chunk_bytes[1] = 16u * P.head_dim * 2u;
+    g.chunk_bytes[2] = (uint32_t)P.ctx * 2u;
+    g.chunk_bytes[5] = g.rpc_f * g.row_bytes_f;
+}
+
+// Source address of chunk c of phase p of layer L.
+__device__ __forceinline__ const uint8_t* dl_chunk_src(const dl_params& P, const dl_geom& g, const galois_b200_decode_layer& L, int p, int c) {
+    switch (p) {
+        case 0: {
+            const int r0 = c * g.rpc_h, m = r0 / P.hidden, r = r0 - m * P.hidden;
+            const void* w = m == 0 ? L.wq : (m == 1 ? L.wk : L.wv);
+            return (const uint8_t*)w + (size_t)r * g.row_bytes_h;
+        }
+        case 1: return (const uint8_t*)L.k_cache + (size_t)c * g.chunk_bytes[1];
+        case 2: return (const uint8_t*)L.v_cache + (size_t)c * g.chunk_bytes[2];
+        case 3: return (const uint8_t*)L.wo + (size_t)c * g.chunk_bytes[3];
+        case 4: {
+            const int r0 = c * g.rpc_h, m = r0 / P.ffn, r = r0 - m * P.ffn;
+            return (const uint8_t*)(m == 0 ? L.w_gate : L.w_up) + (size_t)r * g.row_bytes_h;
+        }
+        default: return (const uint8_t*)L.w_down + (size_t)c * g.chunk_bytes[5];
+    }
+}
+
+// Issue side and consume side of one warp's ring.  All members are warp-uniform.
+struct dl_stream {
+    uint32_t issued, consumed;  // chunks since the kernel began
+    int cph, cj;                // next chunk to issue: phase index (layer * 6 + p), j-th chunk of this warp in it
+    int gw, tw;
+    uint64_t* bars;
+    uint8_t* ring;
+};
+
+// Issues copies until the ring is full, nothing is left, or the next chunk lies beyond phase `upto`.
+__device__ __forceinline__ void dl_pump(dl_stream& st, const dl_params& P, const dl_smem* S, int upto, int lane) {
+    const dl_geom& g = S->geom;
+    const int end = P.n_layers * 6;
+    while (st.issued - st.consumed < (uint32_t)DL_NSLOT) {
+        // skip phases that hold no (further) chunk for this warp
+        while (st.cph < end && st.gw + st.cj * st.tw >= g.nchunks[st.cph % 6]) st.cph++, st.cj = 0;
+        if (st.cph >= end || st.cph > upto) break;
+        const int p = st.cph % 6, c = st.gw + st.cj * st.tw;
+        if (lane == 0) {
+            const uint32_t slot = st.issued % DL_NSLOT;
+            const uint32_t bytes = g.chunk_bytes[p];
+            mbar_expect_tx(&st.bars[slot], bytes);
+            bulk_g2s(st.ring + slot * DL_SLOT, dl_chunk_src(P, g, P.layers[st.cph / 6], p, c), bytes, &st.bars[slot]);
+        }
+        st.issued++;
+        st.cj++;
+    }
+}
+
+// Waits for the oldest chunk in flight; returns its slot, or nullptr after a time-out.
+__device__ __forceinline__ const uint8_t* dl_front(dl_stream& st) {
+    const uint32_t slot = st.consumed % DL_NSLOT;
+    if (!mbar_wait_bounded(&st.bars[slot], (st.consumed / DL_NSLOT) & 1u)) return nullptr;
+    return st.ring + slot * DL_SLOT;
+}
+// The warp has finished reading the front chunk.
+__device__ __forceinline__ void dl_pop(dl_stream& st) {
+    __syncwarp();
+    st.consumed++;
+}
+
+// ---------------------------------------------------------------- activation row -> Q8_0 in shared memory
+// <BlockQ8_0 as QuantType>::from_f32 (src/ggml_quants.rs:736-764 of galois) of one row of K floats, by
+// the whole CTA, into the piece-major layout load_act reads.  Eight lanes own a block.  `load4(e)` yields
+// elements e .. e + 3 of the row (after whatever op pair precedes the mat-mul).
+template <int SEG, class F>
+__device__ __forceinline__ void dl_quantize_row(dl_smem* S, int K, F load4) {
+    const int nblk = K >> 5, nsegk = nblk / (2 * SEG);
+    const int sub = threadIdx.x & 7;
+    for (int blk = (int)(threadIdx.x >> 3); blk - (int)((threadIdx.x & 31) >> 3) < nblk; blk += DL_THREADS / 8) {
+        const float4 v = blk < nblk ? load4(blk * 32 + sub * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float d = __fdiv_rn(amax, 127.0f);
+        const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+        // `as i8` in Rust saturates and maps NaN to 0; so does (int) followed by the clamp
+        const int q0 = max(-128, min(127, (int)roundf(__fmul_rn(v.x, id))));
+        const int q1 = max(-128, min(127, (int)roundf(__fmul_rn(v.y, id))));
+        const int q2 = max(-128, min(127, (int)roundf(__fmul_rn(v.z, id))));
+        const int q3 = max(-128, min(127, (int)roundf(__fmul_rn(v.w, id))));
+        int sum = q0 + q1 + q2 + q3;
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (blk < nblk) {
+            const int seg = blk / (2 * SEG), bi = blk % (2 * SEG);
+            const uint32_t packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+            *reinterpret_cast<uint32_t*>(S->act_qs + ((2 * bi + (sub >> 2)) * nsegk + seg) * 16 + (sub & 3) * 4) = packed;
+            if (sub == 0) {
+                uint32_t* dp = reinterpret_cast<uint32_t*>(S->act_ds + ((bi >> 1) * nsegk + seg) * 16 + (bi & 1) * 8);
+                dp[0] = __float_as_uint(__half2float(__float2half_rn(d)));
+                dp[1] = (uint32_t)(-8 * sum);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- one Q4_0 mat-vec phase
+// Rows of an [N][K] Q4_0 weight against the quantised row in shared memory; the lane decomposition and
+// the order of the sums are those of gemv_q4_0_kernel<1, SEG, SPLIT, NPASS> (one activation row, hoisted).
+// dst[row] = (res ? res[row] + sum : sum).  Chunk c of the phase holds rows c * rpc .. + rpc - 1.
+template <int SEG, bool SPLIT, int NPASS>
+__device__ __forceinline__ bool dl_gemv_phase(dl_stream& st, const dl_params& P, dl_smem* S, int ph, int K, int rpc, float* __restrict__ dst,
+                                              const float* __restrict__ res, int lane) {
+    const int nblk = K >> 5, nsegk = nblk / (2 * SEG);
+    int yh[NPASS][16 * SEG];
+    float4 dh[NPASS][SEG];
+#pragma unroll
+    for (int q = 0; q < NPASS; q++) {
+        const int sg = SPLIT ? (lane & (nsegk - 1)) : lane + 32 * q;
+        if (sg < nsegk) {
+            load_act<SEG>(S->act_qs, S->act_ds, nsegk, sg, yh[q], dh[q]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16 * SEG; i++) yh[q][i] = 0;
+#pragma unroll
+            for (int i = 0; i < SEG; i++) dh[q][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    const int nchunks = S->geom.nchunks[ph % 6];
+    for (int c = st.gw; c < nchunks; c += st.tw) {
+        const uint8_t* buf = dl_front(st);
+        if (buf == nullptr) return false;
+        float acc = 0.0f;
+#pragma unroll
+        for (int q = 0; q < NPASS; q++) {
+            const int sg = lane + 32 * q;  // SPLIT: NPASS == 1 and the chunk is exactly 32 segments
+            if (SPLIT || sg < nsegk) {
+                uint32_t t[9 * SEG];
+                load_segment<SEG>(buf + sg * (36 * SEG), t);
+#pragma unroll
+                for (int p = 0; p < SEG; p++) acc = pair_dot(t + 9 * p, yh[q] + 16 * p, dh[q][p], acc);
+            }
+        }
+        dl_pop(st);
+        dl_pump(st, P, S, ph + 1, lane);
+        const int row0 = c * rpc;
+        if (SPLIT) {
+            float v = acc;
+            for (int o = nsegk >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if ((lane & (nsegk - 1)) == 0) {
+                const int row = row0 + lane / nsegk;
+                if (res) v = __fadd_rn(__ldcg(res + row), v);
+                dst[row] = v;
+            }
+        } else {
+            float v = gb_warp_sum(acc);
+            if (lane == 0) {
+                if (res) v = __fadd_rn(__ldcg(res + row0), v);
+                dst[row0] = v;
+            }
+        }
+    }
+    return true;
+}
+
+// The two row plans the kernel holds (see dl_params::plan_h / plan_f).
+__device__ __forceinline__ bool dl_gemv(int plan, dl_stream& st, const dl_params& P, dl_smem* S, int ph, int K, int rpc, float* dst,
+                                        const float* res, int lane) {
+    if (plan == 0) return dl_gemv_phase<4, true, 1>(st, P, S, ph, K, rpc, dst, res, lane);
+    return dl_gemv_phase<2, false, 3>(st, P, S, ph, K, rpc, dst, res, lane);
+}
+template <class F>
+__device__ __forceinline__ void dl_quantize(int plan, dl_smem* S, int K, F load4) {
+    if (plan == 0)
+        dl_quantize_row<4>(S, K, load4);
+    else
+        dl_quantize_row<2>(S, K, load4);
+}
+
+// ---------------------------------------------------------------- small pieces of the other ops
+// gb_row_sumsq_128 (common.cuh) for a CTA of DL_THREADS: the first 128 threads form the sum in exactly its
+// order, everybody receives it.
+__device__ __forceinline__ float dl_row_sumsq(const float* __restrict__ xr, int n, float* red) {
+    float s = 0.0f;
+    if (threadIdx.x < 128) {
+        for (int i = threadIdx.x; i < n; i += 128) {
+            const float v = __ldcg(xr + i);
+            s = fmaf(v, v, s);
+        }
+        s = gb_warp_sum(s);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    }
+    __syncthreads();
+    const float t = ((red[0] + red[1]) + red[2]) + red[3];
+    __syncthreads();
+    return t;
+}
+
+__device__ __forceinline__ uint32_t dl_pack_h2(float lo, float hi) {
+    return (uint32_t)__half_as_ushort(__float2half_rn(lo)) | ((uint32_t)__half_as_ushort(__float2half_rn(hi)) << 16);
+}
+// Replaces half number idx (0..7) of the eight halves in `raw`.
+__device__ __forceinline__ void dl_patch_half(uint4& raw, int idx, float value) {
+    const uint32_t bits = __half_as_ushort(__float2half_rn(value));
+    const uint32_t mask = (idx & 1) ? 0x0000ffffu : 0xffff0000u, ins = (idx & 1) ? bits << 16 : bits;
+    switch (idx >> 1) {
+        case 0: raw.x = (raw.x & mask) | ins; break;
+        case 1: raw.y = (raw.y & mask) | ins; break;
+        case 2: raw.z = (raw.z & mask) | ins; break;
+        default: raw.w = (raw.w & mask) | ins; break;
+    }
+}
+
+// Rope of one adjacent pair (RopeCustom::f_x_y_x mode 0, src/op.rs:2740-2745; zeta = 1).
+__device__ __forceinline__ void dl_rope_pair(float x0, float x1, float c, float s, float& y0, float& y1) {
+    y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+    y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+}
+
+// soft_max_kernel<true> (rowops.cu) of one row of `nc` scores into S->vec, each probability rounded to f16
+// as the F16 mat-mul that consumes it rounds its f32 operand.  The row is summed exactly as a block of VT =
+// row_threads(nc) threads sums it there: thread t of this CTA plays the virtual threads t, t + 256, ...
+// Returns false (and zero-fills) when every column is masked, like the one-op kernel.
+template <int MAXV>
+__device__ __forceinline__ bool dl_soft_max_row(dl_smem* S, const float* __restrict__ xr, int nc, int limit, float scale, int VT,
+                                                const uint16_t* __restrict__ exp_lut) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // the maximum does not depend on the order it is formed in
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < limit; i += DL_THREADS) mx = fmaxf(mx, __fmul_rn(__ldcg(xr + i), scale));
+    mx = gb_warp_max(mx);
+    if (lane == 0) S->red[warp] = mx;
+    __syncthreads();
+    mx = S->red[0];
+#pragma unroll
+    for (int w = 1; w < DL_WARPS; w++) mx = fmaxf(mx, S->red[w]);
+    __syncthreads();
+    // exponentials and per-virtual-thread sums
+    const int nvw = VT >> 5;  // virtual warps
+#pragma unroll
+    for (int m = 0; m < MAXV; m++) {
+        const int vt = threadIdx.x + DL_THREADS * m;
+        if (vt - lane < VT) {  // warp-uniform: virtual warps are whole
+            float sum = 0.0f;
+            for (int i = vt; i < nc; i += VT) {
+                float val = 0.0f;
+                if (i < limit) {
+                    const float v = __fmul_rn(__ldcg(xr + i), scale);
+                    if (v != -INFINITY) {
+                        const unsigned short h = __half_as_ushort(__float2half_rn(__fsub_rn(v, mx)));
+                        val = __half2float(__ushort_as_half(__ldg(exp_lut + h)));
+                    }
+                }
+                sum += val;
+                S->vec[i] = val;
+            }
+            sum = gb_warp_sum(sum);
+            if (lane == 0) S->red[warp + DL_WARPS * m] = sum;
+        }
+    }
+    __syncthreads();
+    float t = (threadIdx.x < nvw) ? S->red[threadIdx.x] : 0.0f;
+    if (warp == 0) {
+        t = gb_warp_sum(t);
+        if (lane == 0) S->red[32] = t;
+    }
+    __syncthreads();
+    const float sum = S->red[32];
+    if (!(sum > 0.0f)) {
+        for (int i = threadIdx.x; i < nc; i += DL_THREADS) S->vec[i] = 0.0f;
+        __syncthreads();
+        return false;
+    }
+    const float inv = __fdiv_rn(1.0f, sum);
+    for (int i = threadIdx.x; i < nc; i += DL_THREADS) S->vec[i] = __half2float(__float2half_rn(__fmul_rn(S->vec[i], inv)));
+    __syncthreads();
+    return true;
+}
+
+// A ring wait ran out in this warp: tell the host and make every CTA leave at its next barrier.
+__device__ __forceinline__ void dl_give_up(int* words, dl_smem* S, int lane) {
+    if (lane == 0) {
+        atomicExch(words, GALOIS_B200_E_TIMEOUT);
+        atomicExch(words + DL_W_ABORT, 1);
+        S->flag = 1;
+    }
+}
+
+// ---------------------------------------------------------------- the kernel
+__global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __grid_constant__ dl_params P) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    dl_smem* S = reinterpret_cast<dl_smem*>(smem_raw);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int H = P.hidden, F = P.ffn, hd = P.head_dim, ctx = P.ctx, heads = P.heads;
+    int* words = P.status;
+
+    if (threadIdx.x == 0) {
+        dl_make_geom(P, S->geom);
+        S->flag = 0;
+    }
+    dl_stream st;
+    st.issued = st.consumed = 0;
+    st.cph = st.cj = 0;
+    st.gw = blockIdx.x * DL_WARPS + warp;
+    st.tw = gridDim.x * DL_WARPS;
+    st.bars = S->bars + warp * DL_NSLOT;
+    st.ring = smem_raw + ((sizeof(dl_smem) + 127) & ~(size_t)127) + (size_t)warp * DL_NSLOT * DL_SLOT;
+    if (lane == 0) {
+        for (int i = 0; i < DL_NSLOT; i++) mbar_init(&st.bars[i], 1);
+        fence_proxy_async();
+    }
+    __syncthreads();
+    dl_pump(st, P, S, 0, lane);  // weights are nobody's output: the first copies leave before anything else happens
+
+    const dl_ws W = dl_carve(P.ws, H, heads, ctx, F);
+    const int pos = __ldg(P.pos);
+    const int rpc_h = S->geom.rpc_h, rpc_f = S->geom.rpc_f;
+    const int VT = min(1024, max(32, (((ctx + 3) / 4 + 31) / 32) * 32));  // row_threads(ctx) of the one-op soft_max
+    unsigned bar = 0;
+    bool ok = true;
+    if (pos < 0 || pos >= ctx) {
+        // the reference would index its cache out of bounds and panic
+        if (threadIdx.x == 0) atomicExch(words, GALOIS_B200_E_BADARG);
+        return;
+    }
+
+    for (int l = 0; l < P.n_layers; l++) {
+        const galois_b200_decode_layer& L = P.layers[l];
+        const float* xin = l == 0 ? P.x : ((l & 1) ? W.xa : W.xb);
+        float* xout = l == P.n_layers - 1 ? P.out : ((l & 1) ? W.xb : W.xa);
+        const int ph = l * 6;
+
+        // ---- phase 0: rms_norm * gain -> Q8_0 -> q | k | v
+        {
+            const float scale = gb_rms_scale(dl_row_sumsq(xin, H, S->red), H, P.eps);
+            const float* gain = L.attn_norm;
+            dl_quantize(P.plan_h, S, H, [&](int e) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(xin + e)), g = __ldg(reinterpret_cast<const float4*>(gain + e));
+                return make_float4(__fmul_rn(__fmul_rn(v.x, scale), g.x), __fmul_rn(__fmul_rn(v.y, scale), g.y),
+                                   __fmul_rn(__fmul_rn(v.z, scale), g.z), __fmul_rn(__fmul_rn(v.w, scale), g.w));
+            });
+            __syncthreads();
+            dl_pump(st, P, S, ph + 1, lane);
+            ok = dl_gemv(P.plan_h, st, P, S, ph, H, rpc_h, W.qkv, nullptr, lane);
+        }
+        if (!ok) dl_give_up(words, S, lane);
+        if (!dl_grid_barrier(words, bar++, S)) return;
+
+        // ---- phase 1: rope, cache appends, scores
+        {
+            const float* q = W.qkv;
+            const float* k = W.qkv + H;
+            const float* v = W.qkv + 2 * H;
+            const int npair = hd / 2;
+            if ((int)threadIdx.x < npair) {
+                // theta_i = freq_scale * pos * theta_scale^i, one f32 multiply at a time (src/op.rs:2717-2734)
+                float theta = __fmul_rn(P.freq_scale, (float)pos);
+                for (int at = 0; at < (int)threadIdx.x; at++) theta = __fmul_rn(theta, P.theta_scale);
+                S->cs[2 * threadIdx.x] = cosf(theta);
+                S->cs[2 * threadIdx.x + 1] = sinf(theta);
+            }
+            __syncthreads();
+            for (int idx = threadIdx.x; idx < H / 2; idx += DL_THREADS) {
+                const int i = idx % npair;
+                float y0, y1;
+                dl_rope_pair(__ldcg(q + 2 * idx), __ldcg(q + 2 * idx + 1), S->cs[2 * i], S->cs[2 * i + 1], y0, y1);
+                S->vec[2 * idx] = __half2float(__float2half_rn(y0));  // the F16 mat-mul rounds its f32 operand to f16
+                S->vec[2 * idx + 1] = __half2float(__float2half_rn(y1));
+            }
+            for (int h = blockIdx.x; h < heads; h += gridDim.x) {
+                // galois_cpy f32 -> f16 of rope(k) into row `pos` of the K cache and of v into column `pos` of the V cache
+                __half* kc = reinterpret_cast<__half*>(L.k_cache) + ((size_t)h * ctx + pos) * hd;
+                __half* vc = reinterpret_cast<__half*>(L.v_cache) + (size_t)h * hd * ctx + pos;
+                if ((int)threadIdx.x < npair) {
+                    const int i = threadIdx.x;
+                    float y0, y1;
+                    dl_rope_pair(__ldcg(k + h * hd + 2 * i), __ldcg(k + h * hd + 2 * i + 1), S->cs[2 * i], S->cs[2 * i + 1], y0, y1);
+                    kc[2 * i] = __float2half_rn(y0);
+                    kc[2 * i + 1] = __float2half_rn(y1);
+                }
+                if ((int)threadIdx.x < hd) vc[(size_t)threadIdx.x * ctx] = __float2half_rn(__ldcg(v + h * hd + threadIdx.x));
+            }
+            __syncthreads();
+            // scores: 16 cache rows per chunk, a row per 16 lanes (8 halves per lane), xor tree over the 16 lanes
+            const int grp = lane >> 4, sub = lane & 15;
+            const int nchunks = S->geom.nchunks[1];
+            dl_pump(st, P, S, ph + 2, lane);
+            for (int c = st.gw; c < nchunks; c += st.tw) {
+                const uint8_t* buf = dl_front(st);
+                if (buf == nullptr) {
+                    ok = false;
+                    break;
+                }
+                const int r0 = c * 16, h = r0 / ctx, j0 = r0 - h * ctx;
+                float xh[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) xh[i] = S->vec[h * hd + sub * 8 + i];
+                float res[8];
+#pragma unroll
+                for (int rr = 0; rr < 8; rr++) {
+                    const int r = 2 * rr + grp;
+                    uint4 raw = *reinterpret_cast<const uint4*>(buf + (size_t)r * hd * 2 + sub * 16);
+                    if (j0 + r == pos) {
+                        // the row being appended in this step: its values come from rope(k), not from the ring
+                        uint32_t hh[4];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int pi = sub * 4 + i;
+                            float y0, y1;
+                            dl_rope_pair(__ldcg(k + h * hd + 2 * pi), __ldcg(k + h * hd + 2 * pi + 1), S->cs[2 * pi], S->cs[2 * pi + 1], y0, y1);
+                            hh[i] = dl_pack_h2(y0, y1);
+                        }
+                        raw = make_uint4(hh[0], hh[1], hh[2], hh[3]);
+                    }
+                    const __half2* hp = reinterpret_cast<const __half2*>(&raw);
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float2 f = __half22float2(hp[i]);
+                        acc = fmaf(f.x, xh[2 * i], acc);
+                        acc = fmaf(f.y, xh[2 * i + 1], acc);
+                    }
+                    res[rr] = acc;
+                }
+                dl_pop(st);
+                dl_pump(st, P, S, ph + 2, lane);
+#pragma unroll
+                for (int rr = 0; rr < 8; rr++) {
+                    float vsum = res[rr];
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) vsum += __shfl_xor_sync(0xffffffffu, vsum, o);
+                    if (sub == 0) W.scores[(size_t)h * ctx + j0 + 2 * rr + grp] = vsum;
+                }
+            }
+        }
+        if (!ok) dl_give_up(words, S, lane);
+        if (!dl_grid_barrier(words, bar++, S)) return;
+
+        // ---- phase 2: soft_max of the head a step's 8 rows belong to, then context = V cache . f16(probs)
+        {
+            const float* v = W.qkv + 2 * H;
+            const int nrows = S->geom.nchunks[2];
+            const int limit = pos + 1 < ctx ? (pos + 1 < 0 ? 0 : pos + 1) : ctx;
+            dl_pump(st, P, S, ph + 3, lane);
+            for (int base = blockIdx.x * DL_WARPS; base < nrows; base += st.tw) {
+                const int h = base / hd;
+                if (!dl_soft_max_row<4>(S, W.scores + (size_t)h * ctx, ctx, limit, P.kq_scale, VT, P.exp_lut) && threadIdx.x == 0)
+                    atomicExch(words, GALOIS_B200_E_BADARG);
+                const int c = base + warp;  // this warp's row: element d of head h
+                const uint8_t* buf = ok ? dl_front(st) : nullptr;  // after a time-out the warp only keeps the CTA's barriers company
+                if (buf == nullptr) ok = false;
+                float acc = 0.0f;
+                for (int kk = lane * 8; ok && kk < ctx; kk += 256) {
+                    uint4 raw = *reinterpret_cast<const uint4*>(buf + (size_t)kk * 2);
+                    if (pos >= kk && pos < kk + 8) {
+                        // the column being appended in this step
+                        dl_patch_half(raw, pos - kk, __ldcg(v + c));
+                    }
+                    const __half2* hp = reinterpret_cast<const __half2*>(&raw);
+                    const float4 p0 = *reinterpret_cast<const float4*>(S->vec + kk), p1 = *reinterpret_cast<const float4*>(S->vec + kk + 4);
+                    const float xp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float2 f = __half22float2(hp[i]);
+                        acc = fmaf(f.x, xp[2 * i], acc);
+                        acc = fmaf(f.y, xp[2 * i + 1], acc);
+                    }
+                }
+                if (ok) {
+                    dl_pop(st);
+                    dl_pump(st, P, S, ph + 3, lane);
+                }
+                acc = gb_warp_sum(acc);
+                if (lane == 0 && ok) W.ctxv[c] = acc;
+                __syncthreads();  // the probabilities are overwritten by the next step
+            }
+        }
+        if (!ok) dl_give_up(words, S, lane);
+        if (!dl_grid_barrier(words, bar++, S)) return;
+
+        // ---- phase 3: context -> Q8_0 -> Wo rows, + x -> x2
+        dl_quantize(P.plan_h, S, H, [&](int e) { return __ldcg(reinterpret_cast<const float4*>(W.ctxv + e)); });
+        __syncthreads();
+        dl_pump(st, P, S, ph + 4, lane);
+        ok = dl_gemv(P.plan_h, st, P, S, ph + 3, H, rpc_h, W.x2, xin, lane);
+        if (!ok) dl_give_up(words, S, lane);
+        if (!dl_grid_barrier(words, bar++, S)) return;
+
+        // ---- phase 4: rms_norm * gain -> Q8_0 -> gate | up
+        {
+            const float scale = gb_rms_scale(dl_row_sumsq(W.x2, H, S->red), H, P.eps);
+            const float* gain = L.ffn_norm;
+            dl_quantize(P.plan_h, S, H, [&](int e) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(W.x2 + e)), g = __ldg(reinterpret_cast<const float4*>(gain + e));
+                return make_float4(__fmul_rn(__fmul_rn(v.x, scale), g.x), __fmul_rn(__fmul_rn(v.y, scale), g.y),
+                                   __fmul_rn(__fmul_rn(v.z, scale), g.z), __fmul_rn(__fmul_rn(v.w, scale), g.w));
+            });
+            __syncthreads();
+            dl_pump(st, P, S, ph + 5, lane);
+            ok = dl_gemv(P.plan_h, st, P, S, ph + 4, H, rpc_h, W.gu, nullptr, lane);
+        }
+        if (!ok) dl_give_up(words, S, lane);
+        if (!dl_grid_barrier(words, bar++, S)) return;
+
+        // ---- phase 5: silu(gate) * up -> Q8_0 -> W_down rows, + x2 -> the layer's output
+        {
+            const float* gate = W.gu;
+            const float* up = W.gu + F;
+            const uint16_t* lut = P.silu_lut;
+            dl_quantize(P.plan_f, S, F, [&](int e) {
+                const float4 g = __ldcg(reinterpret_cast<const float4*>(gate + e)), u = __ldcg(reinterpret_cast<const float4*>(up + e));
+                // f32::vec_silu through the f16 table (src/lib.rs:543-549), then Mul::f
+                return make_float4(__fmul_rn(__half2float(__ushort_as_half(__ldg(lut + __half_as_ushort(__float2half_rn(g.x))))), u.x),
+                                   __fmul_rn(__half2float(__ushort_as_half(__ldg(lut + __half_as_ushort(__float2half_rn(g.y))))), u.y),
+                                   __fmul_rn(__half2float(__ushort_as_half(__ldg(lut + __half_as_ushort(__float2half_rn(g.z))))), u.z),
+                                   __fmul_rn(__half2float(__ushort_as_half(__ldg(lut + __half_as_ushort(__float2half_rn(g.w))))), u.w));
+            });
+            __syncthreads();
+            dl_pump(st, P, S, ph + 6, lane);
+            ok = dl_gemv(P.plan_f, st, P, S, ph + 5, F, rpc_f, xout, W.x2, lane);
+        }
+        if (!ok) dl_give_up(words, S, lane);
+        if (l + 1 < P.n_layers && !dl_grid_barrier(words, bar++, S)) return;
+    }
+    if (!ok) return;
+    // the last CTA to get here puts the barrier words back to zero for the next launch
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(reinterpret_cast<unsigned*>(words + DL_W_EXIT), 1u) == gridDim.x - 1) {
+            words[DL_W_COUNT] = 0;
+            words[DL_W_EXIT] = 0;
+            __threadfence();
+        }
+    }
+}
+
+}  // namespace
+
+static size_t dl_smem_bytes() { return ((sizeof(dl_smem) + 127) & ~(size_t)127) + (size_t)DL_WARPS * DL_NSLOT * DL_SLOT; }
+
+int gb_decode_init(galois_b200_ctx* ctx) {
+    GB_CUDA(ctx, cudaFuncSetAttribute(decode_layers_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dl_smem_bytes()));
+    return 0;
+}
+
+// 0 / 1 = the row plan of dl_params for rows of K elements, -1 = the one-op GEMV would deal such a row differently.
+static int dl_plan_of(galois_b200_ctx* ctx, int64_t K) {
+    int seg = 0, split = 0, npass = 0;
+    if (!gb_gemv_row_plan(ctx, K, &seg, &split, &npass)) return -1;
+    if (seg == 4 && split && npass == 1) return 0;
+    if (seg == 2 && !split && npass == 3) return 1;
+    return -1;
+}
+
+static int dl_check_shape(galois_b200_ctx* ctx, const galois_b200_decode_shape* s, int* plan_h, int* plan_f) {
+    if (!s) return gb_fail(ctx, GALOIS_B200_E_BADARG, "decode_layers: null shape");
+    if (s->hidden < 256 || s->hidden % 256 != 0 || s->hidden > DL_MAX_VEC || s->ffn < 256 || s->ffn % 256 != 0 || s->ffn > DL_MAX_K)
+        return gb_fail(ctx, GALOIS_B200_E_UNSUPPORTED, "decode_layers: hidden (<= %d) and ffn (<= %d) must be multiples of 256", DL_MAX_VEC, DL_MAX_K);
+    if (s->head_dim != 128 || s->heads < 1 || (int64_t)s->heads * s->head_dim != s->hidden)
+        return gb_fail(ctx, GALOIS_B200_E_UNSUPPORTED, "decode_layers: head_dim must be 128 and heads * head_dim == hidden");
+    if (s->ctx < 256 || s->ctx % 256 != 0 || s->ctx * 2 > DL_SLOT)
+        return gb_fail(ctx, GALOIS_B200_E_UNSUPPORTED, "decode_layers: ctx must be a multiple of 256 in [256, %d]", DL_SLOT / 2 / 256 * 256);
+    *plan_h = dl_plan_of(ctx, s->hidden);
+    *plan_f = dl_plan_of(ctx, s->ffn);
+    if (*plan_h != 0) return gb_fail(ctx, GALOIS_B200_E_UNSUPPORTED, "decode_layers: hidden must be 256 * 2^m (rows dealt as 32 segments of 8 blocks)");
+    if (*plan_f < 0) return gb_fail(ctx, GALOIS_B200_E_UNSUPPORTED, "decode_layers: no row plan for ffn = %d in this kernel", s->ffn);
+    if ((2 * (int64_t)s->ffn) % (32 / (s->hidden / 256)) != 0) return gb_fail(ctx, GALOIS_B200_E_UNSUPPORTED, "decode_layers: ffn does not fill whole chunks");
+    return 0;
+}
+
+extern "C" int galois_b200_decode_workspace_bytes(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, size_t* out_bytes) {
+    GB_CHECK_CTX(ctx);
+    int ph, pf;
+    const int rc = dl_check_shape(ctx, shape, &ph, &pf);
+    if (rc) return rc;
+    if (!out_bytes) return gb_fail(ctx, GALOIS_B200_E_BADARG, "decode_workspace_bytes: null pointer");
+    *out_bytes = dl_ws_floats(shape->hidden, shape->heads, shape->ctx, shape->ffn) * sizeof(float);
+    return 0;
+}
+
+extern "C" int galois_b200_decode_layers_f32(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, const galois_b200_decode_layer* layers,
+                                             int n_layers, const float* x, const int32_t* pos, float* out, void* workspace,
+                                             size_t workspace_bytes) {
+    GB_CHECK_CTX(ctx);
+    dl_params P;
+    memset(&P, 0, sizeof(P));
+    int rc = dl_check_shape(ctx, shape, &P.plan_h, &P.plan_f);
+    if (rc) return rc;
+    if (n_layers < 1 || n_layers > GALOIS_B200_DECODE_MAX_LAYERS)
+        return gb_fail(ctx, GALOIS_B200_E_BADARG, "decode_layers: %d layers (1..%d per call)", n_layers, GALOIS_B200_DECODE_MAX_LAYERS);
+    if (!layers || !x || !pos || !out || !workspace) return gb_fail(ctx, GALOIS_B200_E_BADARG, "decode_layers: null pointer");
+    if (workspace_bytes < dl_ws_floats(shape->hidden, shape->heads, shape->ctx, shape->ffn) * sizeof(float))
+        return gb_fail(ctx, GALOIS_B200_E_NOMEM, "decode_layers: workspace too small (galois_b200_decode_workspace_bytes)");
+    if ((uintptr_t)x % 16 || (uintptr_t)out % 16 || (uintptr_t)workspace % 16 || (uintptr_t)pos % 4)
+        return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "decode_layers: x, out and the workspace must be 16-byte aligned");
+    for (int l = 0; l < n_layers; l++) {
+        const galois_b200_decode_layer& L = layers[l];
+        const void* ptrs[] = {L.wq, L.wk, L.wv, L.wo, L.w_gate, L.w_up, L.w_down, L.attn_norm, L.ffn_norm, L.k_cache, L.v_cache};
+        for (const void* q : ptrs) {
+            if (!q) return gb_fail(ctx, GALOIS_B200_E_BADARG, "decode_layers: null pointer in layer %d", l);
+            if ((uintptr_t)q % 16) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "decode_layers: layer %d holds a pointer that is not 16-byte aligned", l);
+        }
+        P.layers[l] = L;
+    }
+    P.hidden = shape->hidden, P.heads = shape->heads, P.head_dim = shape->head_dim, P.ffn = shape->ffn, P.ctx = shape->ctx;
+    P.n_layers = n_layers;
+    P.eps = shape->eps;
+    P.theta_scale = powf(shape->rope_freq_base, -2.0f / (float)shape->head_dim);  // libm powf on the host, as the CPU path does (src/op.rs:2697)
+    P.freq_scale = shape->rope_freq_scale;
+    P.kq_scale = (float)(1.0 / sqrt((double)shape->head_dim));
+    P.x = x, P.pos = pos, P.out = out, P.ws = (float*)workspace;
+    P.status = ctx->dev_status;
+    P.exp_lut = ctx->exp_lut, P.silu_lut = ctx->silu_lut;
+    // one CTA per SM, all resident at once (cooperative launch): the grid barriers rely on it
+    void* args[] = {&P};
+    GB_CUDA(ctx, cudaLaunchCooperativeKernel((const void*)decode_layers_kernel, dim3((unsigned)ctx->sm_count), dim3(DL_THREADS), args, dl_smem_bytes(),
+                                             ctx->stream));
+    GB_LAUNCHED(ctx, "decode_layers");
+    return 0;
+}

@@ -36,6 +36,7 @@
 #include "gather.cuh"
 #include "gemv_q4_0.cuh"
 #include "ptx.cuh"
+#include "gemv_q4_0_dev.cuh"
 
 namespace {
 
@@ -50,34 +51,6 @@ constexpr int GEMV_KEEP = 64;  // results a warp may hold back before its first 
 constexpr int GEMV_RED_OFFSET = (GEMV_WARPS * GEMV_MAX_STAGES + 1) * 8;  // 4 floats of block-reduction space behind the barriers
 constexpr int GEMV_KEEP_OFFSET = (GEMV_RED_OFFSET + 16 + 15) & ~15;      // GEMV_WARPS * GEMV_KEEP floats of held-back results
 constexpr int GEMV_BAR_BYTES = (GEMV_KEEP_OFFSET + GEMV_WARPS * GEMV_KEEP * 4 + 127) & ~127;  // all of the above, padded
-
-// One 36-byte block pair held as nine aligned words t[0..8] ({d0 | qs0[0:2]}, qs0[2:14],
-// {qs0[14:16] | d1}, qs1[0:16]) against the 64 int8 activations y[0..15] of the same two blocks.
-// ds = {dx0, bits(-8 * sum y0), dx1, bits(-8 * sum y1)}.  High nibbles are used in place
-// (16 * q as an unsigned byte): their dot product is an exact multiple of 16.
-__device__ __forceinline__ void pair_isums(const uint32_t* t, const int* y, const float4 ds, int& i0, int& i1) {
-    int lo0 = 0, hi0 = 0, lo1 = 0, hi1 = 0;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint32_t q0 = __funnelshift_r(t[i], t[i + 1], 16);
-        const uint32_t q1 = t[5 + i];
-        lo0 = dp4a_us(q0 & 0x0F0F0F0Fu, y[i], lo0);
-        hi0 = dp4a_us(q0 & 0xF0F0F0F0u, y[4 + i], hi0);
-        lo1 = dp4a_us(q1 & 0x0F0F0F0Fu, y[8 + i], lo1);
-        hi1 = dp4a_us(q1 & 0xF0F0F0F0u, y[12 + i], hi1);
-    }
-    i0 = lo0 + (hi0 >> 4) + __float_as_int(ds.y);
-    i1 = lo1 + (hi1 >> 4) + __float_as_int(ds.w);
-}
-__device__ __forceinline__ float pair_dot(const uint32_t* t, const int* y, const float4 ds, float acc) {
-    int i0, i1;
-    pair_isums(t, y, ds, i0, i1);
-    const float dw0 = __half2float(__ushort_as_half((unsigned short)(t[0] & 0xffffu)));
-    const float dw1 = __half2float(__ushort_as_half((unsigned short)(t[4] >> 16)));
-    acc = fmaf(dw0 * ds.x, (float)i0, acc);
-    acc = fmaf(dw1 * ds.z, (float)i1, acc);
-    return acc;
-}
 
 // Test hook: the integer sums of pair_isums for block pairs of one weight row against one
 // activation row given as 34-byte Q8_0 blocks (thread = block pair; w 4-byte aligned).
@@ -103,43 +76,6 @@ __global__ void gemv_pair_isums_kernel(const uint8_t* __restrict__ w, const uint
     pair_isums(t, y, make_float4(0.f, __int_as_float(-8 * s[0]), 0.f, __int_as_float(-8 * s[1])), i0, i1);
     out[2 * p] = i0;
     out[2 * p + 1] = i1;
-}
-
-// Loads the 36 * SEG bytes of one lane segment into 9 * SEG words with the widest aligned load.
-template <int SEG>
-__device__ __forceinline__ void load_segment(const uint8_t* p, uint32_t* t) {
-    if (SEG == 4) {
-#pragma unroll
-        for (int i = 0; i < 9; i++) {
-            const uint4 v = reinterpret_cast<const uint4*>(p)[i];
-            t[4 * i] = v.x, t[4 * i + 1] = v.y, t[4 * i + 2] = v.z, t[4 * i + 3] = v.w;
-        }
-    } else if (SEG == 2) {
-#pragma unroll
-        for (int i = 0; i < 9; i++) {
-            const uint2 v = reinterpret_cast<const uint2*>(p)[i];
-            t[2 * i] = v.x, t[2 * i + 1] = v.y;
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 9; i++) t[i] = reinterpret_cast<const uint32_t*>(p)[i];
-    }
-}
-
-// Shared-memory activation layout ("piece-major"): a row of K quants is cut into segments of
-// SEG block pairs (64 * SEG bytes = 4 * SEG pieces of 16 bytes); piece j of segment s lives at
-// j * (nsegk * 16) + s * 16, so the lanes of a warp (lane = segment) read consecutive 16-byte
-// words.  The {d, -8 * sum} pairs of the segment's 2 * SEG blocks (SEG pieces) use the same
-// scheme.
-template <int SEG>
-__device__ __forceinline__ void load_act(const uint8_t* qs, const uint8_t* ds, int nsegk, int s, int* y, float4* d4) {
-#pragma unroll
-    for (int j = 0; j < 4 * SEG; j++) {
-        const int4 v = *reinterpret_cast<const int4*>(qs + (j * nsegk + s) * 16);
-        y[4 * j] = v.x, y[4 * j + 1] = v.y, y[4 * j + 2] = v.z, y[4 * j + 3] = v.w;
-    }
-#pragma unroll
-    for (int j = 0; j < SEG; j++) d4[j] = *reinterpret_cast<const float4*>(ds + (j * nsegk + s) * 16);
 }
 
 // Cluster-cooperative Q8_0 quantiser.  The NB * K/32 blocks are split evenly over the CTAs of the
@@ -579,6 +515,14 @@ int gb_gemv_init(galois_b200_ctx* ctx) {
 
 bool gb_gemv_has_prologue() { return GEMV_THREADS == 128; }
 
+bool gb_gemv_row_plan(const galois_b200_ctx* ctx, int64_t K, int* seg, int* split, int* npass) {
+    if (K % 256 != 0 || K < 256 || K > 65536) return false;
+    const gemv_plan p = plan_gemv(ctx, K, 1 << 20, 1);
+    if (!p.ok) return false;
+    *seg = p.seg, *split = p.split ? 1 : 0, *npass = p.npass;
+    return true;
+}
+
 int gb_gemv_block_isums(galois_b200_ctx* ctx, const void* w, const void* xq, int64_t nb, int32_t* out) {
     if (nb % 2 != 0 || (uintptr_t)w % 4 != 0) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "block_isums: the GEMV path takes block pairs from a 4-byte aligned row");
     gemv_pair_isums_kernel<<<(unsigned)((nb / 2 + 127) / 128), 128, 0, ctx->stream>>>((const uint8_t*)w, (const uint8_t*)xq, nb / 2, out);
@@ -626,7 +570,19 @@ int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* w
     } else {
         gb_hazard_reset(ctx);
     }
-    const gemv_plan p = plan_gemv(ctx, K, N, B, sync_mode == GEMV_SYNC_DEFERRED);
+    gemv_plan p = plan_gemv(ctx, K, N, B, sync_mode == GEMV_SYNC_DEFERRED);
+    if (p.ok && sync_mode == GEMV_SYNC_DEFERRED) {
+        // A deferred launch holds its results back until the kernels in front of it have completed; a warp
+        // with more rows than its hold-back area would stall at its first flush and the launches would run
+        // one after the other on half the CTAs.  Such long kernels gain nothing from overlapping anyway:
+        // they take the ordinary geometry and wait at entry (their input is independent: no barrier needed).
+        const int64_t nsegk = (K / 64) / p.seg, rpc = p.split ? 32 / nsegk : 1;
+        const int64_t nchunks = (N + rpc - 1) / rpc, warps = (int64_t)p.grid * GEMV_WARPS;
+        if ((nchunks + warps - 1) / warps * rpc > GEMV_KEEP) {
+            sync_mode = GEMV_SYNC_ENTRY;
+            p = plan_gemv(ctx, K, N, B, false);
+        }
+    }
     if (!p.ok) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "mul_mat_q4_0: shape not supported by the streaming GEMV");
 #define X(NB_, SEG_, SPLIT_, NP_)                                                   \
     if (p.nbt == NB_ && p.seg == SEG_ && p.split == SPLIT_ && p.npass == NP_)       \

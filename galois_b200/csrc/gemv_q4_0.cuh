@@ -34,3 +34,7 @@ bool gb_gemv_has_prologue();
 // Test hook: per-block integer sums as the GEMV's dp4a sequence forms them (nb even, w 4-byte aligned;
 // xq in the 34-byte Q8_0 format).
 int gb_gemv_block_isums(galois_b200_ctx* ctx, const void* w, const void* xq, int64_t nb, int32_t* out);
+// How the one-row GEMV deals the K / 32 blocks of a weight row to the lanes of a warp (segment of `seg`
+// block pairs per lane, `split`: several rows per pass, `npass` passes with the activations hoisted into
+// registers; npass == 0: not hoisted).  False when the GEMV does not take rows of K elements at all.
+bool gb_gemv_row_plan(const galois_b200_ctx* ctx, int64_t K, int* seg, int* split, int* npass);

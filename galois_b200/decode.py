@@ -168,3 +168,47 @@ class DecodeLayer:
         kv = 2 * s.heads * s.ctx * s.head_dim * 2
         act = 4 * (12 * s.hidden + 3 * s.ffn + 2 * s.heads * s.ctx)
         return wb + kv + act
+
+
+class DecodeStack:
+    """Consecutive decoder layers stepped by ONE persistent kernel (``galois_b200_decode_layers_f32``):
+    the 22-op sequence of ``DecodeLayer.step`` for every layer of the stack, bit-identical to calling
+    ``step`` layer after layer, without a kernel boundary between ops or layers.  Takes op-by-op
+    ``DecodeLayer`` objects (``fused=False``) and uses their weights and caches in place."""
+
+    def __init__(self, layers):
+        import ctypes as C
+
+        from ._lib import GaloisDecodeLayer, GaloisDecodeShape, lib
+        from .tensor import _check
+
+        if not layers or any(L.fused for L in layers):
+            raise ValueError("DecodeStack takes one or more op-by-op DecodeLayer objects")
+        self.layers, self.dev, s = list(layers), layers[0].dev, layers[0].shape
+        self.shape = s
+        self.c_shape = GaloisDecodeShape(s.hidden, s.heads, s.head_dim, s.ffn, s.ctx, s.eps, s.rope_theta, 1.0)
+        self.c_layers = (GaloisDecodeLayer * len(layers))()
+        for i, L in enumerate(self.layers):
+            d = self.c_layers[i]
+            d.wq, d.wk, d.wv, d.wo = (L.w[n].data_ptr() for n in ("wq", "wk", "wv", "wo"))
+            d.w_gate, d.w_up, d.w_down = (L.w[n].data_ptr() for n in ("w_gate", "w_up", "w_down"))
+            d.attn_norm, d.ffn_norm = L.attn_norm.data_ptr(), L.ffn_norm.data_ptr()
+            d.k_cache, d.v_cache = L.k_cache.data_ptr(), L.v_cache.data_ptr()
+        need = C.c_size_t()
+        _check(self.dev.ctx, lib.galois_b200_decode_workspace_bytes(self.dev.ctx, C.byref(self.c_shape), C.byref(need)), "decode_workspace_bytes")
+        self.ws_bytes = need.value
+        self.ws = Tensor.zeros((need.value // 4,), GGmlType.F32, Device.Gpu(self.dev))
+        self.out = Tensor.zeros((s.hidden, 1), GGmlType.F32, Device.Gpu(self.dev))
+
+    def step(self, x: Tensor, pos: Tensor) -> Tensor:
+        """x: f32 {hidden, 1}; pos: i32 {1} on the device (the cache row / column to fill)."""
+        import ctypes as C
+
+        from ._lib import lib
+        from .tensor import _check
+
+        rc = lib.galois_b200_decode_layers_f32(self.dev.ctx, C.byref(self.c_shape), self.c_layers, len(self.layers), C.c_void_p(x.data_ptr()),
+                                               C.c_void_p(pos.data_ptr()), C.c_void_p(self.out.data_ptr()), C.c_void_p(self.ws.data_ptr()),
+                                               self.ws_bytes)
+        _check(self.dev.ctx, rc, "galois_b200_decode_layers_f32")
+        return self.out

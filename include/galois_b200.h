@@ -323,6 +323,44 @@ int galois_b200_cpy_f32_f16_pair(galois_b200_ctx* ctx, const float* x0, const ga
 int galois_b200_get_rows_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const int32_t* idx,
                                   const galois_dim* id, float* dst, const galois_dim* dd);
 
+/* ---- one decode step of a stack of decoder layers, one kernel ---------- */
+
+/* No counterpart in the reference, which has no model code: a caller builds a LLaMA-shaped decoder layer
+ * from 22 galois_* calls (src/op.rs:3034-3341): rms_norm, mul, matmul x 3, rope_custom x 2, cpy x 2 (the
+ * f16 KV-cache append), matmul (F16 K cache), scale + causal mask + soft_max, matmul (F16 V cache), matmul,
+ * add, rms_norm, mul, matmul x 2, unary(Silu), mul, matmul, add.  This entry point runs that sequence for
+ * one token and up to 32 consecutive layers as ONE persistent cooperative kernel (one CTA per SM, bounded
+ * grid barriers in place of kernel boundaries, the next op's weights requested before each barrier).  Every
+ * value is formed exactly as the one-op entry points above form it, so `out` and both caches are
+ * bit-identical to the 22-call sequence.
+ *   weights      Q4_0, dense rows: wq, wk, wv, wo {hidden, hidden}; w_gate, w_up {hidden, ffn}; w_down {ffn, hidden}
+ *   attn_norm,
+ *   ffn_norm     f32 [hidden] gains applied after the two rms_norms
+ *   k_cache      f16 [heads][ctx][head_dim]; row `pos` of every head is written
+ *   v_cache      f16 [heads][head_dim][ctx]; column `pos` of every head is written
+ *   x, out       f32 [hidden] (out may not alias x); pos: one i32 on the device, 0 <= pos < ctx (anything else:
+ *                nothing is written and the next synchronising call returns GALOIS_B200_E_BADARG)
+ *   workspace    galois_b200_decode_workspace_bytes(shape) bytes, 16-byte aligned, contents irrelevant
+ * Shapes this kernel holds: head_dim 128, hidden = 256 * 2^m <= 8192, ffn a multiple of 256 whose rows the
+ * one-row mat-vec deals either like hidden's or in three passes of 72-byte lane segments (11008 does),
+ * ctx a multiple of 256 in [256, 3072]; others return GALOIS_B200_E_UNSUPPORTED (use the one-op calls).
+ * Every pointer must be 16-byte aligned.  One such kernel runs at a time per device. */
+#define GALOIS_B200_DECODE_MAX_LAYERS 32
+typedef struct galois_b200_decode_layer {
+    const void *wq, *wk, *wv, *wo, *w_gate, *w_up, *w_down;
+    const float *attn_norm, *ffn_norm;
+    void *k_cache, *v_cache;
+} galois_b200_decode_layer;
+typedef struct galois_b200_decode_shape {
+    int32_t hidden, heads, head_dim, ffn, ctx;
+    float eps;             /* rms_norm */
+    float rope_freq_base;  /* RopeCustomOption.freq_base, n_dims = head_dim, mode 0 (src/op.rs:3294-3302) */
+    float rope_freq_scale;
+} galois_b200_decode_shape;
+int galois_b200_decode_workspace_bytes(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, size_t* out_bytes);
+int galois_b200_decode_layers_f32(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, const galois_b200_decode_layer* layers_host,
+                                  int n_layers, const float* x, const int32_t* pos, float* out, void* workspace, size_t workspace_bytes);
+
 /* ---- row sharding across GPUs ------------------------------------------ */
 
 /* Row range [*row0, *row0 + *nrows) of an N-row weight owned by `rank` of

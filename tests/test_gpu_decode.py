@@ -203,3 +203,65 @@ def test_layer_ops_teacher_forced(dev, oracle, position):
     assert_close(gu.to_numpy(), np.concatenate([t["g"], t["u"]], axis=1))
     galois_matmul_fused(W["w_down"], up(t["g"]), o, silu_mul=up(t["u"]), res=up(t["x2"]))
     assert_close(o.to_numpy(), t["out"])
+
+
+@pytest.mark.parametrize("hidden,heads,ffn,ctx,position,nlayers", [(512, 4, 1024, 256, 17, 1), (512, 4, 1024, 256, 255, 3),
+                                                                   (4096, 32, 11008, 2048, 2047, 1), (4096, 32, 11008, 2048, 100, 2),
+                                                                   (1024, 8, 2048, 512, 0, 2)])
+def test_persistent_kernel_equals_op_by_op_layers(dev, oracle, hidden, heads, ffn, ctx, position, nlayers):
+    """galois_b200_decode_layers_f32 (one persistent cooperative kernel for the whole stack) gives the bits
+    of the 22-op layer run layer after layer: the output row and both caches of every layer."""
+    import galois_b200 as gb
+    from galois_b200.decode import DecodeLayer, DecodeStack, LayerShape
+
+    O = oracle
+    s = LayerShape(hidden=hidden, heads=heads, head_dim=hidden // heads, ffn=ffn, ctx=ctx)
+    G = gb.Device.Gpu(dev)
+    ref_layers, pk_layers = [], []
+    for l in range(nlayers):
+        wq4, attn_norm, ffn_norm, k_cache, v_cache, x = make_layer_inputs(O, s, 4800 + 200 * l)
+        kc, vc = k_cache.view(np.float16), v_cache.view(np.float16)
+        ref_layers.append(DecodeLayer(dev, s, wq4, attn_norm, ffn_norm, kc, vc))
+        pk_layers.append(DecodeLayer(dev, s, wq4, attn_norm, ffn_norm, kc, vc))
+    xt = gb.Tensor.from_numpy(x, gb.GGmlType.F32, G)
+    pt = gb.Tensor.from_numpy(np.array([position], np.int32), gb.GGmlType.I32, G)
+    h = xt
+    for L in ref_layers:
+        # step() returns the layer's own output buffer: copy it before the next layer reads it as its input
+        h = gb.Tensor.from_numpy(L.step(h, pt, position).to_numpy(), gb.GGmlType.F32, G)
+    want = h.to_numpy()
+    stack = DecodeStack(pk_layers)
+    l0 = dev.launch_count()
+    for _ in range(2):  # twice: the second launch finds the barrier words as the first one left them
+        got = stack.step(xt, pt).to_numpy()
+    assert dev.launch_count() - l0 == 2
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    for a, b in zip(ref_layers, pk_layers):
+        assert np.array_equal(a.k_cache.to_numpy().view(np.uint16), b.k_cache.to_numpy().view(np.uint16))
+        assert np.array_equal(a.v_cache.to_numpy().view(np.uint16), b.v_cache.to_numpy().view(np.uint16))
+
+
+def test_persistent_kernel_rejects_what_it_does_not_hold(dev, oracle):
+    import ctypes as C
+
+    import galois_b200 as gb
+    from galois_b200._lib import GaloisDecodeShape
+
+    need = C.c_size_t()
+    for shape in (GaloisDecodeShape(4096, 64, 64, 11008, 2048, 1e-6, 10000.0, 1.0),    # head_dim 64
+                  GaloisDecodeShape(5120, 40, 128, 13824, 2048, 1e-6, 10000.0, 1.0),   # hidden not 256 * 2^m
+                  GaloisDecodeShape(4096, 32, 128, 11008, 4096, 1e-6, 10000.0, 1.0)):  # ctx beyond a ring slot
+        assert gb.lib.galois_b200_decode_workspace_bytes(dev.ctx, C.byref(shape), C.byref(need)) == -6
+    # a position outside the cache: nothing runs, the next synchronising call says so
+    from galois_b200.decode import DecodeLayer, DecodeStack, LayerShape
+
+    s = LayerShape(hidden=512, heads=4, head_dim=128, ffn=1024, ctx=256)
+    wq4, attn_norm, ffn_norm, k_cache, v_cache, x = make_layer_inputs(oracle, s, 4900)
+    L = DecodeLayer(dev, s, wq4, attn_norm, ffn_norm, k_cache.view(np.float16), v_cache.view(np.float16))
+    G = gb.Device.Gpu(dev)
+    stack = DecodeStack([L])
+    stack.step(gb.Tensor.from_numpy(x, gb.GGmlType.F32, G), gb.Tensor.from_numpy(np.array([256], np.int32), gb.GGmlType.I32, G))
+    with pytest.raises(gb.GError) as e:
+        dev.synchronize()
+    assert e.value.code == -1
+    assert np.array_equal(L.k_cache.to_numpy().view(np.uint16), k_cache)
