@@ -28,6 +28,18 @@ __device__ __forceinline__ uint32_t mbar_test(uint64_t* bar, uint32_t parity, ui
         : "memory");
     return ok;
 }
+// True when the phase with the given parity has completed (one non-blocking test).
+__device__ __forceinline__ bool mbar_done(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Waits for the phase with the given parity; gives up after about two seconds of SM clocks
 // and returns false (the caller records a timeout status and stops; nothing spins forever).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t hint_ns = 20000u) {
