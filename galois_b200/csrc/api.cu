@@ -139,6 +139,11 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
     ctx->ordinal = ordinal;
     ctx->stream = (cudaStream_t)cu_stream;
     ctx->sm_count = prop.multiProcessorCount;
+    ctx->packs = (gb_weight_pack*)calloc(GB_MAX_PACKS, sizeof(gb_weight_pack));
+    if (!ctx->packs) {
+        free(ctx);
+        return gb_fail(nullptr, GALOIS_B200_E_NOMEM, "init: out of host memory");
+    }
     ctx->pdl = 1;
     ctx->hazard_tracking = 1;
     ctx->hazard_unknown = 1;
@@ -165,6 +170,7 @@ extern "C" int galois_b200_init(int ordinal, void* cu_stream, galois_b200_ctx** 
     // kept in device memory (128 KB each; they stay L2-resident).
     uint16_t* tab = (uint16_t*)malloc(2 * 65536 * sizeof(uint16_t));
     if (!tab) {
+        free(ctx->packs);
         free(ctx);
         return gb_fail(nullptr, GALOIS_B200_E_NOMEM, "init: out of host memory");
     }
@@ -212,6 +218,10 @@ extern "C" int galois_b200_destroy(galois_b200_ctx* ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->io) cudaFree(ctx->io);
     if (ctx->tmp) cudaFree(ctx->tmp);
+    if (ctx->packs) {
+        gb_mm_tc_release_all(ctx);
+        free(ctx->packs);
+    }
     if (ctx->prof_ev) {
         for (int i = 0; i < 2 * GB_PROF_MAX; i++)
             if (ctx->prof_ev[i]) cudaEventDestroy(ctx->prof_ev[i]);
@@ -406,7 +416,7 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
     const bool prof = ctx->profiling && ctx->prof_n < GB_PROF_MAX;
     if (prof) GB_CUDA(ctx, cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream));
     if (variant == 3)
-        rc = gb_mm_q4_0_tc(ctx, w, wd, x, xd, dst, dd, scratch);
+        rc = gb_mm_tc_prepared(ctx, w, wd) ? gb_mm_q4_0_tp(ctx, w, wd, x, xd, dst, dd, scratch) : gb_mm_q4_0_tc(ctx, w, wd, x, xd, dst, dd, scratch);
     else if (variant == 4)
         rc = gb_mmq_skinny(ctx, w, wd, x, xd, dst, dd, scratch);
     else if (gemv)
@@ -524,6 +534,17 @@ extern "C" int galois_b200_mul_mat_q4_0_f32_add(galois_b200_ctx* ctx, const void
     GB_CHECK_CTX(ctx);
     if (!res || !rd) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_add: null pointer");
     return galois_b200_mul_mat_q4_0_f32_fused(ctx, w, wd, x, xd, nullptr, res, rd, dst, dd);
+}
+
+extern "C" int galois_b200_prepare_weight_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd) {
+    GB_CHECK_CTX(ctx);
+    if (!w || !wd) return gb_fail(ctx, GALOIS_B200_E_BADARG, "prepare_weight_q4_0: null pointer");
+    return gb_mm_tc_prepare(ctx, w, wd);
+}
+
+extern "C" int galois_b200_release_weight(galois_b200_ctx* ctx, const void* w) {
+    GB_CHECK_CTX(ctx);
+    return gb_mm_tc_release(ctx, w);
 }
 
 extern "C" int galois_b200_set_pdl(galois_b200_ctx* ctx, int on) {

@@ -15,6 +15,15 @@
 #define GB_PROF_MAX 4096
 #define GB_HAZARD_MAX 16
 
+// A weight prepared for the tensor-core GEMM (see mul_mat_q4_0_tc.cuh).
+#define GB_MAX_PACKS 1024
+struct gb_weight_pack {
+    const void* w;   // the caller's Q4_0 tensor this is a copy of (the key)
+    int64_t K, N;
+    void* pa;        // nibbles as unsigned bytes, UMMA operand order
+    void* pd;        // f32 block scales
+};
+
 // Context behind the opaque galois_b200_ctx handle.
 struct galois_b200_ctx {
     int ordinal;
@@ -51,6 +60,8 @@ struct galois_b200_ctx {
     // intermediate of a fused call that runs as separate ops
     void* tmp;
     size_t tmp_bytes;
+    gb_weight_pack* packs;  // GB_MAX_PACKS entries
+    int npacks;
     char err[512];
 };
 

@@ -344,11 +344,13 @@ int launch_tc(galois_b200_ctx* ctx, const uint8_t* w, const uint8_t* qs, const u
 
 }  // namespace
 
+static int gb_mm_tp_init(galois_b200_ctx* ctx);
+
 int gb_mm_tc_init(galois_b200_ctx* ctx) {
     GB_CUDA(ctx, cudaFuncSetAttribute(mm_q4_0_tc_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem<64>::TOTAL));
     GB_CUDA(ctx, cudaFuncSetAttribute(mm_q4_0_tc_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem<128>::TOTAL));
     GB_CUDA(ctx, cudaFuncSetAttribute(mm_q4_0_tc_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem<64>::TOTAL));
-    return 0;
+    return gb_mm_tp_init(ctx);
 }
 
 bool gb_mm_tc_supported(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd,
@@ -400,5 +402,375 @@ int gb_mm_q4_0_tc_block_isums(galois_b200_ctx* ctx, const void* w, const galois_
     mm_q4_0_tc_kernel<BN, true><<<dim3(1, 1), TC_THREADS, tc_smem<BN>::TOTAL, ctx->stream>>>((const uint8_t*)w, qs, xs, dst, dd->nb[1], K, N, B,
                                                                                        ctx->dev_status, out);
     GB_LAUNCHED(ctx, "mm_q4_0_tc (block sums)");
+    return 0;
+}
+
+// ====================================================================================================
+// The same GEMM on weights repacked once at upload (galois_b200_prepare_weight_q4_0): the nibbles of every
+// 128-row tile are stored as unsigned bytes already in the canonical K-major UMMA layout, block after
+// block, with the f32 block scales beside them, so a K step of the A operand is ONE bulk copy and the four
+// unpack warps of the kernel above are gone.  What else changes:
+//   * four (BN = 128) or eight (BN = 64) int32 accumulator tiles live in TMEM, so the MMA issuer runs up to
+//     that many blocks ahead of the epilogue and neither side waits for the other's hand-shake;
+//   * an epilogue warp reads both 32-column halves of its 64 columns before it hands the buffer back and
+//     does its scale-accumulate arithmetic two columns at a time (add / mul / fma .f32x2).
+// Numerics are unchanged: one exact int32 tile per 32-element block, (d_w * d_x) exact in f32, one rounding
+// per fused multiply-add.
+namespace {
+
+constexpr int TP_EPI_WARPS = 8;
+constexpr int TP_THREADS = (TP_EPI_WARPS + 2) * 32;  // + MMA issuer + loader
+constexpr int TP_STAGES = 2;
+
+template <int BN>
+struct tp_smem {
+    static constexpr uint32_t A_BLOCK = TC_M * 32, B_BLOCK = BN * 32;
+    static constexpr uint32_t A_BYTES = TC_KC * A_BLOCK, B_BYTES = TC_KC * B_BLOCK;
+    static constexpr uint32_t DW_BYTES = TC_KC * TC_M * 4, XS_BYTES = TC_KC * BN * 8;
+    static constexpr uint32_t STAGE = A_BYTES + B_BYTES + DW_BYTES + XS_BYTES;
+    static constexpr uint32_t BAR_OFF = TP_STAGES * STAGE;
+    static constexpr uint32_t TOTAL = BAR_OFF + 256;
+    static constexpr int NBUF = 512 / BN > 4 ? 4 : 512 / BN;  // TMEM accumulator tiles
+};
+
+// Repack: thread = (weight row, block).  Layout of the result, per 128-row tile t and block kb:
+//   pa[((t * nkb + kb) * 2 + chunk) * 2048 + row_in_tile * 16 + i]  = nibble i (chunk 0: low nibbles = elements
+//        0..15, chunk 1: high nibbles = elements 16..31) of the block, as an unsigned byte
+//   pd[(t * nkb + kb) * 128 + row_in_tile]                          = f32(d)
+// Rows beyond N (ragged last tile) are zero.
+__global__ void __launch_bounds__(256) repack_q4_0_tc_kernel(const uint8_t* __restrict__ w, int64_t row_blocks, uint8_t* __restrict__ pa,
+                                                             float* __restrict__ pd, int nkb, int N, int ntiles) {
+    const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int64_t total = (int64_t)ntiles * TC_M * nkb;
+    if (idx >= total) return;
+    const int kb = (int)(idx % nkb);
+    const int64_t row = idx / nkb;
+    const int t = (int)(row / TC_M), r = (int)(row % TC_M);
+    uint32_t lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};
+    float d = 0.0f;
+    if (row < N) {
+        const uint16_t* p = reinterpret_cast<const uint16_t*>(w + (row * row_blocks + kb) * GB_Q4_BYTES);
+        d = __half2float(__ushort_as_half(p[0]));
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t q = (uint32_t)p[1 + 2 * i] | ((uint32_t)p[2 + 2 * i] << 16);
+            lo[i] = q & 0x0F0F0F0Fu;
+            hi[i] = (q >> 4) & 0x0F0F0F0Fu;
+        }
+    }
+    uint8_t* base = pa + ((size_t)t * nkb + kb) * (2 * 2048) + (size_t)r * 16;
+    *reinterpret_cast<uint4*>(base) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    *reinterpret_cast<uint4*>(base + 2048) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    pd[((size_t)t * nkb + kb) * TC_M + r] = d;
+}
+
+// The activation quantiser of the kernel above with the block constants of two neighbouring columns side by
+// side: xs[col tile][block][BN / 2] {f32 d0, f32 d1, i32 MAGIC - 8 sum0, i32 MAGIC - 8 sum1}.
+__global__ void __launch_bounds__(256) quantize_q8_tp_kernel(const float* __restrict__ x, int64_t x_stride, int K, int B, int BN,
+                                                             uint8_t* __restrict__ qs, int* __restrict__ xs) {
+    const int nkb = K >> 5;
+    const int sub = threadIdx.x & 7;
+    const int kb = (blockIdx.x * 256 + threadIdx.x) >> 3;
+    const int col = blockIdx.y;  // padded column
+    const bool live = kb < nkb;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live && col < B) v = __ldg(reinterpret_cast<const float4*>(x + (size_t)col * x_stride + kb * 32) + sub);
+    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = (d != 0.0f) ? __fdiv_rn(1.0f, d) : 0.0f;
+    const int q0 = max(-128, min(127, (int)roundf(__fmul_rn(v.x, id))));
+    const int q1 = max(-128, min(127, (int)roundf(__fmul_rn(v.y, id))));
+    const int q2 = max(-128, min(127, (int)roundf(__fmul_rn(v.z, id))));
+    const int q3 = max(-128, min(127, (int)roundf(__fmul_rn(v.w, id))));
+    int s = q0 + q1 + q2 + q3;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (live) {
+        const int tile = col / BN, ci = col % BN;
+        const uint32_t packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+        const size_t blk_base = ((size_t)tile * nkb + kb) * (size_t)(BN * 32);
+        const size_t off = blk_base + (size_t)(sub >> 2) * (BN * 16) + (size_t)(ci >> 3) * 128 + (ci & 7) * 16 + (sub & 3) * 4;
+        *reinterpret_cast<uint32_t*>(qs + off) = packed;
+        if (sub == 0) {
+            int* p = xs + (((size_t)tile * nkb + kb) * (BN / 2) + (ci >> 1)) * 4 + (ci & 1);
+            p[0] = __float_as_int(__half2float(__float2half_rn(d)));
+            p[2] = (int)TC_MAGIC - 8 * s;
+        }
+    }
+}
+
+// Two f32 in one 64-bit register (low word first).
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    return (uint64_t)__float_as_uint(lo) | ((uint64_t)__float_as_uint(hi) << 32);
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(TP_THREADS, 1)
+    mm_q4_0_tp_kernel(const uint8_t* __restrict__ pa, const float* __restrict__ pd, const uint8_t* __restrict__ qs, const uint8_t* __restrict__ xs,
+                      float* __restrict__ dst, int64_t nb1, int K, int N, int B, int* __restrict__ status) {
+    using L = tp_smem<BN>;
+    constexpr int NBUF = L::NBUF;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nkb = K >> 5, nsteps = nkb / TC_KC;
+    const int row_tile = blockIdx.x, col_tile = blockIdx.y;
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+    uint64_t* full = bars;                           // [TP_STAGES] loader: bytes of a K step have landed
+    uint64_t* stage_empty = bars + TP_STAGES;        // [TP_STAGES] 8 epilogue warps are done with its scales
+    uint64_t* tmem_full = bars + 2 * TP_STAGES;      // [NBUF] MMA commit
+    uint64_t* tmem_empty = bars + 2 * TP_STAGES + NBUF;  // [NBUF] 8 epilogue warps
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * TP_STAGES + 2 * NBUF);
+    constexpr uint32_t TMEM_COLS = NBUF * BN;  // 512
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TP_STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&stage_empty[s], TP_EPI_WARPS);
+        }
+        for (int b = 0; b < NBUF; b++) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], TP_EPI_WARPS);
+        }
+        fence_proxy_async();
+    }
+    if (warp == TP_EPI_WARPS) {
+        tmem_alloc(tmem_base_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+    bool ok = true;
+
+    if (warp < TP_EPI_WARPS) {
+        // ------------------------------------------------------------ epilogue
+        const int lane_grp = warp & 3, half = warp >> 2;
+        const int row_in_tile = lane_grp * 32 + lane;
+        constexpr int NC = BN / 2;   // columns of this warp
+        constexpr int NP = NC / 2;   // column pairs
+        uint64_t acc[NP];
+#pragma unroll
+        for (int c = 0; c < NP; c++) acc[c] = 0ull;  // two +0.0f
+        const uint64_t neg_magic = f2_pack(-12582912.0f, -12582912.0f);
+        for (int g = 0; g < nkb && ok; g++) {
+            const int buf = g % NBUF, step = g / TC_KC, kb = g % TC_KC, s = step % TP_STAGES;
+            if (kb == 0) {
+                // the scales of this K step are in shared memory once the step's bytes have landed
+                ok = mbar_wait_bounded(&full[s], (uint32_t)(step / TP_STAGES) & 1u);
+                if (!ok) break;
+            }
+            ok = mbar_wait_bounded(&tmem_full[buf], (uint32_t)(g / NBUF) & 1u);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t r[NC];
+#pragma unroll
+            for (int c0 = 0; c0 < NC; c0 += 32)
+                tmem_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(buf * BN + half * NC + c0), r + c0);
+            tmem_ld_wait();
+            // the tile is in registers: hand the buffer back to the MMA issuer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            const uint8_t* stage = smem + (uint32_t)s * L::STAGE;
+            const float dw = reinterpret_cast<const float*>(stage + L::A_BYTES + L::B_BYTES)[kb * TC_M + row_in_tile];
+            const uint64_t dw2 = f2_pack(dw, dw);
+            const int4* xsp = reinterpret_cast<const int4*>(stage + L::A_BYTES + L::B_BYTES + L::DW_BYTES) + kb * (BN / 2) + half * NP;
+#pragma unroll
+            for (int c = 0; c < NP; c++) {
+                const int4 sc = xsp[c];  // {d_x of two columns, MAGIC - 8 sum of two columns} (the same for all lanes)
+                // float(isum) through the 1.5 * 2^23 trick, exact for |isum| < 2^22
+                const uint64_t i2 = (uint64_t)(uint32_t)((int)r[2 * c] + sc.z) | ((uint64_t)(uint32_t)((int)r[2 * c + 1] + sc.w) << 32);
+                const uint64_t f2 = f2_add(i2, neg_magic);
+                const uint64_t dx2 = (uint64_t)(uint32_t)sc.x | ((uint64_t)(uint32_t)sc.y << 32);
+                // (d_w * d_x) is exact in f32 (two f16 values): the term of vec_dot_q8_0 with one rounding
+                acc[c] = f2_fma(f2_mul(dw2, dx2), f2, acc[c]);
+            }
+            if (kb == TC_KC - 1) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&stage_empty[s]);
+            }
+        }
+        if (ok) {
+            const int row = row_tile * TC_M + row_in_tile;
+            if (row < N) {
+#pragma unroll
+                for (int c = 0; c < NP; c++) {
+                    const int col = col_tile * BN + half * NC + 2 * c;
+                    if (col < B) dst[(size_t)col * nb1 + row] = __uint_as_float((uint32_t)acc[c]);
+                    if (col + 1 < B) dst[(size_t)(col + 1) * nb1 + row] = __uint_as_float((uint32_t)(acc[c] >> 32));
+                }
+            }
+        }
+    } else if (warp == TP_EPI_WARPS) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            // instruction descriptor: D = s32, A = unsigned 8 bit, B = signed 8 bit, both K-major
+            const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+            for (int step = 0; step < nsteps && ok; step++) {
+                const int s = step % TP_STAGES;
+                ok = mbar_wait_bounded(&full[s], (uint32_t)(step / TP_STAGES) & 1u);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + (uint32_t)s * L::STAGE);
+                const uint32_t b_addr = a_addr + L::A_BYTES;
+                for (int kb = 0; kb < TC_KC; kb++) {
+                    const int g = step * TC_KC + kb, buf = g % NBUF;
+                    ok = mbar_wait_bounded(&tmem_empty[buf], ((uint32_t)(g / NBUF) & 1u) ^ 1u);
+                    if (!ok) break;
+                    tc_fence_after();
+                    umma_i8(tmem_base + (uint32_t)(buf * BN), umma_desc(a_addr + kb * L::A_BLOCK, TC_M * 16, 128),
+                            umma_desc(b_addr + kb * L::B_BLOCK, BN * 16, 128), idesc, 0u);
+                    umma_commit(&tmem_full[buf]);
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ loader: four bulk copies per K step
+        if (lane == 0) {
+            const uint8_t* asrc = pa + (size_t)row_tile * nkb * L::A_BLOCK;
+            const uint8_t* dsrc = reinterpret_cast<const uint8_t*>(pd) + (size_t)row_tile * nkb * (TC_M * 4);
+            const uint8_t* qsrc = qs + (size_t)col_tile * nkb * L::B_BLOCK;
+            const uint8_t* xsrc = xs + (size_t)col_tile * nkb * (BN * 8);
+            for (int step = 0; step < nsteps && ok; step++) {
+                const int s = step % TP_STAGES;
+                // the stage is free when the MMAs that read it have completed (their tiles were read by the
+                // epilogue, which arrives here after the step's last block) 
+                ok = mbar_wait_bounded(&stage_empty[s], ((uint32_t)(step / TP_STAGES) & 1u) ^ 1u);
+                if (!ok) break;
+                uint8_t* stage = smem + (uint32_t)s * L::STAGE;
+                mbar_expect_tx(&full[s], L::STAGE);
+                bulk_g2s(stage, asrc + (size_t)step * L::A_BYTES, L::A_BYTES, &full[s]);
+                bulk_g2s(stage + L::A_BYTES, qsrc + (size_t)step * L::B_BYTES, L::B_BYTES, &full[s]);
+                bulk_g2s(stage + L::A_BYTES + L::B_BYTES, dsrc + (size_t)step * L::DW_BYTES, L::DW_BYTES, &full[s]);
+                bulk_g2s(stage + L::A_BYTES + L::B_BYTES + L::DW_BYTES, xsrc + (size_t)step * L::XS_BYTES, L::XS_BYTES, &full[s]);
+            }
+        }
+        __syncwarp();
+    }
+
+    if (!ok && lane == 0) atomicExch(status, GALOIS_B200_E_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == TP_EPI_WARPS) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+}  // namespace
+
+static gb_weight_pack* tp_find(galois_b200_ctx* ctx, const void* w) {
+    for (int i = 0; i < ctx->npacks; i++)
+        if (ctx->packs[i].w == w) return &ctx->packs[i];
+    return nullptr;
+}
+
+int gb_mm_tc_prepare(galois_b200_ctx* ctx, const void* w, const galois_dim* wd) {
+    const int64_t K = wd->ne[0], N = wd->ne[1];
+    if (K % 256 != 0 || K < 256 || K > (1 << 20) || N < 1 || N > (1 << 30) || wd->ne[2] != 1 || wd->ne[3] != 1 || wd->nb[0] != 1 ||
+        wd->nb[1] != K / GB_QK)
+        return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "prepare_weight_q4_0: needs a 2-D weight with dense rows and K %% 256 == 0");
+    if ((uintptr_t)w % 2 != 0) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "prepare_weight_q4_0: weight blocks must be 2-byte aligned");
+    gb_weight_pack* p = tp_find(ctx, w);
+    const int nkb = (int)(K / GB_QK), ntiles = (int)((N + TC_M - 1) / TC_M);
+    const size_t a_bytes = (size_t)ntiles * nkb * (TC_M * 32), d_bytes = (size_t)ntiles * nkb * TC_M * sizeof(float);
+    if (p != nullptr && (p->K != K || p->N != N)) {
+        // the address now holds a different weight: start over
+        int rc = gb_mm_tc_release(ctx, w);
+        if (rc) return rc;
+        p = nullptr;
+    }
+    if (p == nullptr) {
+        if (ctx->npacks == GB_MAX_PACKS) return gb_fail(ctx, GALOIS_B200_E_NOMEM, "prepare_weight_q4_0: %d weights are prepared already", GB_MAX_PACKS);
+        gb_weight_pack np = {};
+        np.w = w, np.K = K, np.N = N;
+        cudaError_t e = cudaMalloc(&np.pa, a_bytes);
+        if (e == cudaSuccess) e = cudaMalloc(&np.pd, d_bytes);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            if (np.pa) cudaFree(np.pa);
+            return gb_fail(ctx, GALOIS_B200_E_NOMEM, "prepare_weight_q4_0: cudaMalloc(%zu + %zu): %s", a_bytes, d_bytes, cudaGetErrorString(e));
+        }
+        ctx->packs[ctx->npacks] = np;
+        p = &ctx->packs[ctx->npacks++];
+    }
+    const int64_t total = (int64_t)ntiles * TC_M * nkb;
+    repack_q4_0_tc_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>((const uint8_t*)w, wd->nb[1], (uint8_t*)p->pa, (float*)p->pd, nkb,
+                                                                                 (int)N, ntiles);
+    GB_LAUNCHED(ctx, "repack_q4_0_tc");
+    return 0;
+}
+
+int gb_mm_tc_release(galois_b200_ctx* ctx, const void* w) {
+    for (int i = 0; i < ctx->npacks; i++) {
+        if (ctx->packs[i].w != w) continue;
+        GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // work already enqueued may still read the copy
+        cudaFree(ctx->packs[i].pa);
+        cudaFree(ctx->packs[i].pd);
+        ctx->packs[i] = ctx->packs[--ctx->npacks];
+        return 0;
+    }
+    return gb_fail(ctx, GALOIS_B200_E_BADARG, "release_weight: this weight was not prepared");
+}
+
+void gb_mm_tc_release_all(galois_b200_ctx* ctx) {
+    for (int i = 0; i < ctx->npacks; i++) {
+        cudaFree(ctx->packs[i].pa);
+        cudaFree(ctx->packs[i].pd);
+    }
+    ctx->npacks = 0;
+}
+
+bool gb_mm_tc_prepared(galois_b200_ctx* ctx, const void* w, const galois_dim* wd) {
+    const gb_weight_pack* p = tp_find(ctx, w);
+    return p != nullptr && p->K == wd->ne[0] && p->N == wd->ne[1];
+}
+
+template <int BN>
+static int launch_tp(galois_b200_ctx* ctx, const gb_weight_pack* p, const uint8_t* qs, const uint8_t* xs, float* dst, int64_t nb1, int K, int N, int B) {
+    dim3 grid((unsigned)((N + TC_M - 1) / TC_M), (unsigned)((B + BN - 1) / BN));
+    mm_q4_0_tp_kernel<BN><<<grid, TP_THREADS, tp_smem<BN>::TOTAL, ctx->stream>>>((const uint8_t*)p->pa, (const float*)p->pd, qs, xs, dst, nb1, K, N, B,
+                                                                                ctx->dev_status);
+    GB_LAUNCHED(ctx, "mm_q4_0_tp");
+    return 0;
+}
+
+// The GEMM on the prepared copy of w (two launches: quantiser, GEMM); scratch as for gb_mm_q4_0_tc.
+int gb_mm_q4_0_tp(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
+                  const galois_dim* dd, void* scratch) {
+    const gb_weight_pack* p = tp_find(ctx, w);
+    if (p == nullptr) return gb_fail(ctx, GALOIS_B200_E_STATE, "mul_mat_q4_0: weight not prepared");
+    const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
+    const int BN = pick_bn(B);
+    const int Bp = (B + BN - 1) / BN * BN;
+    uint8_t* qs = (uint8_t*)scratch;
+    uint8_t* xs = qs + (((size_t)Bp * K + 255) & ~(size_t)255);
+    dim3 qgrid((unsigned)((K / 32 * 8 + 255) / 256), (unsigned)Bp);
+    quantize_q8_tp_kernel<<<qgrid, 256, 0, ctx->stream>>>(x, xd->nb[1], K, B, BN, qs, (int*)xs);
+    GB_LAUNCHED(ctx, "quantize_q8_tp");
+    if (BN == 64) return launch_tp<64>(ctx, p, qs, xs, dst, dd->nb[1], K, N, B);
+    return launch_tp<128>(ctx, p, qs, xs, dst, dd->nb[1], K, N, B);
+}
+
+static int gb_mm_tp_init(galois_b200_ctx* ctx) {
+    GB_CUDA(ctx, cudaFuncSetAttribute(mm_q4_0_tp_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, tp_smem<64>::TOTAL));
+    GB_CUDA(ctx, cudaFuncSetAttribute(mm_q4_0_tp_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, tp_smem<128>::TOTAL));
     return 0;
 }

@@ -19,3 +19,14 @@ int gb_mm_q4_0_tc(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, con
 // every per-block integer sum it scales: out[(block * 128 + row) * 64 + column], int32.
 int gb_mm_q4_0_tc_block_isums(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
                               const galois_dim* dd, void* scratch, int32_t* out);
+
+// One-time repack of a weight for the tensor-core GEMM (the upload step, src/cuda.rs:231-239 of galois): a
+// copy of w with the nibbles as unsigned bytes in UMMA operand order and f32 block scales, kept in the
+// context under w's device address until released.  Calling it again for the same address refreshes the copy.
+int gb_mm_tc_prepare(galois_b200_ctx* ctx, const void* w, const galois_dim* wd);
+int gb_mm_tc_release(galois_b200_ctx* ctx, const void* w);
+void gb_mm_tc_release_all(galois_b200_ctx* ctx);
+bool gb_mm_tc_prepared(galois_b200_ctx* ctx, const void* w, const galois_dim* wd);
+// The GEMM on the prepared copy (quantiser + GEMM, two launches; same scratch as gb_mm_q4_0_tc).
+int gb_mm_q4_0_tp(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
+                  const galois_dim* dd, void* scratch);

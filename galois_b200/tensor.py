@@ -132,6 +132,13 @@ class CudaDevice:
         """Overlap of independent one-row mat-muls (galois_b200_set_overlap; default on)."""
         _check(self.ctx, lib.galois_b200_set_overlap(self.ctx, 1 if on else 0), "set_overlap")
 
+    def prepare_weight(self, w: "Tensor"):
+        """One-time repack of a Q4_0 weight for the large-batch mat-mul (galois_b200_prepare_weight_q4_0)."""
+        _check(self.ctx, lib.galois_b200_prepare_weight_q4_0(self.ctx, C.c_void_p(w.data_ptr()), C.byref(w.dim().c_struct())), "prepare_weight")
+
+    def release_weight(self, w: "Tensor"):
+        _check(self.ctx, lib.galois_b200_release_weight(self.ctx, C.c_void_p(w.data_ptr())), "release_weight")
+
     def overlap_counts(self):
         """(waited at entry, deferred wait, barrier) counts of one-row mat-vec launches so far."""
         out = (C.c_int64 * 3)()

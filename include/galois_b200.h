@@ -178,6 +178,20 @@ int galois_b200_mul_mat_q4_0_tc_block_isums(galois_b200_ctx* ctx, const void* w,
 int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
                                  const galois_dim* xd, float* dst, const galois_dim* dd);
 
+/* One-time repack of a Q4_0 weight at upload, for the large-batch (prefill) mat-mul.  In the reference the
+ * upload is a plain copy of the 18-byte blocks (CudaDevice::from_cpu_storage, src/cuda.rs:231-239) and its
+ * kernels re-decode them on every call.  This call keeps, inside the context and keyed by the device address
+ * `w`, a second copy of the weight with the nibbles already expanded to unsigned bytes in the tensor-core
+ * operand order and the block scales as f32 (1.125 bytes per weight on top of the caller's 0.5625).  The op
+ * API does not change: galois_b200_mul_mat_q4_0_f32 looks the address up and, when the batch is large
+ * enough for the tensor-core kernel, streams the prepared copy with bulk copies instead of unpacking nibbles
+ * in the kernel; results are bit-identical to the unprepared path.  The copy is made on the context's stream
+ * (asynchronous).  If the caller overwrites the weight in place it must call this again; it must call
+ * galois_b200_release_weight before freeing or reusing the address (galois_b200_destroy releases all).
+ * w: 2-D, dense rows, K % 256 == 0. */
+int galois_b200_prepare_weight_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd);
+int galois_b200_release_weight(galois_b200_ctx* ctx, const void* w);
+
 /* Up to four reference ops in one call (not part of the reference API; results are
  * bit-identical to running the ops one after the other):
  *   t   = prologue(x)   none | galois_rms_norm(x, eps) then galois_mul by the gain row `aux`

@@ -156,3 +156,36 @@ def test_reserve_scratch_keeps_later_calls_allocation_free(gb, dev, oracle):
     torch.cuda.synchronize()
     free1, _ = torch.cuda.mem_get_info()
     assert free1 == free0
+
+
+@pytest.mark.parametrize("n,k,b", [(128, 256, 64), (200, 768, 33), (77, 256, 130), (4096, 4096, 512), (300, 1024, 200), (11008, 4096, 256)])
+def test_prepared_weight_gives_the_bits_of_the_unprepared_path(gb, dev, oracle, n, k, b):
+    """galois_b200_prepare_weight_q4_0 (the one-time repack at upload) changes where the tensor-core kernel
+    takes its operands from, not a single result bit; and the op API is unchanged."""
+    G = gb.Device.Gpu(dev)
+    w = oracle.quantize_q4_0(oracle.fill_normal(n * k, 190 + n, 0, 0.02).reshape(n, k))
+    x = oracle.fill_normal(b * k, 191 + b).reshape(b, k)
+    wt = gb.Tensor.from_raw(w, (k, n), gb.GGmlType.Q4_0, G)
+    xt = gb.Tensor.from_numpy(x, gb.GGmlType.F32, G)
+    plain, prepared = gb.Tensor.zeros((n, b), gb.GGmlType.F32, G), gb.Tensor.zeros((n, b), gb.GGmlType.F32, G)
+    dev.set_mul_mat_variant(3)
+    try:
+        l0 = dev.launch_count()
+        gb.galois_matmul(wt, xt, plain)
+        dev.prepare_weight(wt)
+        dev.prepare_weight(wt)  # refreshing an existing copy is allowed
+        l1 = dev.launch_count()
+        gb.galois_matmul(wt, xt, prepared)
+        a, p = plain.to_numpy(), prepared.to_numpy()
+        dev.release_weight(wt)
+        gb.galois_matmul(wt, xt, prepared)  # back on the unprepared kernel
+        assert np.array_equal(prepared.to_numpy(), a)
+    finally:
+        dev.set_mul_mat_variant(0)
+    assert l1 - l0 == 4  # quantiser + GEMM, two repacks
+    assert np.array_equal(a.view(np.uint32), p.view(np.uint32))
+    from conftest import assert_close
+
+    assert_close(p, oracle.mul_mat_q4_0(w, x))
+    with pytest.raises(gb.GError):
+        dev.release_weight(wt)  # not prepared any more
