@@ -45,11 +45,11 @@ def ffn_shapes():
 
 # ----------------------------------------------------------------------------- synthetic data
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemv_q4_0_kernel launch at config 2, batch 1 (ncu capture,
-# mean of the gate/up and down instances: 25 423 872 and 25 453 312 bytes read, 0 written).  A citation of the
+# mean of the gate/up and down instances: 25 441 792 and 25 473 024 bytes read, 0 / 10 240 written).  A citation of the
 # capture summarised in profiles/gemv_q4_0_config2_batch1.md, not a live measurement: NCU_CAPTURE_OF names the
 # kernel revision it was taken on (the weight streaming of the kernel has not changed since).
-NCU_DRAM_BYTES_PER_LAUNCH = (2 * 25423872 + 25453312) / 3.0
-NCU_CAPTURE_OF = "gemv_q4_0_kernel as of commit c7c2a0d"
+NCU_DRAM_BYTES_PER_LAUNCH = (2 * 25441792 + 25473024) / 3.0
+NCU_CAPTURE_OF = "gemv_q4_0_kernel with the deferred wait, grid 144 x 128, captured on the revision that introduced the hazard window"
 
 
 def make_q4_0(n: int, k: int, seed: int, device):
@@ -776,6 +776,7 @@ def run_ours(args):
         import oracle as O
 
         O.build()
+        cpu_build_kind = O.use_native_build()  # -march=native on this host (README.md:33 of galois)
         csets = 2
         sets_host = [[w[0].cpu().numpy().reshape(shapes[i][1], -1) for i, w in enumerate(ws)] for ws in weights[:csets]]
         xs_host = {k: v.cpu().numpy() for k, v in xs.items()}
@@ -783,7 +784,9 @@ def run_ours(args):
         cbytes = csets * sum(algorithmic_bytes(n, k, B) for _, n, k in shapes)
         cpu = {"value": cbytes / dt / 1e9, "unit": UNIT, "cores": 4, "kind": "port",
                "sample": f"{csets} of the {nsets} FFN weight sets ({csets * 3} mat-muls, {cbytes / 1e6:.0f} MB) x {passes} passes, "
-                         f"AVX2 vec_dot, the reference's fixed 4-task split", "host_cpus": os.cpu_count()}
+                         f"AVX2 vec_dot, the reference's fixed 4-task split", "host_cpus": os.cpu_count(),
+               "build": f"g++ -O3 -mavx2 -mfma -mf16c ({cpu_build_kind})",
+               "parity": "unpinned: the reference cannot be built here (no Rust toolchain); C++ restatement"}
 
     if rank == 0:
         line = {
