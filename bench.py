@@ -685,6 +685,53 @@ def run_ours(args):
                                                    "note": "gate and up rows stacked into one 22016 x 4096 weight: one launch for both"}
         extra["config5_head_batch16"] = row("config5: output head 32000 x 4096 at batch 16", 32000, 4096, 16, time_mm(32000, 4096, 16, 8))
         extra["config5_ffn70b_batch16"] = row("config5: 70B-shape FFN 28672 x 8192 at batch 16", 28672, 8192, 16, time_mm(28672, 8192, 16, 4))
+        # Q6K weights (the next block format on the path): 4096 x 4096 mat-vec, GPU and the CPU port side by side
+        def time_q6k(n, k, b, copies):
+            O.build()
+            rng = np.random.default_rng(37000)
+            raw = rng.integers(0, 256, size=(n * (k // 256), 210), dtype=np.uint8)
+            raw[:, 208:210] = (rng.standard_normal(n * (k // 256)) * 1e-3).astype(np.float16).view(np.uint8).reshape(-1, 2)
+            ws = [torch.from_numpy(np.roll(raw, c, axis=0).copy()).to(device) for c in range(copies)]
+            wdim = gb.Dim.ggml((k, n), gb.GGmlType.Q6K).c_struct()
+            xb = torch.randn(b, k, device=device, dtype=torch.float32)
+            yb = torch.zeros(b, n, device=device, dtype=torch.float32)
+            xd_, yd_ = gb.Dim.ggml((k, b), gb.GGmlType.F32).c_struct(), gb.Dim.ggml((n, b), gb.GGmlType.F32).c_struct()
+
+            def run():
+                for wbuf in ws:
+                    rc = lib.galois_b200_mul_mat_q6k_f32(ctx, C.c_void_p(wbuf.data_ptr()), C.byref(wdim), C.c_void_p(xb.data_ptr()), C.byref(xd_),
+                                                         C.c_void_p(yb.data_ptr()), C.byref(yd_))
+                    if rc != 0:
+                        raise RuntimeError(f"mul_mat_q6k failed: {lib.galois_b200_last_error(ctx)} ({rc})")
+            for _ in range(3):
+                run()
+            torch.cuda.synchronize()
+            gg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gg, stream=stream):
+                run()
+            gg.replay()
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(10):
+                gg.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            us_gpu = e0.elapsed_time(e1) * 1e3 / (10 * copies)
+            cpu_us = None
+            if not args.no_cpu:
+                wh, xh = raw.reshape(n, -1), xb.cpu().numpy()
+                O.mul_mat_q6k(wh, xh)
+                t0, reps = time.perf_counter(), 0
+                while reps < 2 or time.perf_counter() - t0 < 0.5:
+                    O.mul_mat_q6k(wh, xh)
+                    reps += 1
+                cpu_us = (time.perf_counter() - t0) / reps * 1e6
+            ab = n * (k // 256) * 210 + b * k * 4 + b * n * 4
+            return {"config": f"Q6K weights {n} x {k} (210-byte super-blocks), batch {b}: quantiser + warp-per-row kernel", "us": us_gpu,
+                    "hbm_gbs": ab / us_gpu / 1e3, "frac_of_measured": ab / us_gpu / 1e3 / peak, "algorithmic_bytes": ab, "cpu_us_4thr": cpu_us,
+                    "host_cpus": ncpu}
+
+        extra["q6k_4096x4096_batch1"] = time_q6k(4096, 4096, 1, 32)
         # the headline step again with the overlap of independent mat-vecs switched off: every kernel waits for the
         # kernel in front of it at entry, as if each mat-mul consumed its predecessor's result
         lib.galois_b200_set_overlap(ctx, 0)

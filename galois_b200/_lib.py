@@ -82,6 +82,9 @@ SIGNATURES = {
     "galois_b200_mul_mat_q4_0_f32_add": ([_P, _P, _DP, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_mul_mat_q4_0_f32_host": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_mul_mat_q4_0_f32_static": ([_P, _P, _DP, _P, _DP, _P, _DP, C.c_char_p, _SZ], _I),
+    "galois_b200_mul_mat_q6k_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
+    "galois_b200_quantize_q8_k": ([_P, _P, _I64, _P, _I64, _I64], _I),
+    "galois_b200_block_isums_q6k_q8k": ([_P, _P, _P, _I64, _P], _I),
     "galois_b200_mul_mat_f16_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_rms_norm_f32": ([_P, _P, _DP, _P, _DP, _F], _I),
     "galois_b200_rms_norm_mul_f32": ([_P, _P, _DP, _P, _DP, _P, _DP, _F], _I),

@@ -71,12 +71,15 @@ def _want(t: Tensor, dtype: GGmlType, what: str):
 
 
 def galois_matmul(a: Tensor, b: Tensor, dst: Tensor) -> None:
-    """src/op.rs:3093-3111 -> CudaMatMul (src/cuda.rs:476-521): (Q4_0, F32, F32) and (F16, F32, F32)."""
+    """src/op.rs:3093-3111 -> CudaMatMul (src/cuda.rs:476-521): (Q4_0, F32, F32) and (F16, F32, F32); the
+    (Q6K, F32, F32) arm exists on the reference's CPU side only (src/op.rs:3454-3456)."""
     ctx = _gpu_ctx(a, b, dst)
     _want(b, GGmlType.F32, "galois_matmul src1")
     _want(dst, GGmlType.F32, "galois_matmul dst")
     if a.dtype == GGmlType.Q4_0:
         rc = lib.galois_b200_mul_mat_q4_0_f32(ctx, _p(a), _d(a), _p(b), _d(b), _p(dst), _d(dst))
+    elif a.dtype == GGmlType.Q6K:  # src/op.rs:3454-3456
+        rc = lib.galois_b200_mul_mat_q6k_f32(ctx, _p(a), _d(a), _p(b), _d(b), _p(dst), _d(dst))
     elif a.dtype == GGmlType.F16:
         rc = lib.galois_b200_mul_mat_f16_f32(ctx, _p(a), _d(a), _p(b), _d(b), _p(dst), _d(dst))
     else:

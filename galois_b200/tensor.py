@@ -33,12 +33,13 @@ class GGmlType(enum.IntEnum):
     F32 = 0
     F16 = 1
     Q4_0 = 2
+    Q6K = 14
     I32 = 18
 
 
 # elements per block and bytes per block (GS_BLCK_SIZE / GS_TYPE_SIZE, src/lib.rs:340-375)
-BLCK_SIZE = {GGmlType.F32: 1, GGmlType.F16: 1, GGmlType.Q4_0: QK4_0, GGmlType.I32: 1}
-TYPE_SIZE = {GGmlType.F32: 4, GGmlType.F16: 2, GGmlType.Q4_0: 18, GGmlType.I32: 4}
+BLCK_SIZE = {GGmlType.F32: 1, GGmlType.F16: 1, GGmlType.Q4_0: QK4_0, GGmlType.Q6K: 256, GGmlType.I32: 1}
+TYPE_SIZE = {GGmlType.F32: 4, GGmlType.F16: 2, GGmlType.Q4_0: 18, GGmlType.Q6K: 210, GGmlType.I32: 4}
 _NP_DTYPE = {GGmlType.F32: np.float32, GGmlType.F16: np.float16, GGmlType.I32: np.int32}
 
 
@@ -203,7 +204,7 @@ class Tensor:
         want = dim.elem_count() // BLCK_SIZE[dtype] * TYPE_SIZE[dtype]
         if raw.size != want:
             raise GError(f"from_raw: {raw.size} bytes for shape {tuple(shape)} {dtype.name}, expected {want}")
-        if dtype == GGmlType.Q4_0:
+        if dtype in (GGmlType.Q4_0, GGmlType.Q6K):
             host = raw.copy()
         else:
             host = raw.view(_NP_DTYPE[dtype]).copy()
@@ -213,8 +214,8 @@ class Tensor:
     def from_numpy(arr: np.ndarray, dtype: GGmlType, device: Device) -> "Tensor":
         """numpy array of shape (n3, n2, n1, n0) (C order) -> tensor with ne = [n0, n1, n2, n3]
         (``Tensor::from_vec``, src/lib.rs:2467-2475)."""
-        if dtype == GGmlType.Q4_0:
-            raise GError("from_numpy: Q4_0 tensors are built with from_raw")
+        if dtype in (GGmlType.Q4_0, GGmlType.Q6K):
+            raise GError("from_numpy: quantised tensors are built with from_raw")
         host = np.ascontiguousarray(arr, dtype=_NP_DTYPE[dtype])
         dim = Dim.ggml(tuple(host.shape)[::-1], dtype)
         return Tensor._place(dtype, dim, host.reshape(-1).copy(), device)
@@ -227,13 +228,13 @@ class Tensor:
             import torch
 
             tdt = {GGmlType.F32: torch.float32, GGmlType.F16: torch.float16, GGmlType.I32: torch.int32}.get(dtype)
-            if dtype == GGmlType.Q4_0:
-                st = torch.zeros(n * 18, dtype=torch.uint8, device=device.gpu.torch_device)
+            if dtype in (GGmlType.Q4_0, GGmlType.Q6K):
+                st = torch.zeros(n * TYPE_SIZE[dtype], dtype=torch.uint8, device=device.gpu.torch_device)
             else:
                 st = torch.zeros(n, dtype=tdt, device=device.gpu.torch_device)
             return Tensor(dtype, dim, st, device)
-        if dtype == GGmlType.Q4_0:
-            return Tensor(dtype, dim, np.zeros(n * 18, dtype=np.uint8), device)
+        if dtype in (GGmlType.Q4_0, GGmlType.Q6K):
+            return Tensor(dtype, dim, np.zeros(n * TYPE_SIZE[dtype], dtype=np.uint8), device)
         return Tensor(dtype, dim, np.zeros(n, dtype=_NP_DTYPE[dtype]), device)
 
     @staticmethod
@@ -285,7 +286,8 @@ class Tensor:
         if not t._dim.ggml_is_contiguous(BLCK_SIZE[t.dtype]):
             raise GError("to_numpy: tensor is not contiguous")
         n = t._dim.elem_count() // BLCK_SIZE[t.dtype]
-        if t.dtype == GGmlType.Q4_0:
-            return np.asarray(t.storage)[t.offset * 18 : (t.offset + n) * 18].copy()
+        if t.dtype in (GGmlType.Q4_0, GGmlType.Q6K):
+            sz = TYPE_SIZE[t.dtype]
+            return np.asarray(t.storage)[t.offset * sz : (t.offset + n) * sz].copy()
         flat = np.asarray(t.storage)[t.offset : t.offset + n]
         return flat.reshape(tuple(t._dim.shape[: t._dim.n_dims])[::-1]).copy()

@@ -248,6 +248,24 @@ int galois_b200_mul_mat_q4_0_f32_static(void* cu_stream, const void* w, const ga
                                         const galois_dim* xd, float* dst, const galois_dim* dd, char* errbuf,
                                         size_t errbuf_len);
 
+/* The (Q6K, F32, F32) arm of galois_matmul (src/op.rs:3454-3456), which the reference has on the CPU only
+ * (CudaStorageSlice holds no Q6K variant, src/cuda.rs:152-157): numerics of
+ * MatMul::f_q_f32_f32::<BlockQ6K> (src/op.rs:1383-1598) with <BlockQ8K as QuantType>::from_f32
+ * (src/ggml_quants.rs:687-719) and BlockQ6K::vec_dot (:568-665).  w: 210-byte super-blocks of 256 weights
+ * {u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d} (:484-491), wd = {K, N, ne02, ne03} with strides in
+ * super-blocks; x, dst as for the Q4_0 mat-mul; K % 256 == 0.  The Q8K quantisation and the integer sum of
+ * every super-block are bit-exact; f32 outputs within 1e-4 relative L2 (order of the additions).
+ * (Q8_0 WEIGHTS have no specification to follow: BlockQ8_0::vec_dot is todo!() in the reference,
+ * src/ggml_quants.rs:730-732.) */
+int galois_b200_mul_mat_q6k_f32(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
+                                const galois_dim* xd, float* dst, const galois_dim* dd);
+/* <BlockQ8K as QuantType>::from_f32 (src/ggml_quants.rs:687-719) into the reference's 292-byte blocks
+ * {f32 d; i8 qs[256]; i16 bsums[16]}, bit-identical to the CPU; and the per-super-block integer sums
+ * sum_s scales[s] * sum (q - 32) * q8 of one Q6K row against one row of such blocks, as the mat-mul kernel
+ * forms them (test hooks). */
+int galois_b200_quantize_q8_k(galois_b200_ctx* ctx, const float* x, int64_t x_row_stride, void* y, int64_t k, int64_t nrows);
+int galois_b200_block_isums_q6k_q8k(galois_b200_ctx* ctx, const void* w, const void* xq_blocks, int64_t nsb, int32_t* out);
+
 /* CudaMap2::f_x_y_y for CudaMatMul, F16 x F32 -> F32 (src/cuda.rs:404-418,
  * impl :881-992, cuBLAS :698-782), numerics of
  * MatMul::f_q_f32_f32::<f16> + vec_dot_f16 (src/ggml_quants.rs:113-135,

@@ -116,6 +116,12 @@ def lib():
             "orc_vec_dot_f16": ([P, P, I64, I], F),
             "orc_mul_mat_q4_0_f32": ([P, DP, P, DP, P, DP, I, I], I),
             "orc_mul_mat_f16_f32": ([P, DP, P, DP, P, DP, I, I], I),
+            "orc_mul_mat_q6k_f32": ([P, DP, P, DP, P, DP, I, I], I),
+            "orc_quantize_row_q8k": ([P, P, I64], None),
+            "orc_quantize_row_q6k": ([P, P, I64], None),
+            "orc_dequantize_row_q6k": ([P, P, I64], None),
+            "orc_vec_dot_q6k_q8k_avx": ([P, P, I64], F),
+            "orc_block_isums_q6k_q8k": ([P, P, I64, P, I], None),
             "orc_rms_norm_f32": ([P, DP, P, DP, F], I),
             "orc_rope_f32": ([P, DP, P, DP, P, DP, I, I, I, F, F, F, I], I),
             "orc_exp_f16_table": ([], P),
@@ -227,6 +233,70 @@ def quantize_q8_0(x: np.ndarray) -> np.ndarray:
     for r in range(rows):
         lib().orc_quantize_row_q8_0(_p(xr[r]), _p(out[r]), k)
     return out.reshape(*x.shape[:-1], k // QK * Q8_0_BYTES)
+
+
+QK_K = 256
+Q6K_BYTES = 210
+Q8K_BYTES = 292
+
+
+def quantize_q6k(x: np.ndarray) -> np.ndarray:
+    """f32 [..., k] -> Q6K bytes [..., k/256 * 210] with the oracle's own (simple) quantiser."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    k = x.shape[-1]
+    rows = x.reshape(-1, k)
+    out = np.empty((rows.shape[0], k // QK_K * Q6K_BYTES), np.uint8)
+    for r in range(rows.shape[0]):
+        lib().orc_quantize_row_q6k(_p(rows[r]), _p(out[r]), k)
+    return out.reshape(*x.shape[:-1], k // QK_K * Q6K_BYTES)
+
+
+def dequantize_q6k(w: np.ndarray, k: int) -> np.ndarray:
+    w = np.ascontiguousarray(w, dtype=np.uint8).reshape(-1, k // QK_K * Q6K_BYTES)
+    out = np.empty((w.shape[0], k), np.float32)
+    for r in range(w.shape[0]):
+        lib().orc_dequantize_row_q6k(_p(w[r]), _p(out[r]), k)
+    return out
+
+
+def quantize_q8k(x: np.ndarray) -> np.ndarray:
+    """f32 [..., k] -> BlockQ8K bytes [..., k/256 * 292] (<BlockQ8K as QuantType>::from_f32)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    k = x.shape[-1]
+    rows = x.reshape(-1, k)
+    out = np.zeros((rows.shape[0], k // QK_K * Q8K_BYTES), np.uint8)
+    for r in range(rows.shape[0]):
+        lib().orc_quantize_row_q8k(_p(rows[r]), _p(out[r]), k)
+    return out.reshape(*x.shape[:-1], k // QK_K * Q8K_BYTES)
+
+
+def vec_dot_q6k_q8k(w_row: np.ndarray, x_row: np.ndarray) -> float:
+    w_row = np.ascontiguousarray(w_row, dtype=np.uint8)
+    x_row = np.ascontiguousarray(x_row, dtype=np.uint8)
+    return float(lib().orc_vec_dot_q6k_q8k_avx(_p(w_row), _p(x_row), w_row.size // Q6K_BYTES))
+
+
+def block_isums_q6k(w_row: np.ndarray, x_row: np.ndarray, avx: bool = False) -> np.ndarray:
+    w_row = np.ascontiguousarray(w_row, dtype=np.uint8)
+    x_row = np.ascontiguousarray(x_row, dtype=np.uint8)
+    nb = w_row.size // Q6K_BYTES
+    out = np.empty(nb, np.int32)
+    lib().orc_block_isums_q6k_q8k(_p(w_row), _p(x_row), nb, _p(out), int(avx))
+    return out
+
+
+def mul_mat_q6k(w: np.ndarray, x: np.ndarray, nth: int = 4) -> np.ndarray:
+    """w: Q6K bytes [N][K/256*210]; x: f32 [B][K] -> f32 [B][N] (MatMul::f_q_f32_f32::<BlockQ6K>)."""
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    n, k = w.shape[0], x.shape[-1]
+    b = x.shape[0]
+    dst = np.empty((b, n), np.float32)
+    wd = Dim.contiguous([k, n], QK_K)
+    xd = Dim.contiguous([k, b])
+    dd = Dim.contiguous([n, b])
+    _check(lib().orc_mul_mat_q6k_f32(_p(w), wd, _p(x), xd, _p(dst), dd, nth, 1), "mul_mat_q6k")
+    return dst
 
 
 def vec_dot_q4_0_q8_0(w_row: np.ndarray, x_row: np.ndarray, avx: bool = True) -> float:

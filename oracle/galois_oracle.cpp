@@ -59,6 +59,22 @@ typedef struct {
     int8_t qs[32];
 } orc_block_q8_0;
 
+// BlockQ6K (src/ggml_quants.rs:484-491) and BlockQ8K (:676-682), QK_K = 256
+#pragma pack(push, 1)
+struct orc_block_q6k {
+    uint8_t ql[128];   // low 4 bits
+    uint8_t qh[64];    // high 2 bits
+    int8_t scales[16]; // one per 16 elements
+    uint16_t d;        // f16 super-block scale
+};
+#pragma pack(pop)
+struct orc_block_q8k {
+    float d;
+    int8_t qs[256];
+    int16_t bsums[16];
+};
+static_assert(sizeof(orc_block_q6k) == 210, "Q6K block is 210 bytes");
+static_assert(sizeof(orc_block_q8k) == 292, "Q8K block is 292 bytes");
 static_assert(sizeof(orc_block_q4_0) == 18, "Q4_0 block is 18 bytes");
 static_assert(sizeof(orc_block_q8_0) == 34, "Q8_0 block is 34 bytes");
 
@@ -359,6 +375,182 @@ float orc_vec_dot_f16(const uint16_t* x, const uint16_t* y, int64_t k, int use_a
     return use_avx ? vec_dot_f16_avx2(x, y, k) : vec_dot_f16_scalar(x, y, k);
 }
 
+// ------------------------------------------------------------------ Q6K . Q8K
+// <BlockQ8K as QuantType>::from_f32 (src/ggml_quants.rs:687-719): per 256 elements, `max` = the first element
+// of largest magnitude WITH its sign, iscale = -128 / max, q = min(round(iscale * x), 127) as i8 (a
+// saturating cast), bsums = sums of 16 quants, d = 1 / iscale; an all-zero block has d = 0.
+void orc_quantize_row_q8k(const float* x, void* vy, int64_t k) {
+    orc_block_q8k* y = (orc_block_q8k*)vy;
+    for (int64_t i = 0; i < k / 256; i++) {
+        const float* xs = x + i * 256;
+        float max = 0.0f, amax = 0.0f;
+        for (int j = 0; j < 256; j++)
+            if (amax < fabsf(xs[j])) amax = fabsf(xs[j]), max = xs[j];
+        if (amax == 0.0f) {
+            y[i].d = 0.0f;
+            memset(y[i].qs, 0, 256);
+            // (the reference leaves bsums as they were; a fresh Vec is zeroed)
+            memset(y[i].bsums, 0, sizeof(y[i].bsums));
+            continue;
+        }
+        const float iscale = -128.0f / max;
+        for (int j = 0; j < 256; j++) {
+            const float v = fminf(roundf(iscale * xs[j]), 127.0f);
+            y[i].qs[j] = (int8_t)std::max(-128.0f, v);  // `as i8` saturates
+        }
+        for (int j = 0; j < 16; j++) {
+            int sum = 0;
+            for (int ii = 0; ii < 16; ii++) sum += y[i].qs[j * 16 + ii];
+            y[i].bsums[j] = (int16_t)sum;
+        }
+        y[i].d = 1.0f / iscale;
+    }
+}
+
+// The 6-bit quant (0..63) of element e of a super-block, as BlockQ6K::from_f32 packs it
+// (src/ggml_quants.rs:543-560): within each half of 128, element l + 32 m (m = 0..3) has its low nibble in
+// ql[l + 32 (m & 1)] (low half of the byte for m < 2, high half otherwise) and its top two bits in bits
+// 2m .. 2m + 1 of qh[l].
+static inline int q6k_quant(const orc_block_q6k& b, int e) {
+    const int half = e / 128, r = e % 128, m = r / 32, l = r % 32;
+    const uint8_t lo = b.ql[half * 64 + l + 32 * (m & 1)];
+    const int nib = m < 2 ? (lo & 0xF) : (lo >> 4);
+    const int top = (b.qh[half * 32 + l] >> (2 * m)) & 3;
+    return nib | (top << 4);
+}
+
+// Element e is d * scales[e / 16] * (q - 32): the decode BlockQ6K::vec_dot presupposes (the reference's
+// to_f32 is an empty body, src/ggml_quants.rs:566).
+void orc_dequantize_row_q6k(const void* vx, float* dst, int64_t k) {
+    const orc_block_q6k* x = (const orc_block_q6k*)vx;
+    for (int64_t i = 0; i < k / 256; i++) {
+        const float d = f16_to_f32(x[i].d);
+        for (int e = 0; e < 256; e++) dst[i * 256 + e] = d * (float)x[i].scales[e / 16] * (float)(q6k_quant(x[i], e) - 32);
+    }
+}
+
+// A Q6K quantiser for synthetic weights (NOT the reference's make_qx_quants search, src/ggml_quants.rs:235-330,
+// 496-563: parity of the mat-mul does not depend on how the bytes were chosen, both sides consume the same
+// ones).  Sub-block scale = amax / 31, super-block d = largest sub-block scale / 127.
+void orc_quantize_row_q6k(const float* x, void* vy, int64_t k) {
+    orc_block_q6k* y = (orc_block_q6k*)vy;
+    for (int64_t i = 0; i < k / 256; i++) {
+        const float* xs = x + i * 256;
+        float sub[16], smax = 0.0f;
+        for (int s = 0; s < 16; s++) {
+            float a = 0.0f;
+            for (int j = 0; j < 16; j++) a = fmaxf(a, fabsf(xs[16 * s + j]));
+            sub[s] = a / 31.0f;
+            smax = fmaxf(smax, sub[s]);
+        }
+        memset(&y[i], 0, sizeof(y[i]));
+        const float d = smax / 127.0f;
+        y[i].d = f32_to_f16(d);
+        const float dq = f16_to_f32(y[i].d);
+        uint8_t L[256];
+        for (int s = 0; s < 16; s++) {
+            int sc = dq > 0.0f ? (int)roundf(sub[s] / dq) : 0;
+            sc = std::min(127, std::max(sc, dq > 0.0f && sub[s] > 0.0f ? 1 : 0));
+            y[i].scales[s] = (int8_t)sc;
+            const float step = dq * (float)sc;
+            for (int j = 0; j < 16; j++) {
+                int q = step > 0.0f ? (int)roundf(xs[16 * s + j] / step) : 0;
+                L[16 * s + j] = (uint8_t)(std::min(31, std::max(-32, q)) + 32);
+            }
+        }
+        for (int half = 0; half < 2; half++)
+            for (int l = 0; l < 32; l++) {
+                const uint8_t* q = L + 128 * half;
+                y[i].ql[64 * half + l] = (q[l] & 0xF) | ((q[l + 64] & 0xF) << 4);
+                y[i].ql[64 * half + l + 32] = (q[l + 32] & 0xF) | ((q[l + 96] & 0xF) << 4);
+                y[i].qh[32 * half + l] = (q[l] >> 4) | ((q[l + 32] >> 4) << 2) | ((q[l + 64] >> 4) << 4) | ((q[l + 96] >> 4) << 6);
+            }
+    }
+}
+
+// BlockQ6K::vec_dot (src/ggml_quants.rs:568-665), AVX2, intrinsic for intrinsic.  get_scale_shuffle(i)
+// (:44-53) is row i of a table whose row i holds byte 2i eight times, then byte 2i + 1 eight times.
+static inline __m128i q6k_scale_shuffle(int i) {
+    return _mm_set_epi8(2 * i + 1, 2 * i + 1, 2 * i + 1, 2 * i + 1, 2 * i + 1, 2 * i + 1, 2 * i + 1, 2 * i + 1, 2 * i, 2 * i, 2 * i, 2 * i,
+                        2 * i, 2 * i, 2 * i, 2 * i);
+}
+float orc_vec_dot_q6k_q8k_avx(const void* vx, const void* vy, int64_t nb) {
+    const orc_block_q6k* xs = (const orc_block_q6k*)vx;
+    const orc_block_q8k* ys = (const orc_block_q8k*)vy;
+    const __m256i m4 = _mm256_set1_epi8(0xF), m2 = _mm256_set1_epi8(3), m32s = _mm256_set1_epi8(32);
+    __m256 acc = _mm256_setzero_ps();
+    for (int64_t i = 0; i < nb; i++) {
+        const float d = ys[i].d * f16_to_f32(xs[i].d);
+        const uint8_t* q4 = xs[i].ql;
+        const uint8_t* qh = xs[i].qh;
+        const int8_t* q8 = ys[i].qs;
+        const __m128i scales = _mm_loadu_si128((const __m128i*)xs[i].scales);
+        __m256i sumi = _mm256_setzero_si256();
+        for (int j = 0; j < 2; j++) {
+            const int is = j * 4;
+            const __m128i scale_0 = _mm_shuffle_epi8(scales, q6k_scale_shuffle(is));
+            const __m128i scale_1 = _mm_shuffle_epi8(scales, q6k_scale_shuffle(is + 1));
+            const __m128i scale_2 = _mm_shuffle_epi8(scales, q6k_scale_shuffle(is + 2));
+            const __m128i scale_3 = _mm_shuffle_epi8(scales, q6k_scale_shuffle(is + 3));
+            const __m256i q4bits1 = _mm256_loadu_si256((const __m256i*)q4);
+            q4 += 32;
+            const __m256i q4bits2 = _mm256_loadu_si256((const __m256i*)q4);
+            q4 += 32;
+            const __m256i q4bits_h = _mm256_loadu_si256((const __m256i*)qh);
+            qh += 32;
+            const __m256i q4h_0 = _mm256_slli_epi16(_mm256_and_si256(q4bits_h, m2), 4);
+            const __m256i q4h_1 = _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(q4bits_h, 2), m2), 4);
+            const __m256i q4h_2 = _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(q4bits_h, 4), m2), 4);
+            const __m256i q4h_3 = _mm256_slli_epi16(_mm256_and_si256(_mm256_srli_epi16(q4bits_h, 6), m2), 4);
+            const __m256i q4_0 = _mm256_or_si256(_mm256_and_si256(q4bits1, m4), q4h_0);
+            const __m256i q4_1 = _mm256_or_si256(_mm256_and_si256(q4bits2, m4), q4h_1);
+            const __m256i q4_2 = _mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(q4bits1, 4), m4), q4h_2);
+            const __m256i q4_3 = _mm256_or_si256(_mm256_and_si256(_mm256_srli_epi16(q4bits2, 4), m4), q4h_3);
+            const __m256i q8_0 = _mm256_loadu_si256((const __m256i*)q8);
+            const __m256i q8_1 = _mm256_loadu_si256((const __m256i*)(q8 + 32));
+            const __m256i q8_2 = _mm256_loadu_si256((const __m256i*)(q8 + 64));
+            const __m256i q8_3 = _mm256_loadu_si256((const __m256i*)(q8 + 96));
+            q8 += 128;
+            const __m256i q8s_0 = _mm256_maddubs_epi16(m32s, q8_0), q8s_1 = _mm256_maddubs_epi16(m32s, q8_1);
+            const __m256i q8s_2 = _mm256_maddubs_epi16(m32s, q8_2), q8s_3 = _mm256_maddubs_epi16(m32s, q8_3);
+            __m256i p16_0 = _mm256_maddubs_epi16(q4_0, q8_0), p16_1 = _mm256_maddubs_epi16(q4_1, q8_1);
+            __m256i p16_2 = _mm256_maddubs_epi16(q4_2, q8_2), p16_3 = _mm256_maddubs_epi16(q4_3, q8_3);
+            p16_0 = _mm256_sub_epi16(p16_0, q8s_0), p16_1 = _mm256_sub_epi16(p16_1, q8s_1);
+            p16_2 = _mm256_sub_epi16(p16_2, q8s_2), p16_3 = _mm256_sub_epi16(p16_3, q8s_3);
+            p16_0 = _mm256_madd_epi16(_mm256_cvtepi8_epi16(scale_0), p16_0);
+            p16_1 = _mm256_madd_epi16(_mm256_cvtepi8_epi16(scale_1), p16_1);
+            p16_2 = _mm256_madd_epi16(_mm256_cvtepi8_epi16(scale_2), p16_2);
+            p16_3 = _mm256_madd_epi16(_mm256_cvtepi8_epi16(scale_3), p16_3);
+            sumi = _mm256_add_epi32(sumi, _mm256_add_epi32(p16_0, p16_1));
+            sumi = _mm256_add_epi32(sumi, _mm256_add_epi32(p16_2, p16_3));
+        }
+        acc = _mm256_fmadd_ps(_mm256_broadcast_ss(&d), _mm256_cvtepi32_ps(sumi), acc);
+    }
+    return hsum_float_8(acc);
+}
+
+// Per super-block: sum over its 16 sub-blocks of scale * sum (q - 32) * q8, in plain integer arithmetic
+// (what the eight i32 lanes of `sumi` above add up to), and with via_avx != 0 the lanes themselves summed.
+void orc_block_isums_q6k_q8k(const void* vx, const void* vy, int64_t nb, int32_t* out, int via_avx) {
+    const orc_block_q6k* xs = (const orc_block_q6k*)vx;
+    const orc_block_q8k* ys = (const orc_block_q8k*)vy;
+    for (int64_t i = 0; i < nb; i++) {
+        if (!via_avx) {
+            int32_t t = 0;
+            for (int e = 0; e < 256; e++) t += (int32_t)xs[i].scales[e / 16] * (q6k_quant(xs[i], e) - 32) * (int32_t)ys[i].qs[e];
+            out[i] = t;
+        } else {
+            // run the vector code on this block alone with both scales forced to 1: acc lanes = float(sumi lanes)
+            orc_block_q6k x1 = xs[i];
+            orc_block_q8k y1 = ys[i];
+            x1.d = f32_to_f16(1.0f);
+            y1.d = 1.0f;
+            // the lanes are exact integers below 2^24 for these magnitudes, and so is their float sum here
+            out[i] = (int32_t)orc_vec_dot_q6k_q8k_avx(&x1, &y1, 1);
+        }
+    }
+}
+
 // ------------------------------------------------------------------ mat-mul
 // src/op.rs:1383-1598  MatMul::f_q_f32_f32<T>, generic over the weight block
 // type T (BlockQ4_0 -> VecDotType BlockQ8_0, block 32; f16 -> VecDotType f16,
@@ -368,7 +560,8 @@ float orc_vec_dot_f16(const uint16_t* x, const uint16_t* y, int64_t k, int use_a
 //      src1 rows (:1491-1492), 16x16 tiling (:1477-1478, :1513-1516)
 //   3. dst[i1*nb1 + i2*nb2 + i3*nb3 + ir0] = vec_dot(src0 row, quantised src1 row)
 // with src0 broadcast over dims 2/3: i02 = i12 / r2, i03 = i13 / r3 (:1482-1483).
-// kind: 0 = Q4_0 weights, 1 = F16 weights.  use_avx selects vec_dot flavour.
+// kind: 0 = Q4_0 weights, 1 = F16 weights, 2 = Q6K weights (VecDotType BlockQ8K, block 256).  use_avx selects
+// the vec_dot flavour.
 // nth is the task count (4 in the reference); returns 0 or a negative code when
 // an assertion of the reference would fire.
 static int mul_mat_driver(int kind, const void* w, const orc_dim* wd, const float* x, const orc_dim* xd,
@@ -379,7 +572,7 @@ static int mul_mat_driver(int kind, const void* w, const orc_dim* wd, const floa
     const int64_t nb00 = wd->nb[0], nb01 = wd->nb[1], nb02 = wd->nb[2], nb03 = wd->nb[3];
     const int64_t nb10 = xd->nb[0], nb11 = xd->nb[1], nb12 = xd->nb[2], nb13 = xd->nb[3];
     const int64_t nb0 = dd->nb[0], nb1 = dd->nb[1], nb2 = dd->nb[2], nb3 = dd->nb[3];
-    const int64_t block_size = kind == 0 ? 32 : 1;
+    const int64_t block_size = kind == 0 ? 32 : (kind == 2 ? 256 : 1);
     if (ne00 != ne10) return -1;
     if (ne10 % block_size != 0) return -1;                                  // from_f32 panics
     if (!(ne0 == ne01 && ne1 == ne11 && ne2 == ne12 && ne3 == ne13)) return -2;  // :1422-1425
@@ -388,8 +581,8 @@ static int mul_mat_driver(int kind, const void* w, const orc_dim* wd, const floa
     if (ne02 == 0 || ne03 == 0 || ne12 % ne02 != 0 || ne13 % ne03 != 0) return -5;  // :1473-1474
 
     const int64_t row_size = ne10 / block_size;  // VecDotType elements per activation row
-    const size_t vd_bytes = kind == 0 ? sizeof(orc_block_q8_0) : sizeof(uint16_t);
-    const size_t w_bytes = kind == 0 ? sizeof(orc_block_q4_0) : sizeof(uint16_t);
+    const size_t vd_bytes = kind == 0 ? sizeof(orc_block_q8_0) : (kind == 2 ? sizeof(orc_block_q8k) : sizeof(uint16_t));
+    const size_t w_bytes = kind == 0 ? sizeof(orc_block_q4_0) : (kind == 2 ? sizeof(orc_block_q6k) : sizeof(uint16_t));
     std::vector<uint8_t> quant_list((size_t)(ne11 * ne12 * ne13 * row_size) * vd_bytes);
     {
         int64_t idx = 0;
@@ -400,6 +593,8 @@ static int mul_mat_driver(int kind, const void* w, const orc_dim* wd, const floa
                     uint8_t* q = quant_list.data() + (size_t)idx * vd_bytes;
                     if (kind == 0)
                         orc_quantize_row_q8_0(src, q, ne10);
+                    else if (kind == 2)
+                        orc_quantize_row_q8k(src, q, ne10);
                     else
                         orc_f32_to_f16_row(src, (uint16_t*)q, ne10);  // src/ggml_quants.rs:117-122
                     idx += row_size;
@@ -434,6 +629,8 @@ static int mul_mat_driver(int kind, const void* w, const orc_dim* wd, const floa
                         if (kind == 0)
                             v = use_avx ? orc_vec_dot_q4_0_q8_0_avx(wrow, src1, ne00 / 32)
                                         : orc_vec_dot_q4_0_q8_0_scalar(wrow, src1, ne00 / 32);
+                        else if (kind == 2)
+                            v = orc_vec_dot_q6k_q8k_avx(wrow, src1, ne00 / 256);  // the reference has no scalar Q6K dot
                         else
                             v = orc_vec_dot_f16((const uint16_t*)wrow, (const uint16_t*)src1, ne00, use_avx);
                         d[ir0] = v;
@@ -454,6 +651,11 @@ static int mul_mat_driver(int kind, const void* w, const orc_dim* wd, const floa
 int orc_mul_mat_q4_0_f32(const void* w, const orc_dim* wd, const float* x, const orc_dim* xd, float* dst,
                          const orc_dim* dd, int nth, int use_avx) {
     return mul_mat_driver(0, w, wd, x, xd, dst, dd, nth, use_avx);
+}
+// (Q6K, F32, F32) arm of Map2::map (src/op.rs:3454-3456)
+int orc_mul_mat_q6k_f32(const void* w, const orc_dim* wd, const float* x, const orc_dim* xd, float* dst,
+                        const orc_dim* dd, int nth, int use_avx) {
+    return mul_mat_driver(2, w, wd, x, xd, dst, dd, nth, use_avx);
 }
 int orc_mul_mat_f16_f32(const void* w, const orc_dim* wd, const float* x, const orc_dim* xd, float* dst,
                         const orc_dim* dd, int nth, int use_avx) {
