@@ -73,6 +73,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // K-major, no-swizzle shared-memory matrix descriptor: 8-row x 16-byte core matrices; `lbo` =
@@ -407,35 +416,42 @@ int gb_mm_q4_0_tc_block_isums(galois_b200_ctx* ctx, const void* w, const galois_
 
 // ====================================================================================================
 // The same GEMM on weights repacked once at upload (galois_b200_prepare_weight_q4_0): the nibbles of every
-// 128-row tile are stored as unsigned bytes already in the canonical K-major UMMA layout, block after
-// block, with the f32 block scales beside them, so a K step of the A operand is ONE bulk copy and the four
-// unpack warps of the kernel above are gone.  What else changes:
-//   * four (BN = 128) or eight (BN = 64) int32 accumulator tiles live in TMEM, so the MMA issuer runs up to
-//     that many blocks ahead of the epilogue and neither side waits for the other's hand-shake;
-//   * an epilogue warp reads both 32-column halves of its 64 columns before it hands the buffer back and
-//     does its scale-accumulate arithmetic two columns at a time (add / mul / fma .f32x2).
+// 128-row tile are stored as signed bytes (nibble - 8) already in the canonical K-major UMMA layout, block
+// after block, with the f32 block scales beside them, so a K step of the A operand is ONE bulk copy and the
+// four unpack warps of the kernel above are gone.  What else changes:
+//   * the int32 tile the tensor core writes is the block sum of vec_dot_q8_0 itself (signed x signed, no
+//     "- 8 * sum of the activation block" correction), converted with one int -> float instruction;
+//   * four int32 accumulator tiles live in TMEM, one per block of a K step, so the MMA issuer runs a whole
+//     K step ahead of the epilogue and neither side waits for the other's hand-shake;
+//   * sixteen epilogue warps, four per TMEM lane group, each with a quarter of the tile's columns; the
+//     scale-accumulate arithmetic handles two columns per instruction (mul / fma .f32x2);
+//   * four stages of four blocks: the bytes in flight, not the step size, set the streaming rate of a CTA.
+// The kernel is bound by the instruction issue of the epilogue (about 2 instructions per output and block:
+// convert, half a multiply, half a fused multiply-add, plus the hand-shakes), not by the tensor pipe, the
+// TMEM reads or the bulk copies: timing the same kernel with each of those parts removed shows it.
 // Numerics are unchanged: one exact int32 tile per 32-element block, (d_w * d_x) exact in f32, one rounding
 // per fused multiply-add.
 namespace {
 
-constexpr int TP_EPI_WARPS = 8;
+constexpr int TP_EPI_WARPS = 16;  // four per TMEM lane group, each with a quarter of the tile's columns
 constexpr int TP_THREADS = (TP_EPI_WARPS + 2) * 32;  // + MMA issuer + loader
-constexpr int TP_STAGES = 2;
+constexpr int TP_KC = 4;      // blocks per K step
+constexpr int TP_STAGES = 4;
 
 template <int BN>
 struct tp_smem {
     static constexpr uint32_t A_BLOCK = TC_M * 32, B_BLOCK = BN * 32;
-    static constexpr uint32_t A_BYTES = TC_KC * A_BLOCK, B_BYTES = TC_KC * B_BLOCK;
-    static constexpr uint32_t DW_BYTES = TC_KC * TC_M * 4, XS_BYTES = TC_KC * BN * 8;
+    static constexpr uint32_t A_BYTES = TP_KC * A_BLOCK, B_BYTES = TP_KC * B_BLOCK;
+    static constexpr uint32_t DW_BYTES = TP_KC * TC_M * 4, XS_BYTES = TP_KC * BN * 4;
     static constexpr uint32_t STAGE = A_BYTES + B_BYTES + DW_BYTES + XS_BYTES;
     static constexpr uint32_t BAR_OFF = TP_STAGES * STAGE;
     static constexpr uint32_t TOTAL = BAR_OFF + 256;
-    static constexpr int NBUF = 512 / BN > 4 ? 4 : 512 / BN;  // TMEM accumulator tiles
+    static constexpr int NBUF = 4;  // TMEM accumulator tiles (BN <= 128 columns each)
 };
 
 // Repack: thread = (weight row, block).  Layout of the result, per 128-row tile t and block kb:
 //   pa[((t * nkb + kb) * 2 + chunk) * 2048 + row_in_tile * 16 + i]  = nibble i (chunk 0: low nibbles = elements
-//        0..15, chunk 1: high nibbles = elements 16..31) of the block, as an unsigned byte
+//        0..15, chunk 1: high nibbles = elements 16..31) of the block minus 8, as a signed byte
 //   pd[(t * nkb + kb) * 128 + row_in_tile]                          = f32(d)
 // Rows beyond N (ragged last tile) are zero.
 __global__ void __launch_bounds__(256) repack_q4_0_tc_kernel(const uint8_t* __restrict__ w, int64_t row_blocks, uint8_t* __restrict__ pa,
@@ -454,8 +470,8 @@ __global__ void __launch_bounds__(256) repack_q4_0_tc_kernel(const uint8_t* __re
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const uint32_t q = (uint32_t)p[1 + 2 * i] | ((uint32_t)p[2 + 2 * i] << 16);
-            lo[i] = q & 0x0F0F0F0Fu;
-            hi[i] = (q >> 4) & 0x0F0F0F0Fu;
+            lo[i] = __vsub4(q & 0x0F0F0F0Fu, 0x08080808u);
+            hi[i] = __vsub4((q >> 4) & 0x0F0F0F0Fu, 0x08080808u);
         }
     }
     uint8_t* base = pa + ((size_t)t * nkb + kb) * (2 * 2048) + (size_t)r * 16;
@@ -464,10 +480,10 @@ __global__ void __launch_bounds__(256) repack_q4_0_tc_kernel(const uint8_t* __re
     pd[((size_t)t * nkb + kb) * TC_M + r] = d;
 }
 
-// The activation quantiser of the kernel above with the block constants of two neighbouring columns side by
-// side: xs[col tile][block][BN / 2] {f32 d0, f32 d1, i32 MAGIC - 8 sum0, i32 MAGIC - 8 sum1}.
+// The activation quantiser of the kernel above; of the block constants only the scale is kept:
+// xs[col tile][block][BN] f32 d.
 __global__ void __launch_bounds__(256) quantize_q8_tp_kernel(const float* __restrict__ x, int64_t x_stride, int K, int B, int BN,
-                                                             uint8_t* __restrict__ qs, int* __restrict__ xs) {
+                                                             uint8_t* __restrict__ qs, float* __restrict__ xs) {
     const int nkb = K >> 5;
     const int sub = threadIdx.x & 7;
     const int kb = (blockIdx.x * 256 + threadIdx.x) >> 3;
@@ -484,31 +500,19 @@ __global__ void __launch_bounds__(256) quantize_q8_tp_kernel(const float* __rest
     const int q1 = max(-128, min(127, (int)roundf(__fmul_rn(v.y, id))));
     const int q2 = max(-128, min(127, (int)roundf(__fmul_rn(v.z, id))));
     const int q3 = max(-128, min(127, (int)roundf(__fmul_rn(v.w, id))));
-    int s = q0 + q1 + q2 + q3;
-#pragma unroll
-    for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     if (live) {
         const int tile = col / BN, ci = col % BN;
         const uint32_t packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
         const size_t blk_base = ((size_t)tile * nkb + kb) * (size_t)(BN * 32);
         const size_t off = blk_base + (size_t)(sub >> 2) * (BN * 16) + (size_t)(ci >> 3) * 128 + (ci & 7) * 16 + (sub & 3) * 4;
         *reinterpret_cast<uint32_t*>(qs + off) = packed;
-        if (sub == 0) {
-            int* p = xs + (((size_t)tile * nkb + kb) * (BN / 2) + (ci >> 1)) * 4 + (ci & 1);
-            p[0] = __float_as_int(__half2float(__float2half_rn(d)));
-            p[2] = (int)TC_MAGIC - 8 * s;
-        }
+        if (sub == 0) xs[((size_t)tile * nkb + kb) * BN + ci] = __half2float(__float2half_rn(d));
     }
 }
 
 // Two f32 in one 64-bit register (low word first).
 __device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
     return (uint64_t)__float_as_uint(lo) | ((uint64_t)__float_as_uint(hi) << 32);
-}
-__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
 }
 __device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
     uint64_t d;
@@ -529,7 +533,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
     constexpr int NBUF = L::NBUF;
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nkb = K >> 5, nsteps = nkb / TC_KC;
+    const int nkb = K >> 5, nsteps = nkb / TP_KC;
     const int row_tile = blockIdx.x, col_tile = blockIdx.y;
 
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
@@ -563,51 +567,51 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
 
     if (warp < TP_EPI_WARPS) {
         // ------------------------------------------------------------ epilogue
-        const int lane_grp = warp & 3, half = warp >> 2;
+        const int lane_grp = warp & 3, half = warp >> 2;  // `half`: which column share of the tile
         const int row_in_tile = lane_grp * 32 + lane;
-        constexpr int NC = BN / 2;   // columns of this warp
+        constexpr int NC = BN / (TP_EPI_WARPS / 4);  // columns of this warp
         constexpr int NP = NC / 2;   // column pairs
-        uint64_t acc[NP];
+        uint64_t acc[NP];  // two f32 each
 #pragma unroll
-        for (int c = 0; c < NP; c++) acc[c] = 0ull;  // two +0.0f
-        const uint64_t neg_magic = f2_pack(-12582912.0f, -12582912.0f);
-        for (int g = 0; g < nkb && ok; g++) {
-            const int buf = g % NBUF, step = g / TC_KC, kb = g % TC_KC, s = step % TP_STAGES;
-            if (kb == 0) {
-                // the scales of this K step are in shared memory once the step's bytes have landed
-                ok = mbar_wait_bounded(&full[s], (uint32_t)(step / TP_STAGES) & 1u);
-                if (!ok) break;
-            }
-            ok = mbar_wait_bounded(&tmem_full[buf], (uint32_t)(g / NBUF) & 1u);
+        for (int c = 0; c < NP; c++) acc[c] = 0ull;
+        const uint32_t tbase = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(half * NC);
+        static_assert(NBUF == TP_KC, "block kb of every K step uses accumulator tile kb");
+        for (int step = 0; step < nsteps && ok; step++) {
+            const int s = step & (TP_STAGES - 1);
+            // the scales of this K step are in shared memory once the step's bytes have landed
+            ok = mbar_spin_bounded(&full[s], (uint32_t)(step / TP_STAGES) & 1u);
             if (!ok) break;
-            tc_fence_after();
-            uint32_t r[NC];
-#pragma unroll
-            for (int c0 = 0; c0 < NC; c0 += 32)
-                tmem_ld32(tmem_base + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)(buf * BN + half * NC + c0), r + c0);
-            tmem_ld_wait();
-            // the tile is in registers: hand the buffer back to the MMA issuer
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
             const uint8_t* stage = smem + (uint32_t)s * L::STAGE;
-            const float dw = reinterpret_cast<const float*>(stage + L::A_BYTES + L::B_BYTES)[kb * TC_M + row_in_tile];
-            const uint64_t dw2 = f2_pack(dw, dw);
-            const int4* xsp = reinterpret_cast<const int4*>(stage + L::A_BYTES + L::B_BYTES + L::DW_BYTES) + kb * (BN / 2) + half * NP;
+            const float* dwp = reinterpret_cast<const float*>(stage + L::A_BYTES + L::B_BYTES) + row_in_tile;
+            const uint64_t* xsp = reinterpret_cast<const uint64_t*>(stage + L::A_BYTES + L::B_BYTES + L::DW_BYTES) + half * NP;
 #pragma unroll
-            for (int c = 0; c < NP; c++) {
-                const int4 sc = xsp[c];  // {d_x of two columns, MAGIC - 8 sum of two columns} (the same for all lanes)
-                // float(isum) through the 1.5 * 2^23 trick, exact for |isum| < 2^22
-                const uint64_t i2 = (uint64_t)(uint32_t)((int)r[2 * c] + sc.z) | ((uint64_t)(uint32_t)((int)r[2 * c + 1] + sc.w) << 32);
-                const uint64_t f2 = f2_add(i2, neg_magic);
-                const uint64_t dx2 = (uint64_t)(uint32_t)sc.x | ((uint64_t)(uint32_t)sc.y << 32);
-                // (d_w * d_x) is exact in f32 (two f16 values): the term of vec_dot_q8_0 with one rounding
-                acc[c] = f2_fma(f2_mul(dw2, dx2), f2, acc[c]);
-            }
-            if (kb == TC_KC - 1) {
+            for (int kb = 0; kb < TP_KC; kb++) {
+                ok = mbar_spin_bounded(&tmem_full[kb], (uint32_t)step & 1u);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t r[NC];
+#pragma unroll
+                for (int c0 = 0; c0 < NC; c0 += (NC < 32 ? 16 : 32)) {
+                    if (NC < 32) tmem_ld16(tbase + (uint32_t)(kb * BN + c0), r + c0);
+                    else tmem_ld32(tbase + (uint32_t)(kb * BN + c0), r + c0);
+                }
+                tmem_ld_wait();
+                // the tile is in registers: hand the buffer back to the MMA issuer
+                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&stage_empty[s]);
+                if (lane == 0) mbar_arrive(&tmem_empty[kb]);
+                const float dw = dwp[kb * TC_M];
+                const uint64_t dw2 = f2_pack(dw, dw);
+#pragma unroll
+                for (int c = 0; c < NP; c++) {
+                    // the tile is the exact integer block sum; (d_w * d_x) is exact in f32 (two f16 values):
+                    // the term of vec_dot_q8_0 with one rounding.  xsp: d_x of two columns (the same for all lanes)
+                    acc[c] = f2_fma(f2_mul(dw2, xsp[kb * (BN / 2) + c]), f2_pack(__int2float_rn((int)r[2 * c]), __int2float_rn((int)r[2 * c + 1])), acc[c]);
+                }
             }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&stage_empty[s]);
         }
         if (ok) {
             const int row = row_tile * TC_M + row_in_tile;
@@ -623,23 +627,23 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
     } else if (warp == TP_EPI_WARPS) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            // instruction descriptor: D = s32, A = unsigned 8 bit, B = signed 8 bit, both K-major
-            const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
+            // instruction descriptor: D = s32, A and B = signed 8 bit, both K-major
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);
             for (int step = 0; step < nsteps && ok; step++) {
-                const int s = step % TP_STAGES;
-                ok = mbar_wait_bounded(&full[s], (uint32_t)(step / TP_STAGES) & 1u);
+                const int s = step & (TP_STAGES - 1);
+                ok = mbar_spin_bounded(&full[s], (uint32_t)(step / TP_STAGES) & 1u);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(smem + (uint32_t)s * L::STAGE);
                 const uint32_t b_addr = a_addr + L::A_BYTES;
-                for (int kb = 0; kb < TC_KC; kb++) {
-                    const int g = step * TC_KC + kb, buf = g % NBUF;
-                    ok = mbar_wait_bounded(&tmem_empty[buf], ((uint32_t)(g / NBUF) & 1u) ^ 1u);
+                for (int kb = 0; kb < TP_KC; kb++) {
+                    // accumulator tile kb is free once all epilogue warps have read the previous step's block kb
+                    ok = mbar_spin_bounded(&tmem_empty[kb], ((uint32_t)step & 1u) ^ 1u);
                     if (!ok) break;
                     tc_fence_after();
-                    umma_i8(tmem_base + (uint32_t)(buf * BN), umma_desc(a_addr + kb * L::A_BLOCK, TC_M * 16, 128),
+                    umma_i8(tmem_base + (uint32_t)(kb * BN), umma_desc(a_addr + kb * L::A_BLOCK, TC_M * 16, 128),
                             umma_desc(b_addr + kb * L::B_BLOCK, BN * 16, 128), idesc, 0u);
-                    umma_commit(&tmem_full[buf]);
+                    umma_commit(&tmem_full[kb]);
                 }
             }
         }
@@ -650,9 +654,9 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
             const uint8_t* asrc = pa + (size_t)row_tile * nkb * L::A_BLOCK;
             const uint8_t* dsrc = reinterpret_cast<const uint8_t*>(pd) + (size_t)row_tile * nkb * (TC_M * 4);
             const uint8_t* qsrc = qs + (size_t)col_tile * nkb * L::B_BLOCK;
-            const uint8_t* xsrc = xs + (size_t)col_tile * nkb * (BN * 8);
+            const uint8_t* xsrc = xs + (size_t)col_tile * nkb * (BN * 4);
             for (int step = 0; step < nsteps && ok; step++) {
-                const int s = step % TP_STAGES;
+                const int s = step & (TP_STAGES - 1);
                 // the stage is free when the MMAs that read it have completed (their tiles were read by the
                 // epilogue, which arrives here after the step's last block) 
                 ok = mbar_wait_bounded(&stage_empty[s], ((uint32_t)(step / TP_STAGES) & 1u) ^ 1u);
@@ -763,7 +767,7 @@ int gb_mm_q4_0_tp(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, con
     uint8_t* qs = (uint8_t*)scratch;
     uint8_t* xs = qs + (((size_t)Bp * K + 255) & ~(size_t)255);
     dim3 qgrid((unsigned)((K / 32 * 8 + 255) / 256), (unsigned)Bp);
-    quantize_q8_tp_kernel<<<qgrid, 256, 0, ctx->stream>>>(x, xd->nb[1], K, B, BN, qs, (int*)xs);
+    quantize_q8_tp_kernel<<<qgrid, 256, 0, ctx->stream>>>(x, xd->nb[1], K, B, BN, qs, (float*)xs);
     GB_LAUNCHED(ctx, "quantize_q8_tp");
     if (BN == 64) return launch_tp<64>(ctx, p, qs, xs, dst, dd->nb[1], K, N, B);
     return launch_tp<128>(ctx, p, qs, xs, dst, dd->nb[1], K, N, B);

@@ -50,6 +50,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
     return true;
 }
+// The same wait as a tight poll (no suspend hint): for hand-shakes whose latency is on the critical path.
+__device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, uint32_t parity) {
+    if (mbar_done(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_done(bar, parity)) {
+        if (clock64() - t0 > (1ll << 32)) return false;
+    }
+    return true;
+}
 // 1-D bulk copy global -> this CTA's shared memory, completing on an mbarrier.  Both addresses
 // 16-byte aligned, size a multiple of 16 bytes.  No multicast.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
