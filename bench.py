@@ -732,6 +732,7 @@ def run_ours(args):
                     "host_cpus": ncpu}
 
         extra["q6k_4096x4096_batch1"] = time_q6k(4096, 4096, 1, 32)
+        extra["q6k_head_32000x4096_batch1"] = time_q6k(32000, 4096, 1, 4)  # the output head of a Q4_0 GGUF model is stored as Q6K
         # the headline step again with the overlap of independent mat-vecs switched off: every kernel waits for the
         # kernel in front of it at entry, as if each mat-mul consumed its predecessor's result
         lib.galois_b200_set_overlap(ctx, 0)

@@ -17,6 +17,10 @@
 namespace {
 
 constexpr int Q6K_BYTES = 210;
+#ifndef GB_Q6K_UNROLL
+#define GB_Q6K_UNROLL 2
+#endif
+constexpr int Q6K_UNROLL = GB_Q6K_UNROLL;
 
 // BlockQ8K quantiser, one warp per (activation row, super-block).  qs: int8 [rows][K]; ds: f32 [rows][K/256].
 // `blocks` (optional): the same in the reference's 292-byte layout {f32 d; i8 qs[256]; i16 bsums[16]}.
@@ -133,6 +137,103 @@ __global__ void __launch_bounds__(128) mul_mat_q6k_kernel(const uint8_t* __restr
     }
 }
 
+// A 32-bit word at a 2-byte-aligned address: one aligned load, or two and a funnel shift (the second
+// word of the misaligned case lies inside the same super-block for every field read this way).
+__device__ __forceinline__ uint32_t ldg_word_a2(const uint8_t* a) {
+    if ((reinterpret_cast<uintptr_t>(a) & 2) == 0) return __ldg(reinterpret_cast<const uint32_t*>(a));
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(a - 2);
+    return __funnelshift_r(__ldg(p), __ldg(p + 1), 16);
+}
+
+// The same product with 32-bit loads and dp4a.  Eight lanes share a super-block, so a warp works on four
+// super-blocks of its row at a time: lane (sbi = lane / 8, u = lane % 8) takes 16 consecutive bytes of ql
+// (half j = u / 4, group grp = (u / 2) % 2, byte positions p0 = 16 (u % 2) .. + 15) and the matching 16
+// bytes of qh: low nibbles are elements 128 j + 32 grp + p, high nibbles the same + 64; sixteen positions
+// share one sub-block scale.  The integer per super-block is the one of the kernel above (a sum in another
+// order, exact either way) and is scaled by the same f32 product; every group of eight lanes accumulates the
+// super-blocks sb = sbi (mod 4) and the four partial sums are added at the end, so only the order of the f32
+// additions over super-blocks differs from the kernel above.
+// Needs the tensor's first byte on a 4-byte boundary (blocks inside it may sit at 2 mod 4).
+template <int NB>
+__global__ void __launch_bounds__(256) mul_mat_q6k_words_kernel(const uint8_t* __restrict__ w, int64_t nb01, int64_t nb02, int64_t nb03, int64_t ne02,
+                                                                int64_t ne03, const int8_t* __restrict__ xq, const float* __restrict__ xd,
+                                                                float* __restrict__ dst, int64_t nb1, int64_t nb2, int64_t nb3, int K, int64_t N,
+                                                                int64_t ne11, int64_t ne12, int64_t ne13) {
+    gb_pdl_entry();
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= N) return;
+    const int nsb = K >> 8;
+    const int64_t i11_0 = (int64_t)blockIdx.y * NB;
+    int64_t i12 = 0, i13 = 0, i02 = 0, i03 = 0;
+    if (gridDim.z > 1) {
+        i12 = blockIdx.z % ne12, i13 = blockIdx.z / ne12;
+        i02 = i12 / (ne12 / ne02), i03 = i13 / (ne13 / ne03);
+    }
+    const uint8_t* wrow = w + (row * nb01 + i02 * nb02 + i03 * nb03) * Q6K_BYTES;
+    const int64_t xrow0 = (i13 * ne12 + i12) * ne11 + i11_0;  // row index in the quantised activations
+    const int sbi = lane >> 3, u = lane & 7;
+    const int j = u >> 2, grp = (u >> 1) & 1, p0 = 16 * (u & 1);
+    const int ql_off = 64 * j + 32 * grp + p0, qh_off = 128 + 32 * j + p0;
+    const int sc_off = 192 + 8 * j + 2 * grp + (p0 >> 4);  // scale of the low-nibble elements; the high-nibble ones' is 4 further
+    const int y_off = 128 * j + 32 * grp + p0;              // activations of the low nibbles; the high nibbles' are 64 further
+    const int sh_lo = 2 * grp, sh_hi = sh_lo + 4;
+    float acc[NB];
+#pragma unroll
+    for (int b = 0; b < NB; b++) acc[b] = 0.0f;
+#pragma unroll Q6K_UNROLL
+    for (int sb0 = 0; sb0 < nsb; sb0 += 4) {
+        const int sb = sb0 + sbi;
+        const bool live = sb < nsb;
+        int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0}, sc_lo = 0, sc_hi = 0;
+        float dw = 0.0f;
+        if (live) {
+            const uint8_t* blk = wrow + sb * Q6K_BYTES;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t ql = ldg_word_a2(blk + ql_off + 4 * i), qh = ldg_word_a2(blk + qh_off + 4 * i);
+                const uint32_t l6 = (ql & 0x0F0F0F0Fu) | (((qh >> sh_lo) & 0x03030303u) << 4);
+                const uint32_t h6 = ((ql >> 4) & 0x0F0F0F0Fu) | (((qh >> sh_hi) & 0x03030303u) << 4);
+                // one activation row: keep the quants 0..63 and subtract 32 * (sum of the activations) below
+                lo[i] = NB == 1 ? (int)l6 : (int)__vsub4(l6, 0x20202020u);
+                hi[i] = NB == 1 ? (int)h6 : (int)__vsub4(h6, 0x20202020u);
+            }
+            sc_lo = (int)(int8_t)__ldg(blk + sc_off);
+            sc_hi = (int)(int8_t)__ldg(blk + sc_off + 4);
+            dw = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(blk + 208))));
+        }
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            if (i11_0 + b >= ne11) break;  // the same for every lane
+            int t = 0;
+            float d = 0.0f;
+            if (live) {
+                const int8_t* y = xq + (xrow0 + b) * K + sb * 256 + y_off;
+                const int4 y_lo = __ldg(reinterpret_cast<const int4*>(y)), y_hi = __ldg(reinterpret_cast<const int4*>(y + 64));
+                const int t_lo = __dp4a(lo[3], y_lo.w, __dp4a(lo[2], y_lo.z, __dp4a(lo[1], y_lo.y, __dp4a(lo[0], y_lo.x, 0))));
+                const int t_hi = __dp4a(hi[3], y_hi.w, __dp4a(hi[2], y_hi.z, __dp4a(hi[1], y_hi.y, __dp4a(hi[0], y_hi.x, 0))));
+                t = sc_lo * t_lo + sc_hi * t_hi;
+                if (NB == 1) {
+                    const int ones = 0x01010101;
+                    const int s_lo = __dp4a(ones, y_lo.w, __dp4a(ones, y_lo.z, __dp4a(ones, y_lo.y, __dp4a(ones, y_lo.x, 0))));
+                    const int s_hi = __dp4a(ones, y_hi.w, __dp4a(ones, y_hi.z, __dp4a(ones, y_hi.y, __dp4a(ones, y_hi.x, 0))));
+                    t -= 32 * (sc_lo * s_lo + sc_hi * s_hi);
+                }
+                d = __fmul_rn(xd[(xrow0 + b) * nsb + sb], dw);  // y.d * x.d.to_f32()
+            }
+            t += __shfl_xor_sync(0xffffffffu, t, 1);
+            t += __shfl_xor_sync(0xffffffffu, t, 2);
+            t += __shfl_xor_sync(0xffffffffu, t, 4);
+            acc[b] = fmaf(d, (float)t, acc[b]);  // dead groups add 0 * 0
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+        const float a1 = __shfl_sync(0xffffffffu, acc[b], 8), a2 = __shfl_sync(0xffffffffu, acc[b], 16), a3 = __shfl_sync(0xffffffffu, acc[b], 24);
+        if (lane == 0 && i11_0 + b < ne11) dst[(i11_0 + b) * nb1 + i12 * nb2 + i13 * nb3 + row] = ((acc[b] + a1) + a2) + a3;
+    }
+}
+
 // Test hook: per super-block integer sums of one weight row against one quantised activation row.
 __global__ void q6k_block_isums_kernel(const uint8_t* __restrict__ w, const int8_t* __restrict__ xq, int nsb, int32_t* __restrict__ out) {
     const int lane = threadIdx.x & 31;
@@ -159,6 +260,13 @@ template <int NB>
 int launch_q6k(galois_b200_ctx* ctx, const uint8_t* w, const galois_dim* wd, const int8_t* xq, const float* xds, const galois_dim* xd, float* dst,
                const galois_dim* dd) {
     const int64_t N = wd->ne[1];
+    if ((uintptr_t)w % 4 == 0) {
+        dim3 grid8((unsigned)((N + 7) / 8), (unsigned)((xd->ne[1] + NB - 1) / NB), (unsigned)(xd->ne[2] * xd->ne[3]));
+        gb_launch(ctx, mul_mat_q6k_words_kernel<NB>, grid8, dim3(256), 0, w, wd->nb[1], wd->nb[2], wd->nb[3], wd->ne[2], wd->ne[3], xq, xds, dst,
+                  dd->nb[1], dd->nb[2], dd->nb[3], (int)wd->ne[0], N, xd->ne[1], xd->ne[2], xd->ne[3]);
+        GB_LAUNCHED(ctx, "mul_mat_q6k_words");
+        return 0;
+    }
     dim3 grid((unsigned)((N + 3) / 4), (unsigned)((xd->ne[1] + NB - 1) / NB), (unsigned)(xd->ne[2] * xd->ne[3]));
     gb_launch(ctx, mul_mat_q6k_kernel<NB>, grid, dim3(128), 0, w, wd->nb[1], wd->nb[2], wd->nb[3], wd->ne[2], wd->ne[3], xq, xds, dst, dd->nb[1],
               dd->nb[2], dd->nb[3], (int)wd->ne[0], N, xd->ne[1], xd->ne[2], xd->ne[3]);
