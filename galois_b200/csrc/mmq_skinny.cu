@@ -51,10 +51,11 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
 // Q8_0 quantiser into MMA fragment order.  Eight threads own one (activation row, block).
 //   qfrag: [nblk][NT][32 lanes][2] u32 -- lane (g = lane / 4, t = lane % 4) of n-tile nt holds
 //          word j = quants k = 16 j + 4 t .. + 3 of activation row 8 nt + g;
-//   ds   : [nblk][8 NT] {d, bits(MAGIC_INT - 8 * sum q)} per activation row.
+//   ds   : [nblk][4 NT] {d of row 2i, d of row 2i + 1, m of row 2i, m of row 2i + 1} per pair of activation rows,
+//          m = bits(MAGIC_INT - 8 * sum q).
 // Rows >= nbatch (padding up to 8 NT) are written as zeros.
 __global__ void __launch_bounds__(256) quantize_q8_frag_kernel(const float* __restrict__ x, long long x_stride, int K, int nbatch, int NT,
-                                                               uint32_t* __restrict__ qfrag, float2* __restrict__ ds) {
+                                                               uint32_t* __restrict__ qfrag, float* __restrict__ ds) {
     gb_pdl_entry();
     const int nblk = K >> 5;
     const int bpad = 8 * NT;
@@ -82,38 +83,55 @@ __global__ void __launch_bounds__(256) quantize_q8_frag_kernel(const float* __re
     qfrag[(((long long)blk * NT + nt) * 32 + g * 4 + t) * 2 + j] = packed;
     if (sub == 0) {
         const float dr = __half2float(__float2half_rn(d));  // the f16 scale the Q8_0 block stores
-        ds[(long long)blk * bpad + b] = make_float2(dr, __int_as_float(SK_MAGIC_INT - 8 * s));
+        float* p = ds + ((long long)blk * bpad + (b & ~1)) * 2 + (b & 1);
+        p[0] = dr;
+        p[2] = __int_as_float(SK_MAGIC_INT - 8 * s);
     }
 }
 
+// Shared-memory loads at a 32-bit per-lane address plus a compile-time offset (no uniform-register base).
+// volatile: they stay behind the mbarrier wait that guards the stage.
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_b32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ float lds_f16(uint32_t addr) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(addr), "n"(OFF));
+    return __half2float(__ushort_as_half(v));
+}
+
 // One block of 16 weight rows (fragment words qa for row g, qb for row g + 8) against one n-tile of
-// activations (fragment bf, {d, m} pairs s of activation rows 2t, 2t + 1): the four integer sums of this
-// lane as exact floats.
+// activations (fragment bf, scales and correction terms s of activation rows 2t, 2t + 1): the four integer sums of this
+// lane as exact floats.  s = {d, d, m, m} of activation rows 2t, 2t + 1.
 __device__ __forceinline__ void block_isums_f(uint32_t qa, uint32_t qb, const uint2 bf, const float4 s, float (&f)[4]) {
     const uint32_t a0 = qa & 0x0F0F0F0Fu, a2 = (qa >> 4) & 0x0F0F0F0Fu;
     const uint32_t a1 = qb & 0x0F0F0F0Fu, a3 = (qb >> 4) & 0x0F0F0F0Fu;
     int c[4];
     mma_u8s8(c, a0, a1, a2, a3, bf.x, bf.y);
     // float(isum) = float(c - 8 * sum q) through the 1.5 * 2^23 trick: exact for |isum| < 2^22
-    f[0] = __int_as_float(c[0] + __float_as_int(s.y)) - SK_MAGIC;
+    f[0] = __int_as_float(c[0] + __float_as_int(s.z)) - SK_MAGIC;
     f[1] = __int_as_float(c[1] + __float_as_int(s.w)) - SK_MAGIC;
-    f[2] = __int_as_float(c[2] + __float_as_int(s.y)) - SK_MAGIC;
+    f[2] = __int_as_float(c[2] + __float_as_int(s.z)) - SK_MAGIC;
     f[3] = __int_as_float(c[3] + __float_as_int(s.w)) - SK_MAGIC;
 }
 
 // The same block against NT n-tiles, scaled (dwa, dwb: the weight rows' f16 scales) and accumulated.
 template <int NT>
 __device__ __forceinline__ void block_mma(uint32_t qa, uint32_t qb, float dwa, float dwb, const uint2 (&bf)[NT], const float4 (&sc)[NT],
-                                          float (&acc)[NT][4]) {
+                                          uint64_t (&acc)[NT][2]) {
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
         const float4 s = sc[nt];
         float f[4];
         block_isums_f(qa, qb, bf[nt], s, f);
-        acc[nt][0] = fmaf(dwa * s.x, f[0], acc[nt][0]);
-        acc[nt][1] = fmaf(dwa * s.z, f[1], acc[nt][1]);
-        acc[nt][2] = fmaf(dwb * s.x, f[2], acc[nt][2]);
-        acc[nt][3] = fmaf(dwb * s.z, f[3], acc[nt][3]);
+        // two activation rows per instruction: (d_w * d_x) is exact in f32, one rounding per fused multiply-add
+        const uint64_t dx2 = f2_pack(s.x, s.y);
+        acc[nt][0] = f2_fma(f2_mul(f2_pack(dwa, dwa), dx2), f2_pack(f[0], f[1]), acc[nt][0]);
+        acc[nt][1] = f2_fma(f2_mul(f2_pack(dwb, dwb), dx2), f2_pack(f[2], f[3]), acc[nt][1]);
     }
 }
 
@@ -133,7 +151,7 @@ __global__ void skinny_block_isums_kernel(const uint8_t* __restrict__ w, const u
     for (int i = 0; i < 32; i++) sum += q[i];
     const float m = __int_as_float(SK_MAGIC_INT - 8 * sum);
     float f[4];
-    block_isums_f(qa, qa, bf, make_float4(0.f, m, 0.f, m), f);
+    block_isums_f(qa, qa, bf, make_float4(0.f, 0.f, m, m), f);
     if (lane == 0) out[ib] = (int)f[0];
 }
 
@@ -143,17 +161,22 @@ __global__ void skinny_block_isums_kernel(const uint8_t* __restrict__ w, const u
 // paid once per group and overlaps the arithmetic of the group before.
 template <int NT, int NP, int PF>
 __device__ __forceinline__ void stage_mma(const uint8_t* ra, const uint8_t* rb, const uint2* __restrict__ qfrag,
-                                          const float4* __restrict__ ds4, int blk0, int lane, float (&acc)[NT][4]) {
+                                          const float4* __restrict__ ds4, int blk0, int lane, uint64_t (&acc)[NT][2]) {
     static_assert(NP % PF == 0, "whole groups");
     const int t = lane & 3;
+    const uint32_t sa = smem_u32(ra);
+    (void)rb;
+    // one pointer per operand stream: every load below is base + compile-time offset
+    const uint2* qf = qfrag + (long long)blk0 * (NT * 32) + lane;
+    const float4* dq = ds4 + (long long)blk0 * (NT * 4) + t;
     uint2 bf[2][2 * PF][NT];
     float4 sc[2][2 * PF][NT];
 #pragma unroll
     for (int i = 0; i < 2 * PF; i++)
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-            bf[0][i][nt] = __ldg(qfrag + ((long long)(blk0 + i) * NT + nt) * 32 + lane);
-            sc[0][i][nt] = __ldg(ds4 + ((long long)(blk0 + i) * NT + nt) * 4 + t);
+            bf[0][i][nt] = __ldg(qf + (i * NT + nt) * 32);
+            sc[0][i][nt] = __ldg(dq + (i * NT + nt) * 4);
         }
 #pragma unroll
     for (int grp = 0; grp < NP / PF; grp++) {
@@ -162,23 +185,20 @@ __device__ __forceinline__ void stage_mma(const uint8_t* ra, const uint8_t* rb, 
             for (int i = 0; i < 2 * PF; i++)
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
-                    const int blk = blk0 + 2 * PF * (grp + 1) + i;
-                    bf[(grp + 1) & 1][i][nt] = __ldg(qfrag + ((long long)blk * NT + nt) * 32 + lane);
-                    sc[(grp + 1) & 1][i][nt] = __ldg(ds4 + ((long long)blk * NT + nt) * 4 + t);
+                    const int rel = 2 * PF * (grp + 1) + i;
+                    bf[(grp + 1) & 1][i][nt] = __ldg(qf + (rel * NT + nt) * 32);
+                    sc[(grp + 1) & 1][i][nt] = __ldg(dq + (rel * NT + nt) * 4);
                 }
         }
 #pragma unroll
         for (int q = 0; q < PF; q++) {
             const int p = grp * PF + q;
             // a block pair is nine aligned words: {d0 | qs0[0:2]}, qs0[2:14], {qs0[14:16] | d1}, qs1[0:16]
-            const uint32_t* ta = reinterpret_cast<const uint32_t*>(ra + p * 36);
-            const uint32_t* tb = reinterpret_cast<const uint32_t*>(rb + p * 36);
-            const uint32_t a_lo = ta[t], a_hi = ta[t + 1], a_1 = ta[5 + t];
-            const uint32_t b_lo = tb[t], b_hi = tb[t + 1], b_1 = tb[5 + t];
-            const float dwa0 = __half2float(*reinterpret_cast<const __half*>(ra + p * 36));
-            const float dwa1 = __half2float(*reinterpret_cast<const __half*>(ra + p * 36 + 18));
-            const float dwb0 = __half2float(*reinterpret_cast<const __half*>(rb + p * 36));
-            const float dwb1 = __half2float(*reinterpret_cast<const __half*>(rb + p * 36 + 18));
+            const uint32_t pa = sa + p * 36, pb = pa + 8 * SK_PITCH;  // this pair in rows g and g + 8
+            const uint32_t a_lo = lds_b32<0>(pa + 4 * t), a_hi = lds_b32<4>(pa + 4 * t), a_1 = lds_b32<20>(pa + 4 * t);
+            const uint32_t b_lo = lds_b32<0>(pb + 4 * t), b_hi = lds_b32<4>(pb + 4 * t), b_1 = lds_b32<20>(pb + 4 * t);
+            const float dwa0 = lds_f16<0>(pa), dwa1 = lds_f16<18>(pa);
+            const float dwb0 = lds_f16<0>(pb), dwb1 = lds_f16<18>(pb);
             block_mma<NT>(__funnelshift_r(a_lo, a_hi, 16), __funnelshift_r(b_lo, b_hi, 16), dwa0, dwb0, bf[grp & 1][2 * q], sc[grp & 1][2 * q], acc);
             block_mma<NT>(a_1, b_1, dwa1, dwb1, bf[grp & 1][2 * q + 1], sc[grp & 1][2 * q + 1], acc);
         }
@@ -239,11 +259,9 @@ __global__ void __launch_bounds__(SK_THREADS, 2) mmq_skinny_kernel(const uint8_t
     bool ok = true;
     int idx = 0;
     for (int j = 0; j < my_tiles; j++) {
-        float acc[NT][4];
+        uint64_t acc[NT][2];  // {row g: activation rows 2t, 2t + 1}, {row g + 8: the same}, two f32 each
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
+        for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = 0ull;
 
         for (int q = 0; q < my_steps && ok; q++, idx++) {
             const int s = idx % stages;
@@ -267,7 +285,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2) mmq_skinny_kernel(const uint8_t
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-            for (int i = 0; i < 4; i++) mine[(nt * 4 + i) * 32 + lane] = acc[nt][i];
+            for (int i = 0; i < 4; i++) mine[(nt * 4 + i) * 32 + lane] = __uint_as_float((uint32_t)(acc[nt][i >> 1] >> (32 * (i & 1))));
         __syncthreads();
         const int tile = (int)blockIdx.x + j * (int)gridDim.x;
         for (int o = threadIdx.x; o < NT * 128; o += SK_THREADS) {
@@ -378,7 +396,7 @@ int gb_mmq_skinny(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, con
         }
         uint8_t* base = reinterpret_cast<uint8_t*>(scratch) + (size_t)(b0 / 16) * pass_scratch_bytes((size_t)nblk);
         uint32_t* qfrag = reinterpret_cast<uint32_t*>(base);
-        float2* ds = reinterpret_cast<float2*>(base + (((size_t)nblk * p.nt * 256 + 255) & ~(size_t)255));
+        float* ds = reinterpret_cast<float*>(base + (((size_t)nblk * p.nt * 256 + 255) & ~(size_t)255));
         const float* xp = x + (long long)b0 * xd->nb[1];
         float* dp = dst + (long long)b0 * dd->nb[1];
         const long long items = (long long)nblk * 8 * p.nt * 8;  // eight threads per (block, padded activation row)

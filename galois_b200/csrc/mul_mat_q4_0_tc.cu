@@ -510,21 +510,6 @@ __global__ void __launch_bounds__(256) quantize_q8_tp_kernel(const float* __rest
     }
 }
 
-// Two f32 in one 64-bit register (low word first).
-__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
-    return (uint64_t)__float_as_uint(lo) | ((uint64_t)__float_as_uint(hi) << 32);
-}
-__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-
 template <int BN>
 __global__ void __launch_bounds__(TP_THREADS, 1)
     mm_q4_0_tp_kernel(const uint8_t* __restrict__ pa, const float* __restrict__ pd, const uint8_t* __restrict__ qs, const uint8_t* __restrict__ xs,
