@@ -181,7 +181,7 @@ int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galo
 /* One-time repack of a Q4_0 weight at upload, for the large-batch (prefill) mat-mul.  In the reference the
  * upload is a plain copy of the 18-byte blocks (CudaDevice::from_cpu_storage, src/cuda.rs:231-239) and its
  * kernels re-decode them on every call.  This call keeps, inside the context and keyed by the device address
- * `w`, a second copy of the weight with the nibbles already expanded to unsigned bytes in the tensor-core
+ * `w`, a second copy of the weight with the nibbles already expanded to signed bytes (q - 8) in the tensor-core
  * operand order and the block scales as f32 (1.125 bytes per weight on top of the caller's 0.5625).  The op
  * API does not change: galois_b200_mul_mat_q4_0_f32 looks the address up and, when the batch is large
  * enough for the tensor-core kernel, streams the prepared copy with bulk copies instead of unpacking nibbles
