@@ -484,6 +484,7 @@ __global__ void __launch_bounds__(256) repack_q4_0_tc_kernel(const uint8_t* __re
 // xs[col tile][block][BN] f32 d.
 __global__ void __launch_bounds__(256) quantize_q8_tp_kernel(const float* __restrict__ x, int64_t x_stride, int K, int B, int BN,
                                                              uint8_t* __restrict__ qs, float* __restrict__ xs) {
+    gb_pdl_entry();
     const int nkb = K >> 5;
     const int sub = threadIdx.x & 7;
     const int kb = (blockIdx.x * 256 + threadIdx.x) >> 3;
@@ -640,6 +641,9 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
             const uint8_t* dsrc = reinterpret_cast<const uint8_t*>(pd) + (size_t)row_tile * nkb * (TC_M * 4);
             const uint8_t* qsrc = qs + (size_t)col_tile * nkb * L::B_BLOCK;
             const uint8_t* xsrc = xs + (size_t)col_tile * nkb * (BN * 4);
+            // launched with programmatic stream serialization: barriers, TMEM and the roles above are set up
+            // while the quantiser in front of this kernel finishes; nothing is read from global memory before here
+            pdl_wait();
             for (int step = 0; step < nsteps && ok; step++) {
                 const int s = step & (TP_STAGES - 1);
                 // the stage is free when the MMAs that read it have completed (their tiles were read by the
@@ -735,8 +739,8 @@ bool gb_mm_tc_prepared(galois_b200_ctx* ctx, const void* w, const galois_dim* wd
 template <int BN>
 static int launch_tp(galois_b200_ctx* ctx, const gb_weight_pack* p, const uint8_t* qs, const uint8_t* xs, float* dst, int64_t nb1, int K, int N, int B) {
     dim3 grid((unsigned)((N + TC_M - 1) / TC_M), (unsigned)((B + BN - 1) / BN));
-    mm_q4_0_tp_kernel<BN><<<grid, TP_THREADS, tp_smem<BN>::TOTAL, ctx->stream>>>((const uint8_t*)p->pa, (const float*)p->pd, qs, xs, dst, nb1, K, N, B,
-                                                                                ctx->dev_status);
+    GB_CUDA(ctx, gb_launch(ctx, mm_q4_0_tp_kernel<BN>, grid, dim3(TP_THREADS), tp_smem<BN>::TOTAL, (const uint8_t*)p->pa, (const float*)p->pd, qs, xs,
+                           dst, nb1, K, N, B, ctx->dev_status));
     GB_LAUNCHED(ctx, "mm_q4_0_tp");
     return 0;
 }
@@ -752,7 +756,7 @@ int gb_mm_q4_0_tp(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, con
     uint8_t* qs = (uint8_t*)scratch;
     uint8_t* xs = qs + (((size_t)Bp * K + 255) & ~(size_t)255);
     dim3 qgrid((unsigned)((K / 32 * 8 + 255) / 256), (unsigned)Bp);
-    quantize_q8_tp_kernel<<<qgrid, 256, 0, ctx->stream>>>(x, xd->nb[1], K, B, BN, qs, (float*)xs);
+    GB_CUDA(ctx, gb_launch(ctx, quantize_q8_tp_kernel, qgrid, dim3(256), 0, x, xd->nb[1], K, B, BN, qs, (float*)xs));
     GB_LAUNCHED(ctx, "quantize_q8_tp");
     if (BN == 64) return launch_tp<64>(ctx, p, qs, xs, dst, dd->nb[1], K, N, B);
     return launch_tp<128>(ctx, p, qs, xs, dst, dd->nb[1], K, N, B);
