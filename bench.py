@@ -499,7 +499,7 @@ def run_ours(args):
         # config 4: one decode step of a LLaMA-7B-shaped layer built from galois ops, 4 distinct layers in rotation
         from galois_b200.decode import DecodeLayer, LayerShape, weight_shapes
         shp = LayerShape()
-        def measure_layer(fused_layer):
+        def measure_layer(fused_layer, attention_kernel=False):
             layers = []
             for li in range(4):
                 wq4 = {name: make_q4_0(n, k, 31000 + 100 * li + i, device).cpu().numpy()
@@ -509,7 +509,7 @@ def run_ours(args):
                 kc = torch.randn(shp.heads, shp.ctx, shp.head_dim, generator=gk, device=device).to(torch.float16).cpu().numpy()
                 vc = torch.randn(shp.heads, shp.head_dim, shp.ctx, generator=gk, device=device).to(torch.float16).cpu().numpy()
                 layers.append(DecodeLayer(dev, shp, wq4, np.ones(shp.hidden, np.float32), np.ones(shp.hidden, np.float32), kc, vc,
-                                          fused=fused_layer))
+                                          fused=fused_layer, attention_kernel=attention_kernel))
             G = gb.Device.Gpu(dev)
             xin = gb.Tensor.from_numpy(xs[HIDDEN][:1].cpu().numpy(), gb.GGmlType.F32, G)
             post = gb.Tensor.from_numpy(np.array([shp.ctx - 1], np.int32), gb.GGmlType.I32, G)
@@ -544,6 +544,8 @@ def run_ours(args):
 
         extra["decode_layer"] = measure_layer(False)       # the op-by-op sequence a galois caller writes
         extra["decode_layer_fused"] = measure_layer(True)  # stacked QKV / gate-up weights + two-op fusions, same numbers
+        # ... and with rope, cache appends, scores, soft_max and context as one launch (galois_b200_decode_attention_f32)
+        extra["decode_layer_one_attention_launch"] = measure_layer(True, True)
         # the same 22-op layers as ONE persistent cooperative kernel per token (galois_b200_decode_layers_f32)
         def measure_stack(nl):
             from galois_b200.decode import DecodeStack

@@ -102,6 +102,7 @@ SIGNATURES = {
     "galois_b200_get_rows_q4_0_f32": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_decode_workspace_bytes": ([_P, C.POINTER(GaloisDecodeShape), C.POINTER(_SZ)], _I),
     "galois_b200_decode_layers_f32": ([_P, C.POINTER(GaloisDecodeShape), C.POINTER(GaloisDecodeLayer), _I, _P, _P, _P, _P, _SZ], _I),
+    "galois_b200_decode_attention_f32": ([_P, C.POINTER(GaloisDecodeShape), C.POINTER(GaloisDecodeLayer), _P, _P, _P, _P, _SZ], _I),
     "galois_b200_shard_rows": ([_I64, _I, _I, C.POINTER(_I64), C.POINTER(_I64)], _I),
     "galois_b200_ipc_export": ([_P, _P, C.c_char_p], _I),
     "galois_b200_ipc_import": ([_P, C.c_char_p, C.POINTER(_P)], _I),

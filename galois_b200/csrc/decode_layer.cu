@@ -48,6 +48,7 @@ constexpr int DL_W_COUNT = 16, DL_W_EXIT = 17, DL_W_ABORT = 18;
 struct dl_params {
     int hidden, heads, head_dim, ffn, ctx, n_layers;
     int plan_h, plan_f;   // row plan of K = hidden / K = ffn: 0 = 32 segments of 4 block pairs per pass (split), 1 = 3 passes of 2 pairs
+    int phase_lo, phase_hi;  // the phases to run: 0..5 = whole layers; 1..2 = the attention of one layer (x = q | k | v, out = context)
     float eps, theta_scale, freq_scale, kq_scale;
     const float* x;       // [hidden]
     const int32_t* pos;   // the token's position (one value)
@@ -642,10 +643,17 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
     __syncthreads();
     const dl_geom& g = S->geom;
     DL_PROF(0);
-    // weights are nobody's output: the first copies leave before anything else happens
-    while (st.ahead < g.count[0][warp] && st.issued - st.consumed < (uint32_t)DL_NSLOT) dl_issue(st, S, 1, 0, st.ahead++, lane);
+    const int plo = P.phase_lo, phi = P.phase_hi;
+    // the first copies leave before anything else happens (weights are nobody's output; the cache row this
+    // step appends is never read from the ring)
+    while (st.ahead < g.count[plo][warp] && st.issued - st.consumed < (uint32_t)DL_NSLOT) dl_issue(st, S, 1, plo, st.ahead++, lane);
 
-    const dl_ws W = dl_carve(P.ws, H, P.heads, ctx, F);
+    dl_ws W = dl_carve(P.ws, H, P.heads, ctx, F);
+    if (plo == 1) {
+        // attention only: q | k | v come from the caller, the context goes to the caller
+        W.qkv = const_cast<float*>(P.x);
+        W.ctxv = P.out;
+    }
     const int pos = __ldg(P.pos);
     const int rpc_h = g.rpc_h, rpc_f = g.rpc_f;
     const int VT = min(1024, max(32, (((ctx + 3) / 4 + 31) / 32) * 32));  // row_threads(ctx) of the one-op soft_max
@@ -670,7 +678,7 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
         float* xout = l == P.n_layers - 1 ? P.out : ((l & 1) ? W.xb : W.xa);
 
         // ---- phase 0: rms_norm * gain -> Q8_0 -> q | k | v
-        {
+        if (plo == 0) {
             const float scale = gb_rms_scale(dl_row_sumsq(xin, H, S->red), H, P.eps);
             dl_quantize(P.plan_h, S, H, DL_ACT_RMS_GAIN, xin, L.attn_norm, scale, nullptr);
             __syncthreads();
@@ -678,9 +686,9 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
             if (threadIdx.x == 0) S->prof_base = l == 1 ? 320 : 0;
             __syncthreads();
             ok = dl_gemv_phase<4, true, 1>(st, S, 0, 1, 0, H, rpc_h, W.qkv, nullptr, lane);
+            if (!ok) dl_give_up(words, S, lane);
+            if (!dl_grid_barrier(words, bar++, S)) return;
         }
-        if (!ok) dl_give_up(words, S, lane);
-        if (!dl_grid_barrier(words, bar++, S)) return;
 
         // ---- phase 1: rope, cache appends, scores.  The CTAs of a head rope that head's query; the first of them
         // also ropes its key and appends key and value to the caches.
@@ -805,13 +813,14 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
                     }
                 }
                 dl_pop(st);
-                dl_refill(st, S, 2, 3, 0, n, lane);
+                dl_refill(st, S, 2, 3, phi > 2 ? 0 : -1, n, lane);
                 acc = gb_warp_sum(acc);
                 if (lane == 0) W.ctxv[c] = acc;
             }
-            if (ok) dl_refill(st, S, 2, 3, 0, n, lane);
+            if (ok) dl_refill(st, S, 2, 3, phi > 2 ? 0 : -1, n, lane);
         }
         if (!ok) dl_give_up(words, S, lane);
+        if (phi == 2) break;
         if (!dl_grid_barrier(words, bar++, S)) return;
 
         // ---- phase 3: context -> Q8_0 -> Wo rows, + x -> x2
@@ -907,10 +916,9 @@ extern "C" int galois_b200_decode_workspace_bytes(galois_b200_ctx* ctx, const ga
     return 0;
 }
 
-extern "C" int galois_b200_decode_layers_f32(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, const galois_b200_decode_layer* layers,
-                                             int n_layers, const float* x, const int32_t* pos, float* out, void* workspace,
-                                             size_t workspace_bytes) {
-    GB_CHECK_CTX(ctx);
+// Phases plo..phi of the kernel: 0..5 = whole layers, 1..2 = the attention of one layer.
+static int dl_launch(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, const galois_b200_decode_layer* layers, int n_layers, const float* x,
+                     const int32_t* pos, float* out, void* workspace, size_t workspace_bytes, int plo, int phi) {
     dl_params P;
     memset(&P, 0, sizeof(P));
     int rc = dl_check_shape(ctx, shape, &P.plan_h, &P.plan_f);
@@ -924,8 +932,10 @@ extern "C" int galois_b200_decode_layers_f32(galois_b200_ctx* ctx, const galois_
         return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "decode_layers: x, out and the workspace must be 16-byte aligned");
     for (int l = 0; l < n_layers; l++) {
         const galois_b200_decode_layer& L = layers[l];
-        const void* ptrs[] = {L.wq, L.wk, L.wv, L.wo, L.w_gate, L.w_up, L.w_down, L.attn_norm, L.ffn_norm, L.k_cache, L.v_cache};
-        for (const void* q : ptrs) {
+        const void* all[] = {L.k_cache, L.v_cache, L.wq, L.wk, L.wv, L.wo, L.w_gate, L.w_up, L.w_down, L.attn_norm, L.ffn_norm};
+        const int nptr = plo == 1 ? 2 : 11;  // the attention phases touch the caches only
+        for (int i = 0; i < nptr; i++) {
+            const void* q = all[i];
             if (!q) return gb_fail(ctx, GALOIS_B200_E_BADARG, "decode_layers: null pointer in layer %d", l);
             if ((uintptr_t)q % 16) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "decode_layers: layer %d holds a pointer that is not 16-byte aligned", l);
         }
@@ -933,6 +943,7 @@ extern "C" int galois_b200_decode_layers_f32(galois_b200_ctx* ctx, const galois_
     }
     P.hidden = shape->hidden, P.heads = shape->heads, P.head_dim = shape->head_dim, P.ffn = shape->ffn, P.ctx = shape->ctx;
     P.n_layers = n_layers;
+    P.phase_lo = plo, P.phase_hi = phi;
     P.eps = shape->eps;
     P.theta_scale = powf(shape->rope_freq_base, -2.0f / (float)shape->head_dim);  // libm powf on the host, as the CPU path does (src/op.rs:2697)
     P.freq_scale = shape->rope_freq_scale;
@@ -944,8 +955,21 @@ extern "C" int galois_b200_decode_layers_f32(galois_b200_ctx* ctx, const galois_
     void* args[] = {&P};
     GB_CUDA(ctx, cudaLaunchCooperativeKernel((const void*)decode_layers_kernel, dim3((unsigned)ctx->sm_count), dim3(DL_THREADS), args, dl_smem_bytes(),
                                              ctx->stream));
-    GB_LAUNCHED(ctx, "decode_layers");
+    GB_LAUNCHED(ctx, plo == 1 ? "decode_attention" : "decode_layers");
     return 0;
+}
+
+extern "C" int galois_b200_decode_layers_f32(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, const galois_b200_decode_layer* layers,
+                                             int n_layers, const float* x, const int32_t* pos, float* out, void* workspace,
+                                             size_t workspace_bytes) {
+    GB_CHECK_CTX(ctx);
+    return dl_launch(ctx, shape, layers, n_layers, x, pos, out, workspace, workspace_bytes, 0, 5);
+}
+
+extern "C" int galois_b200_decode_attention_f32(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, const galois_b200_decode_layer* layer,
+                                                const float* qkv, const int32_t* pos, float* context, void* workspace, size_t workspace_bytes) {
+    GB_CHECK_CTX(ctx);
+    return dl_launch(ctx, shape, layer, 1, qkv, pos, context, workspace, workspace_bytes, 1, 2);
 }
 
 #ifdef GB_DL_PROF

@@ -53,12 +53,17 @@ class DecodeLayer:
     q and k; rms_norm + gain and silu + gate product run inside the mat-mul that consumes them, the
     residual sums inside the mat-mul that produces their other operand (``galois_matmul_fused``).  Rows
     of a mat-mul are independent and the fusions round like the op pairs, so both variants give
-    the same numbers bit for bit."""
+    the same numbers bit for bit.
+    ``fused=True, attention_kernel=True``: 5 kernels.  Rope, the two cache appends, the scores, the masked
+    soft_max and the context product run as ONE launch (``galois_b200_decode_attention_f32``, the attention
+    phases of the persistent decode kernel), again the same numbers bit for bit."""
 
     def __init__(self, dev, shape: LayerShape, weights: dict, attn_norm: np.ndarray, ffn_norm: np.ndarray,
-                 k_cache: np.ndarray, v_cache: np.ndarray, fused: bool = False):
+                 k_cache: np.ndarray, v_cache: np.ndarray, fused: bool = False, attention_kernel: bool = False):
         s, G = shape, Device.Gpu(dev)
-        self.shape, self.dev, self.fused = s, dev, fused
+        if attention_kernel and not fused:
+            raise ValueError("attention_kernel needs fused=True")
+        self.shape, self.dev, self.fused, self.attention_kernel = s, dev, fused, attention_kernel
         self.w = {}
         for name, (n, k) in weight_shapes(s).items():
             if fused and name in ("wq", "wk", "wv", "w_gate", "w_up"):
@@ -87,6 +92,19 @@ class DecodeLayer:
         self.d, self.out = z(s.hidden, 1), z(s.hidden, 1)
         self.rope = RopeCustomOption(n_dims=s.head_dim, mode=0, n_ctx=s.ctx, freq_base=s.rope_theta, freq_scale=1.0)
         self.scale = 1.0 / math.sqrt(s.head_dim)
+        if attention_kernel:
+            import ctypes as C
+
+            from ._lib import GaloisDecodeLayer, GaloisDecodeShape, lib
+            from .tensor import _check
+
+            self.c_shape = GaloisDecodeShape(s.hidden, s.heads, s.head_dim, s.ffn, s.ctx, s.eps, s.rope_theta, 1.0)
+            self.c_layer = GaloisDecodeLayer()
+            self.c_layer.k_cache, self.c_layer.v_cache = self.k_cache.data_ptr(), self.v_cache.data_ptr()
+            need = C.c_size_t()
+            _check(dev.ctx, lib.galois_b200_decode_workspace_bytes(dev.ctx, C.byref(self.c_shape), C.byref(need)), "decode_workspace_bytes")
+            self.ws_bytes = need.value
+            self.ws = Tensor.zeros((need.value // 4,), GGmlType.F32, G)
 
     def step(self, x: Tensor, pos: Tensor, position: int) -> Tensor:
         """x: f32 {hidden, 1}; pos: i32 {1} holding `position` (the row of the caches to fill)."""
@@ -138,6 +156,8 @@ class DecodeLayer:
         # attention block
         # rms_norm + gain run where the GEMV quantises its input; rows [0, H) = q, [H, 2H) = k, [2H, 3H) = v
         galois_matmul_fused(self.w["wqkv"], x, self.qkv, rms_gain=self.attn_norm, eps=s.eps)
+        if self.attention_kernel:
+            return self._step_tail(x, self._attention_one_launch(pos))
         qk3 = self.qkv.view((hd, 2 * nh, 1), (1, hd, hd * 2 * nh, hd * 2 * nh))
         galois_rope_custom(self.rope, qk3, pos, self.qkr)  # heads 0..nh-1 of q, then of k
         k_src = self.qkr.view((hd, 1, nh), (1, hd, hd, hd * nh), offset=H)
@@ -151,7 +171,23 @@ class DecodeLayer:
         pr = self.probs.view((ctx, nh, 1), (1, ctx, ctx * nh, ctx * nh))
         galois_soft_max_ext(sc, pr, self.scale, pos)
         galois_matmul(self.v_cache, self.probs, self.ctxv)
-        ctx_flat = self.ctxv.view((H, 1), (1, H, H, H))
+        return self._step_tail(x, self.ctxv.view((H, 1), (1, H, H, H)))
+
+    def _attention_one_launch(self, pos: Tensor) -> Tensor:
+        import ctypes as C
+
+        from ._lib import lib
+        from .tensor import _check
+
+        H = self.shape.hidden
+        rc = lib.galois_b200_decode_attention_f32(self.dev.ctx, C.byref(self.c_shape), C.byref(self.c_layer), C.c_void_p(self.qkv.data_ptr()),
+                                                  C.c_void_p(pos.data_ptr()), C.c_void_p(self.ctxv.data_ptr()), C.c_void_p(self.ws.data_ptr()),
+                                                  self.ws_bytes)
+        _check(self.dev.ctx, rc, "galois_b200_decode_attention_f32")
+        return self.ctxv.view((H, 1), (1, H, H, H))
+
+    def _step_tail(self, x: Tensor, ctx_flat: Tensor) -> Tensor:
+        s = self.shape
         galois_matmul_add(self.w["wo"], ctx_flat, x, self.x2)  # x2 = x + Wo ctx
         # feed-forward block (SwiGLU)
         # rows [0, ffn) = gate, [ffn, 2 ffn) = up

@@ -241,6 +241,32 @@ def test_persistent_kernel_equals_op_by_op_layers(dev, oracle, hidden, heads, ff
         assert np.array_equal(a.v_cache.to_numpy().view(np.uint16), b.v_cache.to_numpy().view(np.uint16))
 
 
+@pytest.mark.parametrize("hidden,heads,ffn,ctx,position", [(512, 4, 1024, 256, 17), (512, 4, 1024, 256, 255), (4096, 32, 11008, 2048, 2047),
+                                                           (4096, 32, 11008, 2048, 0), (1024, 8, 2048, 512, 300)])
+def test_layer_with_one_attention_launch_equals_op_by_op_layer(dev, oracle, hidden, heads, ffn, ctx, position):
+    """DecodeLayer(fused=True, attention_kernel=True): 5 launches (stacked q|k|v mat-vec, galois_b200_decode_attention_f32,
+    Wo, gate|up, down) give the bits of the 22-op layer: the output row and both caches, step after step."""
+    import galois_b200 as gb
+    from galois_b200.decode import DecodeLayer, LayerShape
+
+    s = LayerShape(hidden=hidden, heads=heads, head_dim=hidden // heads, ffn=ffn, ctx=ctx)
+    G = gb.Device.Gpu(dev)
+    wq4, attn_norm, ffn_norm, k_cache, v_cache, x = make_layer_inputs(oracle, s, 5100)
+    kc, vc = k_cache.view(np.float16), v_cache.view(np.float16)
+    ref = DecodeLayer(dev, s, wq4, attn_norm, ffn_norm, kc, vc)
+    one = DecodeLayer(dev, s, wq4, attn_norm, ffn_norm, kc, vc, fused=True, attention_kernel=True)
+    xt = gb.Tensor.from_numpy(x, gb.GGmlType.F32, G)
+    for step, p in enumerate([position, min(position + 1, ctx - 1)]):  # the second step reads what the first appended
+        pt = gb.Tensor.from_numpy(np.array([p], np.int32), gb.GGmlType.I32, G)
+        want = ref.step(xt, pt, p).to_numpy()
+        l0 = dev.launch_count()
+        got = one.step(xt, pt, p).to_numpy()
+        assert dev.launch_count() - l0 == 5
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), step
+        assert np.array_equal(ref.k_cache.to_numpy().view(np.uint16), one.k_cache.to_numpy().view(np.uint16))
+        assert np.array_equal(ref.v_cache.to_numpy().view(np.uint16), one.v_cache.to_numpy().view(np.uint16))
+
+
 def test_persistent_kernel_rejects_what_it_does_not_hold(dev, oracle):
     import ctypes as C
 
