@@ -348,13 +348,17 @@ int gb_validate_mul_mat(galois_b200_ctx* ctx, const void* w, const galois_dim* w
 // the tcgen05 kernel (one 128 x 128 output tile per CTA, whole waves of CTAs) apply; the choice follows
 // a cost model fitted to measurements on a B200: a skinny pass costs max(6.8 us, weight bytes at
 // 1.6 TB/s) (passes after the first read the weights from L2), a wave of tensor-core tiles 0.68 us
-// per 32-element block of K.
-static bool skinny_beats_tc(const galois_b200_ctx* ctx, const galois_dim* wd, const galois_dim* xd) {
+// per 32-element block of K; on a weight prepared at upload 0.36 us (128-column tiles) or 0.20 us (64-column
+// tiles, up to 64 activation rows) plus 3.5 us for the quantiser in front of it.
+static bool skinny_beats_tc(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const galois_dim* xd) {
     const double K = (double)wd->ne[0], N = (double)wd->ne[1], B = (double)xd->ne[1];
     const double pass_us = fmax(6.8, N * (K / 32.0) * 18.0 / 1.6e6);
     const double skinny_us = ceil(B / 16.0) * pass_us;
-    const double tiles = ceil(N / 128.0) * ceil(B / 128.0);
-    const double tc_us = ceil(tiles / (double)ctx->sm_count) * (K / 32.0) * 0.68;
+    const bool prepared = gb_mm_tc_prepared(const_cast<galois_b200_ctx*>(ctx), w, wd);
+    const double bn = B <= 64.0 ? 64.0 : 128.0;
+    const double tiles = ceil(N / 128.0) * ceil(B / bn);
+    const double per_block = !prepared ? 0.68 : (bn == 64.0 ? 0.20 : 0.36);
+    const double tc_us = ceil(tiles / (double)ctx->sm_count) * (K / 32.0) * per_block + (prepared ? 3.5 : 0.0);
     return skinny_us <= tc_us;
 }
 
@@ -369,7 +373,7 @@ int gb_choose_mul_mat_variant(const galois_b200_ctx* ctx, const void* w, const g
     // one activation row: dp4a GEMV; 2..16 rows: mma.sync skinny kernel; 17..192: whichever the cost model
     // prefers; more: tcgen05 GEMM
     if (gemv_ok && xd->ne[1] < GB_SKINNY_MIN_BATCH) return 2;
-    if (skinny_ok && (!tc_ok || xd->ne[1] <= 16 || skinny_beats_tc(ctx, wd, xd))) return 4;
+    if (skinny_ok && (!tc_ok || xd->ne[1] <= 16 || skinny_beats_tc(ctx, w, wd, xd))) return 4;
     if (tc_ok && xd->ne[1] >= GB_TC_MIN_BATCH) return 3;
     return gemv_ok ? 2 : 1;
 }

@@ -87,7 +87,6 @@ __device__ __forceinline__ unsigned dl_ld_acquire(const int* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ float ldcg_f(const float* p) { return __ldcg(p); }
 
 struct dl_geom {
     int rpc_h, rpc_f;                 // rows per chunk of a K = hidden / K = ffn weight
