@@ -544,8 +544,8 @@ def run_ours(args):
 
         extra["decode_layer"] = measure_layer(False)       # the op-by-op sequence a galois caller writes
         extra["decode_layer_fused"] = measure_layer(True)  # stacked QKV / gate-up weights + two-op fusions, same numbers
-        # ... and with rope, cache appends, scores, soft_max and context as one launch (galois_b200_decode_attention_f32)
-        extra["decode_layer_one_attention_launch"] = measure_layer(True, True)
+        # ... and with rope + cache appends + scores, and soft_max + context, as two launches (galois_b200_decode_attention_f32)
+        extra["decode_layer_attention_kernels"] = measure_layer(True, True)
         # the same 22-op layers as ONE persistent cooperative kernel per token (galois_b200_decode_layers_f32)
         def measure_stack(nl):
             from galois_b200.decode import DecodeStack

@@ -48,7 +48,6 @@ constexpr int DL_W_COUNT = 16, DL_W_EXIT = 17, DL_W_ABORT = 18;
 struct dl_params {
     int hidden, heads, head_dim, ffn, ctx, n_layers;
     int plan_h, plan_f;   // row plan of K = hidden / K = ffn: 0 = 32 segments of 4 block pairs per pass (split), 1 = 3 passes of 2 pairs
-    int phase_lo, phase_hi;  // the phases to run: 0..5 = whole layers; 1..2 = the attention of one layer (x = q | k | v, out = context)
     float eps, theta_scale, freq_scale, kq_scale;
     const float* x;       // [hidden]
     const int32_t* pos;   // the token's position (one value)
@@ -507,7 +506,8 @@ __device__ __forceinline__ void dl_rope_pair(float x0, float x1, float c, float 
 // elements of the virtual threads t, t + 256, ...  Returns false (and zero-fills) when every column is
 // masked, like the one-op kernel.
 constexpr int DL_SM_MAXJ = 3072 / DL_THREADS;  // elements per thread (ctx <= 3072)
-__device__ __noinline__ bool dl_soft_max_row(dl_smem* S, const float* __restrict__ xr, int nc, int limit, float scale, int VT,
+template <typename SM>
+__device__ __noinline__ bool dl_soft_max_row(SM* S, const float* __restrict__ xr, int nc, int limit, float scale, int VT,
                                                 const uint16_t* __restrict__ exp_lut) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nvw = VT >> 5;  // virtual warps
@@ -642,17 +642,10 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
     __syncthreads();
     const dl_geom& g = S->geom;
     DL_PROF(0);
-    const int plo = P.phase_lo, phi = P.phase_hi;
-    // the first copies leave before anything else happens (weights are nobody's output; the cache row this
-    // step appends is never read from the ring)
-    while (st.ahead < g.count[plo][warp] && st.issued - st.consumed < (uint32_t)DL_NSLOT) dl_issue(st, S, 1, plo, st.ahead++, lane);
+    // weights are nobody's output: the first copies leave before anything else happens
+    while (st.ahead < g.count[0][warp] && st.issued - st.consumed < (uint32_t)DL_NSLOT) dl_issue(st, S, 1, 0, st.ahead++, lane);
 
-    dl_ws W = dl_carve(P.ws, H, P.heads, ctx, F);
-    if (plo == 1) {
-        // attention only: q | k | v come from the caller, the context goes to the caller
-        W.qkv = const_cast<float*>(P.x);
-        W.ctxv = P.out;
-    }
+    const dl_ws W = dl_carve(P.ws, H, P.heads, ctx, F);
     const int pos = __ldg(P.pos);
     const int rpc_h = g.rpc_h, rpc_f = g.rpc_f;
     const int VT = min(1024, max(32, (((ctx + 3) / 4 + 31) / 32) * 32));  // row_threads(ctx) of the one-op soft_max
@@ -677,7 +670,7 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
         float* xout = l == P.n_layers - 1 ? P.out : ((l & 1) ? W.xb : W.xa);
 
         // ---- phase 0: rms_norm * gain -> Q8_0 -> q | k | v
-        if (plo == 0) {
+        {
             const float scale = gb_rms_scale(dl_row_sumsq(xin, H, S->red), H, P.eps);
             dl_quantize(P.plan_h, S, H, DL_ACT_RMS_GAIN, xin, L.attn_norm, scale, nullptr);
             __syncthreads();
@@ -685,9 +678,9 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
             if (threadIdx.x == 0) S->prof_base = l == 1 ? 320 : 0;
             __syncthreads();
             ok = dl_gemv_phase<4, true, 1>(st, S, 0, 1, 0, H, rpc_h, W.qkv, nullptr, lane);
-            if (!ok) dl_give_up(words, S, lane);
-            if (!dl_grid_barrier(words, bar++, S)) return;
         }
+        if (!ok) dl_give_up(words, S, lane);
+        if (!dl_grid_barrier(words, bar++, S)) return;
 
         // ---- phase 1: rope, cache appends, scores.  The CTAs of a head rope that head's query; the first of them
         // also ropes its key and appends key and value to the caches.
@@ -812,14 +805,13 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
                     }
                 }
                 dl_pop(st);
-                dl_refill(st, S, 2, 3, phi > 2 ? 0 : -1, n, lane);
+                dl_refill(st, S, 2, 3, 0, n, lane);
                 acc = gb_warp_sum(acc);
                 if (lane == 0) W.ctxv[c] = acc;
             }
-            if (ok) dl_refill(st, S, 2, 3, phi > 2 ? 0 : -1, n, lane);
+            if (ok) dl_refill(st, S, 2, 3, 0, n, lane);
         }
         if (!ok) dl_give_up(words, S, lane);
-        if (phi == 2) break;
         if (!dl_grid_barrier(words, bar++, S)) return;
 
         // ---- phase 3: context -> Q8_0 -> Wo rows, + x -> x2
@@ -871,12 +863,158 @@ __global__ void __launch_bounds__(DL_THREADS, 1) decode_layers_kernel(const __gr
     }
 }
 
+// ---------------------------------------------------------------- the attention ops as two plain launches
+// Shared memory of their CTAs: what dl_soft_max_row and the rope need, nothing of the rings.
+// Dynamic shared memory the two launches ask for without using it: at most two of their CTAs then share an SM, so
+// the block scheduler spreads a grid that starts while its predecessor still holds part of the device (with no
+// such limit the CTAs pile up on the SMs that become free first: 70.7 instead of 65.7 us per layer).
+constexpr int ATT_SPREAD_SMEM = 96 * 1024;
+struct att_smem {
+    float red[40];
+    float cs[DL_MAX_PAIRS * 2];
+    alignas(128) float vec[3072];  // rope(q) of the head (launch 1); the probabilities of the head (launch 2)
+};
+// The attention phases of the kernel above without its rings and grid barriers, for a host that keeps one op
+// per mat-mul: each is an ordinary kernel in the stream (programmatic dependent launch like every other op).
+//
+// Launch 1: galois_rope_custom of q and k, the two cache appends (galois_cpy f32 -> f16) and
+// scores = K cache x f16(rope(q)) (the F16 mat-mul).  A head belongs to `cph` consecutive CTAs; each ropes the
+// head's query for itself, the first of them also ropes the key and appends key and value.  Row `pos` of the
+// scores is formed from rope(k) directly, whichever CTA owns it (the append may not be visible yet).
+__global__ void __launch_bounds__(DL_THREADS) attn_rope_scores_kernel(const float* __restrict__ qkv, const int32_t* __restrict__ posp,
+                                                                      __half* __restrict__ k_cache, __half* __restrict__ v_cache,
+                                                                      float* __restrict__ scores, int heads, int ctx, int cph, float theta_scale,
+                                                                      float freq_scale, int* __restrict__ status) {
+    __shared__ att_smem S_;
+    att_smem* S = &S_;
+    gb_pdl_entry();
+    constexpr int hd = 128, npair = hd / 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int H = heads * hd, h = blockIdx.x / cph, part = blockIdx.x % cph;
+    const int pos = __ldg(posp);
+    if (pos < 0 || pos >= ctx) {
+        // the reference would index its cache out of bounds and panic
+        if (threadIdx.x == 0) atomicExch(status, GALOIS_B200_E_BADARG);
+        return;
+    }
+    const float* q = qkv;
+    const float* k = qkv + H;
+    const float* v = qkv + 2 * H;
+    if ((int)threadIdx.x < npair) {
+        // theta_i = freq_scale * pos * theta_scale^i, one f32 multiply at a time (src/op.rs:2717-2734)
+        float theta = __fmul_rn(freq_scale, (float)pos);
+        for (int at = 0; at < (int)threadIdx.x; at++) theta = __fmul_rn(theta, theta_scale);
+        const float c = cosf(theta), sn = sinf(theta);
+        S->cs[2 * threadIdx.x] = c;
+        S->cs[2 * threadIdx.x + 1] = sn;
+        const int i = threadIdx.x;
+        float y0, y1;
+        dl_rope_pair(__ldcg(q + h * hd + 2 * i), __ldcg(q + h * hd + 2 * i + 1), c, sn, y0, y1);
+        S->vec[2 * i] = __half2float(__float2half_rn(y0));  // the F16 mat-mul rounds its f32 operand to f16
+        S->vec[2 * i + 1] = __half2float(__float2half_rn(y1));
+        if (part == 0) {
+            // galois_cpy f32 -> f16 of rope(k) into row `pos` of the K cache
+            __half* kc = k_cache + ((size_t)h * ctx + pos) * hd;
+            dl_rope_pair(__ldcg(k + h * hd + 2 * i), __ldcg(k + h * hd + 2 * i + 1), c, sn, y0, y1);
+            kc[2 * i] = __float2half_rn(y0);
+            kc[2 * i + 1] = __float2half_rn(y1);
+        }
+    } else if ((int)threadIdx.x >= 128 && (int)threadIdx.x < 128 + hd && part == 0) {
+        // ... and of v into column `pos` of the V cache
+        __half* vc = v_cache + (size_t)h * hd * ctx + pos;
+        vc[(size_t)(threadIdx.x - 128) * ctx] = __float2half_rn(__ldcg(v + h * hd + threadIdx.x - 128));
+    }
+    __syncthreads();
+    // 16 cache rows per step of a warp, a row per 16 lanes (8 halves per lane), xor tree over the 16 lanes
+    const int grp = lane >> 4, sub = lane & 15;
+    float xh[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) xh[i] = S->vec[sub * 8 + i];
+    const uint8_t* kbase = reinterpret_cast<const uint8_t*>(k_cache + (size_t)h * ctx * hd);
+    for (int c = part * DL_WARPS + warp; c < ctx / 16; c += cph * DL_WARPS) {
+        const int j0 = c * 16;
+        uint4 raw[8];
+#pragma unroll
+        for (int rr = 0; rr < 8; rr++) raw[rr] = __ldcg(reinterpret_cast<const uint4*>(kbase + (size_t)(j0 + 2 * rr + grp) * hd * 2 + sub * 16));
+#pragma unroll
+        for (int rr = 0; rr < 8; rr++) {
+            const int r = 2 * rr + grp;
+            if (j0 + r == pos) {
+                // the row being appended in this step: its values come from rope(k), not from memory
+                uint32_t hh[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int pi = sub * 4 + i;
+                    float y0, y1;
+                    dl_rope_pair(__ldcg(k + h * hd + 2 * pi), __ldcg(k + h * hd + 2 * pi + 1), S->cs[2 * pi], S->cs[2 * pi + 1], y0, y1);
+                    hh[i] = dl_pack_h2(y0, y1);
+                }
+                raw[rr] = make_uint4(hh[0], hh[1], hh[2], hh[3]);
+            }
+            const __half2* hp = reinterpret_cast<const __half2*>(&raw[rr]);
+            float acc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(hp[i]);
+                acc = fmaf(f.x, xh[2 * i], acc);
+                acc = fmaf(f.y, xh[2 * i + 1], acc);
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (sub == 0) scores[(size_t)h * ctx + j0 + r] = acc;
+        }
+    }
+}
+
+// Launch 2: galois_scale by 1/sqrt(head_dim), the causal mask and galois_soft_max of a head (the one-op kernel's
+// arithmetic and summation order, dl_soft_max_row), then context = V cache x f16(probabilities) for this CTA's
+// rows of that head (the F16 mat-mul's order: eight sequential terms per lane and 256-element stride, xor tree).
+__global__ void __launch_bounds__(DL_THREADS) attn_softmax_pv_kernel(const float* __restrict__ scores, const __half* __restrict__ v_cache,
+                                                                     float* __restrict__ ctxv, const int32_t* __restrict__ posp, int heads, int ctx,
+                                                                     int cph, float kq_scale, const uint16_t* __restrict__ exp_lut,
+                                                                     int* __restrict__ status) {
+    __shared__ att_smem S_;
+    att_smem* S = &S_;
+    gb_pdl_entry();
+    constexpr int hd = 128;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = blockIdx.x / cph, part = blockIdx.x % cph;
+    (void)heads;
+    const int pos = __ldg(posp);
+    if (pos < 0 || pos >= ctx) return;  // reported by the launch in front of this one
+    const int limit = pos + 1 < ctx ? pos + 1 : ctx;
+    const int VT = min(1024, max(32, (((ctx + 3) / 4 + 31) / 32) * 32));  // row_threads(ctx) of the one-op soft_max
+    if (!dl_soft_max_row(S, scores + (size_t)h * ctx, ctx, limit, kq_scale, VT, exp_lut) && threadIdx.x == 0) atomicExch(status, GALOIS_B200_E_BADARG);
+    const int rows = hd / cph;
+    for (int d = part * rows + warp; d < (part + 1) * rows; d += DL_WARPS) {
+        const uint8_t* vrow = reinterpret_cast<const uint8_t*>(v_cache + ((size_t)h * hd + d) * ctx);
+        float acc = 0.0f;
+#pragma unroll 4
+        for (int kk = lane * 8; kk < ctx; kk += 256) {
+            const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(vrow + (size_t)kk * 2));
+            const __half2* hp = reinterpret_cast<const __half2*>(&raw);
+            const float4 p0 = *reinterpret_cast<const float4*>(S->vec + kk), p1 = *reinterpret_cast<const float4*>(S->vec + kk + 4);
+            const float xp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 f = __half22float2(hp[i]);
+                acc = fmaf(f.x, xp[2 * i], acc);
+                acc = fmaf(f.y, xp[2 * i + 1], acc);
+            }
+        }
+        acc = gb_warp_sum(acc);
+        if (lane == 0) ctxv[h * hd + d] = acc;
+    }
+}
+
 }  // namespace
 
 static size_t dl_smem_bytes() { return ((sizeof(dl_smem) + 127) & ~(size_t)127) + (size_t)DL_WARPS * DL_NSLOT * DL_SLOT; }
 
 int gb_decode_init(galois_b200_ctx* ctx) {
     GB_CUDA(ctx, cudaFuncSetAttribute(decode_layers_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dl_smem_bytes()));
+    GB_CUDA(ctx, cudaFuncSetAttribute(attn_rope_scores_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SPREAD_SMEM));
+    GB_CUDA(ctx, cudaFuncSetAttribute(attn_softmax_pv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SPREAD_SMEM));
     return 0;
 }
 
@@ -915,9 +1053,10 @@ extern "C" int galois_b200_decode_workspace_bytes(galois_b200_ctx* ctx, const ga
     return 0;
 }
 
-// Phases plo..phi of the kernel: 0..5 = whole layers, 1..2 = the attention of one layer.
-static int dl_launch(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, const galois_b200_decode_layer* layers, int n_layers, const float* x,
-                     const int32_t* pos, float* out, void* workspace, size_t workspace_bytes, int plo, int phi) {
+extern "C" int galois_b200_decode_layers_f32(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, const galois_b200_decode_layer* layers,
+                                             int n_layers, const float* x, const int32_t* pos, float* out, void* workspace,
+                                             size_t workspace_bytes) {
+    GB_CHECK_CTX(ctx);
     dl_params P;
     memset(&P, 0, sizeof(P));
     int rc = dl_check_shape(ctx, shape, &P.plan_h, &P.plan_f);
@@ -931,10 +1070,8 @@ static int dl_launch(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape
         return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "decode_layers: x, out and the workspace must be 16-byte aligned");
     for (int l = 0; l < n_layers; l++) {
         const galois_b200_decode_layer& L = layers[l];
-        const void* all[] = {L.k_cache, L.v_cache, L.wq, L.wk, L.wv, L.wo, L.w_gate, L.w_up, L.w_down, L.attn_norm, L.ffn_norm};
-        const int nptr = plo == 1 ? 2 : 11;  // the attention phases touch the caches only
-        for (int i = 0; i < nptr; i++) {
-            const void* q = all[i];
+        const void* ptrs[] = {L.wq, L.wk, L.wv, L.wo, L.w_gate, L.w_up, L.w_down, L.attn_norm, L.ffn_norm, L.k_cache, L.v_cache};
+        for (const void* q : ptrs) {
             if (!q) return gb_fail(ctx, GALOIS_B200_E_BADARG, "decode_layers: null pointer in layer %d", l);
             if ((uintptr_t)q % 16) return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "decode_layers: layer %d holds a pointer that is not 16-byte aligned", l);
         }
@@ -942,7 +1079,6 @@ static int dl_launch(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape
     }
     P.hidden = shape->hidden, P.heads = shape->heads, P.head_dim = shape->head_dim, P.ffn = shape->ffn, P.ctx = shape->ctx;
     P.n_layers = n_layers;
-    P.phase_lo = plo, P.phase_hi = phi;
     P.eps = shape->eps;
     P.theta_scale = powf(shape->rope_freq_base, -2.0f / (float)shape->head_dim);  // libm powf on the host, as the CPU path does (src/op.rs:2697)
     P.freq_scale = shape->rope_freq_scale;
@@ -954,21 +1090,37 @@ static int dl_launch(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape
     void* args[] = {&P};
     GB_CUDA(ctx, cudaLaunchCooperativeKernel((const void*)decode_layers_kernel, dim3((unsigned)ctx->sm_count), dim3(DL_THREADS), args, dl_smem_bytes(),
                                              ctx->stream));
-    GB_LAUNCHED(ctx, plo == 1 ? "decode_attention" : "decode_layers");
+    GB_LAUNCHED(ctx, "decode_layers");
     return 0;
-}
-
-extern "C" int galois_b200_decode_layers_f32(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, const galois_b200_decode_layer* layers,
-                                             int n_layers, const float* x, const int32_t* pos, float* out, void* workspace,
-                                             size_t workspace_bytes) {
-    GB_CHECK_CTX(ctx);
-    return dl_launch(ctx, shape, layers, n_layers, x, pos, out, workspace, workspace_bytes, 0, 5);
 }
 
 extern "C" int galois_b200_decode_attention_f32(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, const galois_b200_decode_layer* layer,
                                                 const float* qkv, const int32_t* pos, float* context, void* workspace, size_t workspace_bytes) {
     GB_CHECK_CTX(ctx);
-    return dl_launch(ctx, shape, layer, 1, qkv, pos, context, workspace, workspace_bytes, 1, 2);
+    int plan_h = 0, plan_f = 0;
+    const int rc = dl_check_shape(ctx, shape, &plan_h, &plan_f);
+    if (rc) return rc;
+    if (!layer || !qkv || !pos || !context || !workspace || !layer->k_cache || !layer->v_cache)
+        return gb_fail(ctx, GALOIS_B200_E_BADARG, "decode_attention: null pointer");
+    if (workspace_bytes < dl_ws_floats(shape->hidden, shape->heads, shape->ctx, shape->ffn) * sizeof(float))
+        return gb_fail(ctx, GALOIS_B200_E_NOMEM, "decode_attention: workspace too small (galois_b200_decode_workspace_bytes)");
+    if ((uintptr_t)qkv % 16 || (uintptr_t)context % 16 || (uintptr_t)workspace % 16 || (uintptr_t)pos % 4 || (uintptr_t)layer->k_cache % 16 ||
+        (uintptr_t)layer->v_cache % 16)
+        return gb_fail(ctx, GALOIS_B200_E_LAYOUT, "decode_attention: q | k | v, context, the caches and the workspace must be 16-byte aligned");
+    const dl_ws W = dl_carve((float*)workspace, shape->hidden, shape->heads, shape->ctx, shape->ffn);
+    // CTAs per head: a power of two that divides the head's rows, as many as the device holds at once, at most 8
+    int cph = 1;
+    while (cph < 8 && shape->heads * cph * 2 <= 2 * ctx->sm_count) cph *= 2;
+    const float theta_scale = powf(shape->rope_freq_base, -2.0f / (float)shape->head_dim);  // libm powf on the host, as the CPU path does (src/op.rs:2697)
+    const float kq_scale = (float)(1.0 / sqrt((double)shape->head_dim));
+    const dim3 grid((unsigned)(shape->heads * cph));
+    GB_CUDA(ctx, gb_launch(ctx, attn_rope_scores_kernel, grid, dim3(DL_THREADS), ATT_SPREAD_SMEM, qkv, pos, (__half*)layer->k_cache, (__half*)layer->v_cache,
+                           W.scores, (int)shape->heads, (int)shape->ctx, cph, theta_scale, shape->rope_freq_scale, ctx->dev_status));
+    GB_LAUNCHED(ctx, "attn_rope_scores");
+    GB_CUDA(ctx, gb_launch(ctx, attn_softmax_pv_kernel, grid, dim3(DL_THREADS), ATT_SPREAD_SMEM, (const float*)W.scores, (const __half*)layer->v_cache, context,
+                           pos, (int)shape->heads, (int)shape->ctx, cph, kq_scale, ctx->exp_lut, ctx->dev_status));
+    GB_LAUNCHED(ctx, "attn_softmax_pv");
+    return 0;
 }
 
 #ifdef GB_DL_PROF

@@ -54,9 +54,9 @@ class DecodeLayer:
     residual sums inside the mat-mul that produces their other operand (``galois_matmul_fused``).  Rows
     of a mat-mul are independent and the fusions round like the op pairs, so both variants give
     the same numbers bit for bit.
-    ``fused=True, attention_kernel=True``: 5 kernels.  Rope, the two cache appends, the scores, the masked
-    soft_max and the context product run as ONE launch (``galois_b200_decode_attention_f32``, the attention
-    phases of the persistent decode kernel), again the same numbers bit for bit."""
+    ``fused=True, attention_kernel=True``: 6 kernels.  Rope, the two cache appends and the scores run as one
+    launch, the masked soft_max and the context product as a second (``galois_b200_decode_attention_f32``, the
+    attention phases of the persistent decode kernel as plain kernels), again the same numbers bit for bit."""
 
     def __init__(self, dev, shape: LayerShape, weights: dict, attn_norm: np.ndarray, ffn_norm: np.ndarray,
                  k_cache: np.ndarray, v_cache: np.ndarray, fused: bool = False, attention_kernel: bool = False):

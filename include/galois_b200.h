@@ -393,11 +393,12 @@ int galois_b200_decode_workspace_bytes(galois_b200_ctx* ctx, const galois_b200_d
 int galois_b200_decode_layers_f32(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, const galois_b200_decode_layer* layers_host,
                                   int n_layers, const float* x, const int32_t* pos, float* out, void* workspace, size_t workspace_bytes);
 
-/* The attention of one such layer in one launch: rope of q and k (src/op.rs:2717-2734), the two cache appends
- * (galois_cpy f32 -> f16), scores = K cache x q (F16 mat-mul), galois_scale by 1/sqrt(head_dim) with the causal
- * mask and galois_soft_max, context = V cache x probabilities: five calls of the one-op API, same numbers bit
- * for bit.  qkv: f32 [3 * hidden] = q | k | v as the stacked projection wrote them; context: f32 [hidden];
- * of `layer` only k_cache and v_cache are used; shape, pos, workspace and the limits as above. */
+/* The attention of one such layer in two launches (each an ordinary kernel in the stream): rope of q and k
+ * (src/op.rs:2717-2734), the two cache appends (galois_cpy f32 -> f16) and scores = K cache x q (F16 mat-mul);
+ * then galois_scale by 1/sqrt(head_dim) with the causal mask, galois_soft_max and context = V cache x
+ * probabilities: five calls of the one-op API, same numbers bit for bit.  qkv: f32 [3 * hidden] = q | k | v as
+ * the stacked projection wrote them; context: f32 [hidden]; of `layer` only k_cache and v_cache are used;
+ * shape, pos, workspace and the limits as above. */
 int galois_b200_decode_attention_f32(galois_b200_ctx* ctx, const galois_b200_decode_shape* shape, const galois_b200_decode_layer* layer,
                                      const float* qkv, const int32_t* pos, float* context, void* workspace, size_t workspace_bytes);
 
