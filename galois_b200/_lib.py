@@ -68,6 +68,9 @@ SIGNATURES = {
     "galois_b200_free": ([_P, _P], _I),
     "galois_b200_htod": ([_P, _P, _P, _SZ], _I),
     "galois_b200_dtoh": ([_P, _P, _P, _SZ], _I),
+    "galois_b200_htod_async": ([_P, _P, _P, _SZ], _I),
+    "galois_b200_dtoh_async": ([_P, _P, _P, _SZ, C.POINTER(_I)], _I),
+    "galois_b200_dtoh_wait": ([_P, _I], _I),
     "galois_b200_synchronize": ([_P], _I),
     "galois_b200_reserve_scratch": ([_P, _SZ], _I),
     "galois_b200_mul_mat_q4_0_scratch_bytes": ([_P, _DP, _DP, C.POINTER(_SZ)], _I),

@@ -218,6 +218,14 @@ extern "C" int galois_b200_destroy(galois_b200_ctx* ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->io) cudaFree(ctx->io);
     if (ctx->tmp) cudaFree(ctx->tmp);
+    if (ctx->copy_ready) {
+        cudaStreamDestroy(ctx->h2d_stream);
+        cudaStreamDestroy(ctx->d2h_stream);
+        cudaEventDestroy(ctx->h2d_done);
+        cudaEventDestroy(ctx->compute_done);
+        for (int i = 0; i < GB_COPY_TICKETS; i++) cudaEventDestroy(ctx->d2h_done[i]);
+        cudaFreeHost(ctx->d2h_status);
+    }
     if (ctx->packs) {
         gb_mm_tc_release_all(ctx);
         free(ctx->packs);
@@ -313,6 +321,59 @@ extern "C" int galois_b200_dtoh(galois_b200_ctx* ctx, void* dst_host, const void
     GB_CUDA(ctx, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     // synchronises, and reports a bounded device-side wait that ran out in the work the result came from
     return check_dev_status(ctx);
+}
+// ---- pipelined host copies: uploads and read-backs on their own streams, ordered against the context's stream by
+// events, so that the copies of one step overlap the kernels of its neighbours (double-buffered by the caller).
+static int copy_streams(galois_b200_ctx* ctx) {
+    if (ctx->copy_ready) return 0;
+    GB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));
+    GB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking));
+    GB_CUDA(ctx, cudaEventCreateWithFlags(&ctx->h2d_done, cudaEventDisableTiming));
+    GB_CUDA(ctx, cudaEventCreateWithFlags(&ctx->compute_done, cudaEventDisableTiming));
+    for (int i = 0; i < GB_COPY_TICKETS; i++) GB_CUDA(ctx, cudaEventCreateWithFlags(&ctx->d2h_done[i], cudaEventDisableTiming));
+    GB_CUDA(ctx, cudaMallocHost(&ctx->d2h_status, GB_COPY_TICKETS * sizeof(int)));
+    memset(ctx->d2h_status, 0, GB_COPY_TICKETS * sizeof(int));
+    ctx->copy_ready = 1;
+    return 0;
+}
+extern "C" int galois_b200_htod_async(galois_b200_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes) {
+    GB_CHECK_CTX(ctx);
+    if (bytes == 0) return 0;
+    if (!dst_dev || !src_host) return gb_fail(ctx, GALOIS_B200_E_BADARG, "htod_async: null pointer");
+    int rc = copy_streams(ctx);
+    if (rc) return rc;
+    GB_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->h2d_stream));
+    GB_CUDA(ctx, cudaEventRecord(ctx->h2d_done, ctx->h2d_stream));
+    GB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->h2d_done, 0));  // what is enqueued from now on sees the data
+    gb_hazard_reset(ctx);
+    return 0;
+}
+extern "C" int galois_b200_dtoh_async(galois_b200_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes, int* ticket) {
+    GB_CHECK_CTX(ctx);
+    if (!ticket) return gb_fail(ctx, GALOIS_B200_E_BADARG, "dtoh_async: null ticket");
+    if (bytes != 0 && (!dst_host || !src_dev)) return gb_fail(ctx, GALOIS_B200_E_BADARG, "dtoh_async: null pointer");
+    int rc = copy_streams(ctx);
+    if (rc) return rc;
+    const int t = ctx->next_ticket;
+    ctx->next_ticket = (t + 1) % GB_COPY_TICKETS;
+    GB_CUDA(ctx, cudaEventRecord(ctx->compute_done, ctx->stream));
+    GB_CUDA(ctx, cudaStreamWaitEvent(ctx->d2h_stream, ctx->compute_done, 0));  // after everything enqueued so far
+    if (bytes) GB_CUDA(ctx, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->d2h_stream));
+    GB_CUDA(ctx, cudaMemcpyAsync(ctx->d2h_status + t, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->d2h_stream));
+    GB_CUDA(ctx, cudaEventRecord(ctx->d2h_done[t], ctx->d2h_stream));
+    *ticket = t;
+    return 0;
+}
+extern "C" int galois_b200_dtoh_wait(galois_b200_ctx* ctx, int ticket) {
+    GB_CHECK_CTX(ctx);
+    if (!ctx->copy_ready || ticket < 0 || ticket >= GB_COPY_TICKETS) return gb_fail(ctx, GALOIS_B200_E_BADARG, "dtoh_wait: no such ticket");
+    GB_CUDA(ctx, cudaEventSynchronize(ctx->d2h_done[ticket]));
+    const int st = ctx->d2h_status[ticket];
+    if (st != 0) {
+        // the status word stays set on the device until a synchronising call (galois_b200_synchronize, galois_b200_dtoh) clears it
+        return gb_fail(ctx, st, "a bounded device-side wait ran out in the work this read-back followed (status %d)", st);
+    }
+    return 0;
 }
 extern "C" int galois_b200_synchronize(galois_b200_ctx* ctx) {
     GB_CHECK_CTX(ctx);

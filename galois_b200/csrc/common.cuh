@@ -25,6 +25,7 @@ struct gb_weight_pack {
 };
 
 // Context behind the opaque galois_b200_ctx handle.
+constexpr int GB_COPY_TICKETS = 8;
 struct galois_b200_ctx {
     int ordinal;
     cudaStream_t stream;
@@ -62,6 +63,11 @@ struct galois_b200_ctx {
     size_t tmp_bytes;
     gb_weight_pack* packs;  // GB_MAX_PACKS entries
     int npacks;
+    // asynchronous host copies (galois_b200_htod_async / dtoh_async): one stream per direction, created on first use
+    cudaStream_t h2d_stream, d2h_stream;
+    cudaEvent_t h2d_done, compute_done, d2h_done[GB_COPY_TICKETS];
+    int* d2h_status;  // pinned: the device status word as it stood when each ticket's data left
+    int copy_ready, next_ticket;
     char err[512];
 };
 

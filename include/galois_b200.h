@@ -124,6 +124,16 @@ int galois_b200_alloc(galois_b200_ctx* ctx, size_t bytes, void** out_dev);
 int galois_b200_free(galois_b200_ctx* ctx, void* dev);
 int galois_b200_htod(galois_b200_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
 int galois_b200_dtoh(galois_b200_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+/* The same copies on streams of their own, for a host that pipelines steps (both host buffers pinned):
+ * htod_async uploads on an upload stream and makes everything enqueued on the context's stream afterwards wait
+ * for it; the caller must not name a device buffer that kernels already enqueued still read (two buffers in
+ * turn).  dtoh_async reads back, on a read-back stream, after everything enqueued on the context's stream so
+ * far, and hands out a ticket (eight in rotation); dtoh_wait blocks until that ticket's data is in dst_host and
+ * returns the device status as it stood then (a bounded device-side wait that ran out), without waiting for
+ * work enqueued after the ticket was taken.  The reference has the synchronous forms only. */
+int galois_b200_htod_async(galois_b200_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+int galois_b200_dtoh_async(galois_b200_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes, int* ticket);
+int galois_b200_dtoh_wait(galois_b200_ctx* ctx, int ticket);
 int galois_b200_synchronize(galois_b200_ctx* ctx);
 /* galois_b200_dtoh and galois_b200_synchronize also report a bounded device-side wait that ran out
  * in the work they waited for (GALOIS_B200_E_TIMEOUT, a bad get_rows index as GALOIS_B200_E_BADARG):

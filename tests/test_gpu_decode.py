@@ -268,6 +268,23 @@ def test_layer_with_one_attention_launch_equals_op_by_op_layer(dev, oracle, hidd
         assert np.array_equal(ref.v_cache.to_numpy().view(np.uint16), one.v_cache.to_numpy().view(np.uint16))
 
 
+def test_attention_launches_report_a_position_outside_the_cache(dev, oracle):
+    import galois_b200 as gb
+    from galois_b200.decode import DecodeLayer, LayerShape
+
+    s = LayerShape(hidden=512, heads=4, head_dim=128, ffn=1024, ctx=256)
+    wq4, attn_norm, ffn_norm, k_cache, v_cache, x = make_layer_inputs(oracle, s, 5200)
+    L = DecodeLayer(dev, s, wq4, attn_norm, ffn_norm, k_cache.view(np.float16), v_cache.view(np.float16), fused=True, attention_kernel=True)
+    G = gb.Device.Gpu(dev)
+    L.step(gb.Tensor.from_numpy(x, gb.GGmlType.F32, G), gb.Tensor.from_numpy(np.array([256], np.int32), gb.GGmlType.I32, G), 255)
+    with pytest.raises(gb.GError) as e:
+        dev.synchronize()
+    assert e.value.code == -1
+    # nothing was appended
+    assert np.array_equal(L.k_cache.to_numpy().view(np.uint16), k_cache)
+    assert np.array_equal(L.v_cache.to_numpy().view(np.uint16), v_cache)
+
+
 def test_persistent_kernel_rejects_what_it_does_not_hold(dev, oracle):
     import ctypes as C
 

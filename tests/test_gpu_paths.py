@@ -189,3 +189,48 @@ def test_prepared_weight_gives_the_bits_of_the_unprepared_path(gb, dev, oracle, 
     assert_close(p, oracle.mul_mat_q4_0(w, x))
     with pytest.raises(gb.GError):
         dev.release_weight(wt)  # not prepared any more
+
+
+def test_pipelined_host_copies_give_the_results_of_the_synchronous_ones(gb, dev, oracle):
+    """galois_b200_htod_async / dtoh_async / dtoh_wait: two buffer sets in turn, the host waits for step i - 1 after
+    enqueuing step i; every step's read-back equals the synchronous call's."""
+    import torch
+
+    n, k = 1024, 4096
+    w = oracle.quantize_q4_0(oracle.fill_normal(n * k, 210, 0, 0.02).reshape(n, k))
+    G = gb.Device.Gpu(dev)
+    wt = gb.Tensor.from_raw(w, (k, n), gb.GGmlType.Q4_0, G)
+    wd = wt.dim().c_struct()
+    xdim = gb.Dim.ggml((k, 1), gb.GGmlType.F32).c_struct()
+    ydim = gb.Dim.ggml((n, 1), gb.GGmlType.F32).c_struct()
+    steps = 6
+    xs = [torch.from_numpy(oracle.fill_normal(k, 220 + i)).pin_memory() for i in range(steps)]
+    xd = [torch.zeros(k, device=dev.torch_device) for _ in range(2)]
+    yd = [torch.zeros(n, device=dev.torch_device) for _ in range(2)]
+    yh = [torch.zeros(n).pin_memory() for _ in range(steps)]
+    vp = lambda t: C.c_void_p(t.data_ptr())
+    tickets, ticket = [None, None], C.c_int(-1)
+    for i in range(steps):
+        p = i & 1
+        assert gb.lib.galois_b200_htod_async(dev.ctx, vp(xd[p]), vp(xs[i]), k * 4) == 0
+        assert gb.lib.galois_b200_mul_mat_q4_0_f32(dev.ctx, C.c_void_p(wt.data_ptr()), C.byref(wd), vp(xd[p]), C.byref(xdim), vp(yd[p]), C.byref(ydim)) == 0
+        assert gb.lib.galois_b200_dtoh_async(dev.ctx, vp(yh[i]), vp(yd[p]), n * 4, C.byref(ticket)) == 0
+        tickets[p] = ticket.value
+        if tickets[1 - p] is not None:
+            assert gb.lib.galois_b200_dtoh_wait(dev.ctx, tickets[1 - p]) == 0
+            tickets[1 - p] = None
+    for t in tickets:
+        if t is not None:
+            assert gb.lib.galois_b200_dtoh_wait(dev.ctx, t) == 0
+    assert gb.lib.galois_b200_dtoh_wait(dev.ctx, 99) == -1
+    dev.synchronize()
+    from conftest import assert_close
+
+    for i in range(steps):
+        xt = gb.Tensor.from_numpy(xs[i].numpy().reshape(1, k), gb.GGmlType.F32, G)
+        yt = gb.Tensor.zeros((n, 1), gb.GGmlType.F32, G)
+        gb.galois_matmul(wt, xt, yt)
+        want = yt.to_numpy().reshape(-1)
+        assert np.array_equal(yh[i].numpy().view(np.uint32), want.view(np.uint32)), i
+        if i == 0:
+            assert_close(want.reshape(1, n), oracle.mul_mat_q4_0(w, xs[i].numpy().reshape(1, k)))
