@@ -289,17 +289,47 @@ extern "C" int galois_b200_alloc(galois_b200_ctx* ctx, size_t bytes, void** out_
         (void)cudaGetLastError();
         return gb_fail(ctx, GALOIS_B200_E_NOMEM, "alloc: cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
     }
+    if (ctx->nallocs < GB_MAX_ALLOCS) {
+        ctx->allocs[ctx->nallocs].p = *out_dev;
+        ctx->allocs[ctx->nallocs].bytes = bytes;
+        ctx->nallocs++;
+    }
     return 0;
 }
 extern "C" int galois_b200_free(galois_b200_ctx* ctx, void* dev) {
     GB_CHECK_CTX(ctx);
-    if (dev) GB_CUDA(ctx, cudaFree(dev));
+    if (!dev) return 0;
+    for (int i = 0; i < ctx->nallocs; i++) {
+        if (ctx->allocs[i].p != dev) continue;
+        // prepared copies of weights that lived here go with the memory
+        int rc = gb_mm_tc_release_range(ctx, dev, (const uint8_t*)dev + ctx->allocs[i].bytes);
+        if (rc) return rc;
+        ctx->allocs[i] = ctx->allocs[--ctx->nallocs];
+        break;
+    }
+    GB_CUDA(ctx, cudaFree(dev));
+    return 0;
+}
+// Is [w, w + 1) inside memory that galois_b200_alloc handed out (so that its free and its uploads are seen here)?
+static bool gb_tracked(const galois_b200_ctx* ctx, const void* w) {
+    for (int i = 0; i < ctx->nallocs; i++)
+        if ((uintptr_t)w >= (uintptr_t)ctx->allocs[i].p && (uintptr_t)w < (uintptr_t)ctx->allocs[i].p + ctx->allocs[i].bytes) return true;
+    return false;
+}
+extern "C" int galois_b200_set_auto_prepare(galois_b200_ctx* ctx, int on) {
+    GB_CHECK_CTX(ctx);
+    ctx->auto_prepare = on != 0;
     return 0;
 }
 extern "C" int galois_b200_htod(galois_b200_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes) {
     GB_CHECK_CTX(ctx);
     if (bytes == 0) return 0;
     if (!dst_dev || !src_host) return gb_fail(ctx, GALOIS_B200_E_BADARG, "htod: null pointer");
+    if (ctx->npacks) {
+        // an upload over a prepared weight: its copy is stale, the next large-batch mat-mul prepares it again
+        int rc = gb_mm_tc_release_range(ctx, dst_dev, (const uint8_t*)dst_dev + bytes);
+        if (rc) return rc;
+    }
     GB_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
     gb_hazard_reset(ctx);
     return 0;
@@ -342,6 +372,10 @@ extern "C" int galois_b200_htod_async(galois_b200_ctx* ctx, void* dst_dev, const
     if (!dst_dev || !src_host) return gb_fail(ctx, GALOIS_B200_E_BADARG, "htod_async: null pointer");
     int rc = copy_streams(ctx);
     if (rc) return rc;
+    if (ctx->npacks) {
+        rc = gb_mm_tc_release_range(ctx, dst_dev, (const uint8_t*)dst_dev + bytes);
+        if (rc) return rc;
+    }
     GB_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->h2d_stream));
     GB_CUDA(ctx, cudaEventRecord(ctx->h2d_done, ctx->h2d_stream));
     GB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->h2d_done, 0));  // what is enqueued from now on sees the data
@@ -415,7 +449,8 @@ static bool skinny_beats_tc(const galois_b200_ctx* ctx, const void* w, const gal
     const double K = (double)wd->ne[0], N = (double)wd->ne[1], B = (double)xd->ne[1];
     const double pass_us = fmax(6.8, N * (K / 32.0) * 18.0 / 1.6e6);
     const double skinny_us = ceil(B / 16.0) * pass_us;
-    const bool prepared = gb_mm_tc_prepared(const_cast<galois_b200_ctx*>(ctx), w, wd);
+    // a weight the context may prepare on first use counts as prepared
+    const bool prepared = gb_mm_tc_prepared(const_cast<galois_b200_ctx*>(ctx), w, wd) || (ctx->auto_prepare && gb_tracked(ctx, w));
     const double bn = B <= 64.0 ? 64.0 : 128.0;
     const double tiles = ceil(N / 128.0) * ceil(B / bn);
     const double per_block = !prepared ? 0.68 : (bn == 64.0 ? 0.20 : 0.36);
@@ -480,8 +515,15 @@ extern "C" int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w,
     }
     const bool prof = ctx->profiling && ctx->prof_n < GB_PROF_MAX;
     if (prof) GB_CUDA(ctx, cudaEventRecord(ctx->prof_ev[2 * ctx->prof_n], ctx->stream));
-    if (variant == 3)
-        rc = gb_mm_tc_prepared(ctx, w, wd) ? gb_mm_q4_0_tp(ctx, w, wd, x, xd, dst, dd, scratch) : gb_mm_q4_0_tc(ctx, w, wd, x, xd, dst, dd, scratch);
+    if (variant == 3) {
+        bool prepared = gb_mm_tc_prepared(ctx, w, wd);
+        if (!prepared && ctx->auto_prepare && gb_tracked(ctx, w)) {
+            // first large batch on a weight whose memory this context handed out: repack it once (1.125 bytes per weight)
+            // (a full table or a failed allocation leaves the weight on the unprepared kernel)
+            prepared = gb_mm_tc_prepare(ctx, w, wd) == 0;
+        }
+        rc = prepared ? gb_mm_q4_0_tp(ctx, w, wd, x, xd, dst, dd, scratch) : gb_mm_q4_0_tc(ctx, w, wd, x, xd, dst, dd, scratch);
+    }
     else if (variant == 4)
         rc = gb_mmq_skinny(ctx, w, wd, x, xd, dst, dd, scratch);
     else if (gemv)

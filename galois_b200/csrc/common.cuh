@@ -26,6 +26,7 @@ struct gb_weight_pack {
 
 // Context behind the opaque galois_b200_ctx handle.
 constexpr int GB_COPY_TICKETS = 8;
+constexpr int GB_MAX_ALLOCS = 4096;
 struct galois_b200_ctx {
     int ordinal;
     cudaStream_t stream;
@@ -63,6 +64,10 @@ struct galois_b200_ctx {
     size_t tmp_bytes;
     gb_weight_pack* packs;  // GB_MAX_PACKS entries
     int npacks;
+    // device memory handed out by galois_b200_alloc (address, bytes): weights inside it may be prepared for the
+    // tensor-core kernel on first use (galois_b200_set_auto_prepare), because free and htod are seen here too
+    struct { void* p; size_t bytes; } allocs[GB_MAX_ALLOCS];
+    int nallocs, auto_prepare;
     // asynchronous host copies (galois_b200_htod_async / dtoh_async): one stream per direction, created on first use
     cudaStream_t h2d_stream, d2h_stream;
     cudaEvent_t h2d_done, compute_done, d2h_done[GB_COPY_TICKETS];

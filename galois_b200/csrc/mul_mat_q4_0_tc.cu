@@ -723,6 +723,24 @@ int gb_mm_tc_release(galois_b200_ctx* ctx, const void* w) {
     return gb_fail(ctx, GALOIS_B200_E_BADARG, "release_weight: this weight was not prepared");
 }
 
+// Drops every prepared copy whose weight starts inside [lo, hi): the memory is being freed or overwritten.
+int gb_mm_tc_release_range(galois_b200_ctx* ctx, const void* lo, const void* hi) {
+    bool synced = false;
+    for (int i = 0; i < ctx->npacks;) {
+        const uintptr_t w = (uintptr_t)ctx->packs[i].w;
+        if (w < (uintptr_t)lo || w >= (uintptr_t)hi) {
+            i++;
+            continue;
+        }
+        if (!synced) GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // work already enqueued may still read the copy
+        synced = true;
+        cudaFree(ctx->packs[i].pa);
+        cudaFree(ctx->packs[i].pd);
+        ctx->packs[i] = ctx->packs[--ctx->npacks];
+    }
+    return 0;
+}
+
 void gb_mm_tc_release_all(galois_b200_ctx* ctx) {
     for (int i = 0; i < ctx->npacks; i++) {
         cudaFree(ctx->packs[i].pa);

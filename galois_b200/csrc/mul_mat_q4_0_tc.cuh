@@ -25,6 +25,7 @@ int gb_mm_q4_0_tc_block_isums(galois_b200_ctx* ctx, const void* w, const galois_
 // context under w's device address until released.  Calling it again for the same address refreshes the copy.
 int gb_mm_tc_prepare(galois_b200_ctx* ctx, const void* w, const galois_dim* wd);
 int gb_mm_tc_release(galois_b200_ctx* ctx, const void* w);
+int gb_mm_tc_release_range(galois_b200_ctx* ctx, const void* lo, const void* hi);
 void gb_mm_tc_release_all(galois_b200_ctx* ctx);
 bool gb_mm_tc_prepared(galois_b200_ctx* ctx, const void* w, const galois_dim* wd);
 // The GEMM on the prepared copy (quantiser + GEMM, two launches; same scratch as gb_mm_q4_0_tc).

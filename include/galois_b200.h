@@ -201,6 +201,12 @@ int galois_b200_mul_mat_q4_0_f32(galois_b200_ctx* ctx, const void* w, const galo
  * w: 2-D, dense rows, K % 256 == 0. */
 int galois_b200_prepare_weight_q4_0(galois_b200_ctx* ctx, const void* w, const galois_dim* wd);
 int galois_b200_release_weight(galois_b200_ctx* ctx, const void* w);
+/* The same repack without a call per weight: with auto-prepare on (default off), the first large-batch mat-mul on
+ * a Q4_0 weight that lies in memory handed out by galois_b200_alloc prepares it.  For such memory the context sees
+ * what invalidates a copy: galois_b200_free releases the copies of the weights inside the block, galois_b200_htod /
+ * galois_b200_htod_async over a prepared weight drop its copy (the next large batch makes a new one).  Weights in
+ * memory the context did not allocate are never prepared behind the caller's back. */
+int galois_b200_set_auto_prepare(galois_b200_ctx* ctx, int on);
 
 /* Up to four reference ops in one call (not part of the reference API; results are
  * bit-identical to running the ops one after the other):

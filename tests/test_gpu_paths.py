@@ -234,3 +234,64 @@ def test_pipelined_host_copies_give_the_results_of_the_synchronous_ones(gb, dev,
         assert np.array_equal(yh[i].numpy().view(np.uint32), want.view(np.uint32)), i
         if i == 0:
             assert_close(want.reshape(1, n), oracle.mul_mat_q4_0(w, xs[i].numpy().reshape(1, k)))
+
+
+def test_auto_prepare_follows_alloc_upload_and_free(gb, dev, oracle):
+    """galois_b200_set_auto_prepare: a weight in memory from galois_b200_alloc is repacked by its first large-batch
+    mat-mul, re-uploading it drops the copy (the next call repacks the new contents), freeing the block releases
+    it; a weight in memory the context did not allocate is left alone.  Results equal the unprepared kernel's bits."""
+    import torch
+
+    n, k, b = 256, 512, 96
+    G = gb.Device.Gpu(dev)
+    wa = oracle.quantize_q4_0(oracle.fill_normal(n * k, 230, 0, 0.02).reshape(n, k))
+    wb = oracle.quantize_q4_0(oracle.fill_normal(n * k, 231, 0, 0.02).reshape(n, k))
+    x = oracle.fill_normal(b * k, 232).reshape(b, k)
+    xt = gb.Tensor.from_numpy(x, gb.GGmlType.F32, G)
+    wd = gb.Dim.ggml((k, n), gb.GGmlType.Q4_0).c_struct()
+    nbytes = wa.size
+
+    def reference(wraw):  # the unprepared tensor-core kernel on an ordinary tensor
+        out = gb.Tensor.zeros((n, b), gb.GGmlType.F32, G)
+        gb.galois_matmul(gb.Tensor.from_raw(wraw, (k, n), gb.GGmlType.Q4_0, G), xt, out)
+        return out.to_numpy()
+
+    def run(ptr):
+        out = gb.Tensor.zeros((n, b), gb.GGmlType.F32, G)
+        rc = gb.lib.galois_b200_mul_mat_q4_0_f32(dev.ctx, ptr, C.byref(wd), C.c_void_p(xt.data_ptr()), C.byref(xt.dim().c_struct()),
+                                                 C.c_void_p(out.data_ptr()), C.byref(out.dim().c_struct()))
+        assert rc == 0, gb.lib.galois_b200_last_error(dev.ctx)
+        return out.to_numpy()
+
+    dev.set_mul_mat_variant(3)
+    assert gb.lib.galois_b200_set_auto_prepare(dev.ctx, 1) == 0
+    ptr = C.c_void_p()
+    assert gb.lib.galois_b200_alloc(dev.ctx, nbytes, C.byref(ptr)) == 0
+    try:
+        want_a, want_b = reference(wa), reference(wb)   # ordinary tensors: never prepared
+        l0 = dev.launch_count()
+        reference(wa)
+        assert dev.launch_count() - l0 == 2              # quantiser + unprepared GEMM, no repack
+        host = np.ascontiguousarray(wa).view(np.uint8).reshape(-1)
+        assert gb.lib.galois_b200_htod(dev.ctx, ptr, host.ctypes.data_as(C.c_void_p), nbytes) == 0
+        l0 = dev.launch_count()
+        got = run(ptr)
+        assert dev.launch_count() - l0 == 3              # repack + quantiser + GEMM
+        assert np.array_equal(got.view(np.uint32), want_a.view(np.uint32))
+        l0 = dev.launch_count()
+        run(ptr)
+        assert dev.launch_count() - l0 == 2              # the copy is reused
+        host_b = np.ascontiguousarray(wb).view(np.uint8).reshape(-1)
+        assert gb.lib.galois_b200_htod(dev.ctx, ptr, host_b.ctypes.data_as(C.c_void_p), nbytes) == 0
+        l0 = dev.launch_count()
+        got = run(ptr)
+        assert dev.launch_count() - l0 == 3              # new contents: repacked again
+        assert np.array_equal(got.view(np.uint32), want_b.view(np.uint32))
+        assert gb.lib.galois_b200_free(dev.ctx, ptr) == 0
+        ptr = C.c_void_p()
+        assert gb.lib.galois_b200_release_weight(dev.ctx, C.c_void_p(0x1000)) != 0  # nothing prepared is left behind
+    finally:
+        gb.lib.galois_b200_set_auto_prepare(dev.ctx, 0)
+        dev.set_mul_mat_variant(0)
+        if ptr.value:
+            gb.lib.galois_b200_free(dev.ctx, ptr)
