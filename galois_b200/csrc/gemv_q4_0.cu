@@ -248,12 +248,15 @@ __global__ void __launch_bounds__(GEMV_THREADS)
     quantize_rows_cluster<SEG>(x, x_stride, K, nbatch, NB, act_qs, act_ds, nsegk, crank, csize, act_bar, pro);
     bool ok = mbar_wait_bounded(act_bar, 0);  // all slices of the quantised activations have landed here
 
-    int yh[HOIST ? NPASS : 1][HOIST ? 16 * SEG : 1];
-    float4 dh[HOIST ? NPASS : 1][HOIST ? SEG : 1];
+    // Passes whose activations a lane keeps in registers for the whole kernel.  Three passes would take 120
+    // registers (164 in all): the third is read from shared memory per row instead, which keeps the kernel at
+    // 128 registers, so that CTAs of four consecutive launches still share an SM.  Same values, same order.
+    constexpr int NHOIST = NPASS > 2 ? 2 : NPASS;
+    int yh[HOIST ? NHOIST : 1][HOIST ? 16 * SEG : 1];
+    float4 dh[HOIST ? NHOIST : 1][HOIST ? SEG : 1];
     if (HOIST) {
-        // every lane keeps its own activations in registers for the whole kernel
 #pragma unroll
-        for (int q = 0; q < NPASS; q++) {
+        for (int q = 0; q < NHOIST; q++) {
             const int sg = SPLIT ? (lane & (nsegk - 1)) : lane + 32 * q;
             if (sg < nsegk) {
                 load_act<SEG>(act_qs, act_ds, nsegk, sg, yh[q], dh[q]);
@@ -301,8 +304,16 @@ __global__ void __launch_bounds__(GEMV_THREADS)
                 if (SPLIT || sg < nsegk) {
                     uint32_t t[9 * SEG];
                     load_segment<SEG>(buf + sg * (36 * SEG), t);
+                    if (q < NHOIST) {
 #pragma unroll
-                    for (int p = 0; p < SEG; p++) acc[0] = pair_dot(t + 9 * p, yh[q] + 16 * p, dh[q][p], acc[0]);
+                        for (int p = 0; p < SEG; p++) acc[0] = pair_dot(t + 9 * p, yh[q < NHOIST ? q : 0] + 16 * p, dh[q < NHOIST ? q : 0][p], acc[0]);
+                    } else {
+                        int y[16 * SEG];
+                        float4 d4[SEG];
+                        load_act<SEG>(act_qs, act_ds, nsegk, sg, y, d4);
+#pragma unroll
+                        for (int p = 0; p < SEG; p++) acc[0] = pair_dot(t + 9 * p, y + 16 * p, d4[p], acc[0]);
+                    }
                 }
             }
         } else {
