@@ -15,6 +15,7 @@ from .op import (  # noqa: F401
     galois_matmul,
     galois_matmul_add,
     galois_matmul_fused,
+    galois_matmul_swiglu,
     galois_mul,
     galois_rms_norm,
     galois_rms_norm_mul,

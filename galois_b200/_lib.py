@@ -83,6 +83,7 @@ SIGNATURES = {
     "galois_b200_release_weight": ([_P, _P], _I),
     "galois_b200_set_auto_prepare": ([_P, _I], _I),
     "galois_b200_mul_mat_q4_0_f32_fused": ([_P, _P, _DP, _P, _DP, C.POINTER(GaloisPrologue), _P, _DP, _P, _DP], _I),
+    "galois_b200_mul_mat_q4_0_f32_swiglu": ([_P, _P, _DP, _P, _DP, C.POINTER(GaloisPrologue), _P, _DP], _I),
     "galois_b200_mul_mat_q4_0_f32_add": ([_P, _P, _DP, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_mul_mat_q4_0_f32_host": ([_P, _P, _DP, _P, _DP, _P, _DP], _I),
     "galois_b200_mul_mat_q4_0_f32_static": ([_P, _P, _DP, _P, _DP, _P, _DP, C.c_char_p, _SZ], _I),

@@ -218,6 +218,7 @@ extern "C" int galois_b200_destroy(galois_b200_ctx* ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->io) cudaFree(ctx->io);
     if (ctx->tmp) cudaFree(ctx->tmp);
+    if (ctx->tmp2) cudaFree(ctx->tmp2);
     if (ctx->copy_ready) {
         cudaStreamDestroy(ctx->h2d_stream);
         cudaStreamDestroy(ctx->d2h_stream);
@@ -566,20 +567,22 @@ extern "C" int galois_b200_mul_mat_q4_0_tc_block_isums(galois_b200_ctx* ctx, con
 }
 
 // A context-owned buffer for the intermediate of a fused call that has to run as separate ops.
-static int gb_tmp(galois_b200_ctx* ctx, size_t bytes, void** out) {
-    if (bytes > ctx->tmp_bytes) {
+static int gb_grow(galois_b200_ctx* ctx, void** buf, size_t* have, size_t bytes, void** out) {
+    if (bytes > *have) {
         GB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        if (ctx->tmp) GB_CUDA(ctx, cudaFree(ctx->tmp));
-        ctx->tmp = nullptr;
-        ctx->tmp_bytes = 0;
+        if (*buf) GB_CUDA(ctx, cudaFree(*buf));
+        *buf = nullptr;
+        *have = 0;
         const size_t want = (bytes + (1u << 20) - 1) & ~(size_t)((1u << 20) - 1);
-        const cudaError_t e = cudaMalloc(&ctx->tmp, want);
+        const cudaError_t e = cudaMalloc(buf, want);
         if (e != cudaSuccess) return gb_fail(ctx, GALOIS_B200_E_NOMEM, "fused mat-mul: cannot allocate %zu bytes: %s", want, cudaGetErrorString(e));
-        ctx->tmp_bytes = want;
+        *have = want;
     }
-    *out = ctx->tmp;
+    *out = *buf;
     return 0;
 }
+static int gb_tmp(galois_b200_ctx* ctx, size_t bytes, void** out) { return gb_grow(ctx, &ctx->tmp, &ctx->tmp_bytes, bytes, out); }
+static int gb_tmp2(galois_b200_ctx* ctx, size_t bytes, void** out) { return gb_grow(ctx, &ctx->tmp2, &ctx->tmp2_bytes, bytes, out); }
 
 extern "C" int galois_b200_mul_mat_q4_0_f32_fused(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
                                                   const galois_dim* xd, const galois_b200_prologue* pro, const float* res,
@@ -633,6 +636,52 @@ extern "C" int galois_b200_mul_mat_q4_0_f32_fused(galois_b200_ctx* ctx, const vo
     rc = galois_b200_mul_mat_q4_0_f32(ctx, w, wd, xin, &td, dst, dd);
     if (rc || !res) return rc;
     return galois_b200_add_f32(ctx, res, rd, dst, dd, dst, dd);  // Add::f needs a contiguous dst; it may alias src1
+}
+
+int gb_swiglu_pairs(galois_b200_ctx* ctx, const float* x, int64_t xb1, float* y, int64_t yb1, int64_t nc, int64_t nr);
+
+extern "C" int galois_b200_mul_mat_q4_0_f32_swiglu(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
+                                                   const galois_dim* xd, const galois_b200_prologue* pro, float* dst, const galois_dim* dd) {
+    GB_CHECK_CTX(ctx);
+    if (!wd || !xd || !dd) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_swiglu: null pointer");
+    const int64_t N = wd->ne[1], K = wd->ne[0], B = xd->ne[1];
+    if (N % 2 != 0) return gb_fail(ctx, GALOIS_B200_E_SHAPE, "mul_mat_q4_0_swiglu: the weight needs an even number of rows (gate_i, up_i interleaved)");
+    if (wd->ne[2] != 1 || wd->ne[3] != 1 || xd->ne[2] != 1 || xd->ne[3] != 1)
+        return gb_fail(ctx, GALOIS_B200_E_SHAPE, "mul_mat_q4_0_swiglu: 2-D operands only");
+    if (!(dd->ne[0] == N / 2 && dd->ne[1] == B && dd->ne[2] == 1 && dd->ne[3] == 1))
+        return gb_fail(ctx, GALOIS_B200_E_SHAPE, "mul_mat_q4_0_swiglu: dst must be {N / 2, batch}");
+    if (dd->nb[0] != 1) return gb_fail(ctx, GALOIS_B200_E_DST, "mul_mat_q4_0_swiglu: dst rows must be contiguous");
+    const int kind = pro ? pro->kind : GALOIS_B200_PROLOGUE_NONE;
+    if (kind != GALOIS_B200_PROLOGUE_NONE && kind != GALOIS_B200_PROLOGUE_RMS_NORM_MUL)
+        return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_swiglu: prologue %d not supported here", kind);
+    if (kind != GALOIS_B200_PROLOGUE_NONE && !pro->aux) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_swiglu: prologue without its second operand");
+    // the mat-mul's own result shape, for the checks it shares with galois_b200_mul_mat_q4_0_f32
+    galois_dim yd = *dd;
+    yd.ne[0] = N;
+    yd.nb[1] = N, yd.nb[2] = N * B, yd.nb[3] = N * B;
+    if (!dst) return gb_fail(ctx, GALOIS_B200_E_BADARG, "mul_mat_q4_0_swiglu: null pointer");
+    int rc = gb_validate_mul_mat(ctx, w, wd, x, xd, dst, &yd);
+    if (rc) return rc;
+    if (N == 0 || B == 0) return 0;
+    const bool aux_ok = kind == GALOIS_B200_PROLOGUE_NONE || ((uintptr_t)pro->aux % 16 == 0 && gb_gemv_has_prologue());
+    if (ctx->variant == 0 && K > 0 && B < GB_SKINNY_MIN_BATCH && aux_ok && dd->nb[1] < (1ll << 30) && gb_gemv_supported(ctx, w, wd, x, xd, &yd)) {
+        // one launch: rows 2i and 2i + 1 meet in one warp of the streaming GEMV and leave it as silu(gate_i) * up_i
+        gb_gather_args none = {};
+        gb_gemv_extra ex = {};
+        ex.pro_kind = kind;
+        ex.pro_aux = pro ? pro->aux : nullptr;
+        ex.pro_eps = pro ? pro->eps : 0.0f;
+        ex.epi_kind = 1;
+        rc = gb_gemv_q4_0_gather(ctx, w, wd, x, xd, dst, dd, &none, &ex);
+        if (rc != GB_GEMV_NO_PAIR_EPILOGUE) return rc;
+    }
+    // any other shape: the fused mat-mul into a context-owned buffer, then the pairs
+    void* y = nullptr;
+    rc = gb_tmp2(ctx, (size_t)N * B * sizeof(float), &y);
+    if (rc) return rc;
+    rc = galois_b200_mul_mat_q4_0_f32_fused(ctx, w, wd, x, xd, pro, nullptr, nullptr, (float*)y, &yd);
+    if (rc) return rc;
+    return gb_swiglu_pairs(ctx, (const float*)y, N, dst, dd->nb[1], N / 2, B);
 }
 
 extern "C" int galois_b200_mul_mat_q4_0_f32_add(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,

@@ -62,6 +62,8 @@ struct galois_b200_ctx {
     // intermediate of a fused call that runs as separate ops
     void* tmp;
     size_t tmp_bytes;
+    void* tmp2;  // the mat-mul result of galois_b200_mul_mat_q4_0_f32_swiglu when it runs as separate ops
+    size_t tmp2_bytes;
     gb_weight_pack* packs;  // GB_MAX_PACKS entries
     int npacks;
     // device memory handed out by galois_b200_alloc (address, bytes): weights inside it may be prepared for the

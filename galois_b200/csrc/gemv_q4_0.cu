@@ -189,7 +189,7 @@ template <int NB, int SEG, bool SPLIT, int NPASS>
 __global__ void __launch_bounds__(GEMV_THREADS)
     gemv_q4_0_kernel(const uint8_t* __restrict__ w, const float* __restrict__ x, int x_stride, float* __restrict__ dst, int nb1, int K, int N, int nbatch, int stages,
                      int* __restrict__ status, const gb_gather_args G, const float* __restrict__ res, int res_nb1,
-                     int pro_kind, const float* __restrict__ pro_aux, float pro_eps, const uint16_t* __restrict__ silu_lut, int sync_mode) {
+                     int pro_kind, const float* __restrict__ pro_aux, float pro_eps, const uint16_t* __restrict__ silu_lut, int sync_mode, int epi_kind) {
     extern __shared__ __align__(128) uint8_t smem[];
     const bool late_wait = sync_mode == GEMV_SYNC_DEFERRED;
     if (sync_mode != GEMV_SYNC_BARRIER) pdl_launch_dependents();
@@ -286,6 +286,9 @@ __global__ void __launch_bounds__(GEMV_THREADS)
         __syncwarp();
     };
 
+    unsigned short pend_h = 0;  // pairing epilogue: the result of the chunk before this one, waiting for its table entry
+    float pend_up = 0.0f;
+    int pend_row = -1;
     for (int j = 0; j < my_chunks && ok; j++) {
         const int s = j % stages;
         ok = mbar_wait_bounded(&my_bars[s], (uint32_t)(j / stages) & 1u);
@@ -356,6 +359,20 @@ __global__ void __launch_bounds__(GEMV_THREADS)
             for (int b = 0; b < NB; b++) {
                 float v = acc[b];
                 for (int o = nsegk >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (epi_kind == 1) {
+                    // rows 2i, 2i + 1 of the weight are gate_i and up_i: galois_unary(Silu) of the first through the
+                    // f16 table (src/lib.rs:543-549), galois_mul by the second, stored as row i (rows per chunk is even).
+                    // The table entry asked for here is used one chunk later, so its latency is not waited for.
+                    const float up = __shfl_xor_sync(0xffffffffu, v, nsegk);
+                    if (pend_row >= 0) dst[pend_row] = __fmul_rn(__half2float(__ushort_as_half(pend_h)), pend_up);
+                    pend_row = -1;
+                    if ((lane & (2 * nsegk - 1)) == 0 && row0 + r + 1 < N && b < nbatch) {
+                        pend_h = __ldg(silu_lut + __half_as_ushort(__float2half_rn(v)));
+                        pend_up = up;
+                        pend_row = b * nb1 + ((row0 + r) >> 1);
+                    }
+                    continue;
+                }
                 if ((lane & (nsegk - 1)) == 0 && row0 + r < N && b < nbatch) {
                     if (res) v = __fadd_rn(res[b * res_nb1 + row0 + r], v);  // Add::f on top of the mat-mul result
                     dst[b * nb1 + row0 + r] = v;
@@ -375,6 +392,7 @@ __global__ void __launch_bounds__(GEMV_THREADS)
         }
         done = j + 1;
     }
+    if (pend_row >= 0) dst[pend_row] = __fmul_rn(__half2float(__ushort_as_half(pend_h)), pend_up);
     if (late_wait) {
         if (kept) flush_kept(done - kept, kept);
         pdl_wait();  // every warp, also one without rows: this kernel completes after the kernels in front of it
@@ -508,7 +526,7 @@ int launch_gemv(galois_b200_ctx* ctx, const gemv_plan& p, const uint8_t* w, cons
     }
     GB_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4_0_kernel<NB, SEG, SPLIT, NPASS>, w, x, x_stride, dst, nb1, K, N, B, p.stages,
                                     ctx->dev_status, gather, ex.res, (int)ex.res_nb1, ex.pro_kind, ex.pro_aux, ex.pro_eps,
-                                    ctx->silu_lut, sync_mode));
+                                    ctx->silu_lut, sync_mode, ex.epi_kind));
     ctx->launches++;
     ctx->sync_counts[sync_mode]++;
     gb_hazard_note_write(ctx, dst, (size_t)N * sizeof(float), sync_mode == GEMV_SYNC_BARRIER);
@@ -581,7 +599,10 @@ int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* w
     } else {
         gb_hazard_reset(ctx);
     }
+    if (ex.epi_kind != 0 && sync_mode == GEMV_SYNC_DEFERRED) sync_mode = GEMV_SYNC_BARRIER;  // the pairing epilogue stores directly
     gemv_plan p = plan_gemv(ctx, K, N, B, sync_mode == GEMV_SYNC_DEFERRED);
+    if (ex.epi_kind != 0 && !(p.ok && p.split && (K / 64) / p.seg <= 16 && N % 2 == 0 && gather->P.nranks == 0))
+        return GB_GEMV_NO_PAIR_EPILOGUE;  // pairs of rows do not share a warp in this plan: the caller runs the ops one by one
     if (p.ok && sync_mode == GEMV_SYNC_DEFERRED) {
         // A deferred launch holds its results back until the kernels in front of it have completed; a warp
         // with more rows than its hold-back area would stall at its first flush and the launches would run

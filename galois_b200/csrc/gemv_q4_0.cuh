@@ -26,7 +26,10 @@ struct gb_gemv_extra {
     int pro_kind;
     const float* pro_aux;
     float pro_eps;
+    int epi_kind;  // 1: weight rows 2i / 2i + 1 are gate_i / up_i and dst row i = silu(gate_i . x) * (up_i . x) (dst has N / 2 rows)
 };
+// gb_gemv_q4_0_gather with epi_kind != 0 on a shape whose row pairs do not share a warp: nothing was launched.
+constexpr int GB_GEMV_NO_PAIR_EPILOGUE = 1;
 int gb_gemv_q4_0_gather(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
                         const galois_dim* dd, const gb_gather_args* gather, const gb_gemv_extra* extra);
 // True when the GEMV was built with the 128-thread CTAs the in-kernel rms_norm needs.

@@ -162,6 +162,19 @@ __global__ void silu_kernel(const float* __restrict__ x, int64_t xb1, float* __r
     }
 }
 
+// The same product over interleaved pairs: y[r][i] = silu(x[r][2 i]) * x[r][2 i + 1] (gate_i and up_i side by side).
+__global__ void swiglu_pairs_kernel(const float* __restrict__ x, int64_t xb1, float* __restrict__ y, int64_t yb1, int64_t nc,
+                                    int64_t nr, const uint16_t* __restrict__ lut) {
+    gb_pdl_entry();
+    const int64_t total = nc * nr;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / nc, c = i - r * nc;
+        const float2 gu = *reinterpret_cast<const float2*>(x + r * xb1 + 2 * c);
+        const unsigned short h = __half_as_ushort(__float2half_rn(gu.x));
+        y[r * yb1 + c] = __fmul_rn(__half2float(__ushort_as_half(__ldg(lut + h))), gu.y);
+    }
+}
+
 // ---------------------------------------------------------------- add / mul
 // Add::f / Mul::f (src/op.rs:318-611): destination row ir (contiguous chunks of
 // ne00) = src0 row (op) src1 row, src1 broadcast by modulo over dims 1..3.
@@ -351,6 +364,14 @@ extern "C" int galois_b200_silu_f32(galois_b200_ctx* ctx, const float* x, const 
     gb_launch(ctx, silu_kernel, dim3(ew_grid(nc * nr, ctx->sm_count)), dim3(256), 0, x, xd->nb[1], y, yd->nb[1], nc, nr, ctx->silu_lut,
               (const float*)nullptr, (int64_t)0);
     GB_LAUNCHED(ctx, "silu");
+    return 0;
+}
+
+// x: nr rows of 2 nc floats (8-byte aligned rows), y: nr rows of nc floats.
+int gb_swiglu_pairs(galois_b200_ctx* ctx, const float* x, int64_t xb1, float* y, int64_t yb1, int64_t nc, int64_t nr) {
+    if (nc == 0 || nr == 0) return 0;
+    gb_launch(ctx, swiglu_pairs_kernel, dim3(ew_grid(nc * nr, ctx->sm_count)), dim3(256), 0, x, xb1, y, yb1, nc, nr, ctx->silu_lut);
+    GB_LAUNCHED(ctx, "swiglu_pairs");
     return 0;
 }
 

@@ -17,7 +17,7 @@ from dataclasses import dataclass
 
 import numpy as np
 
-from .op import (RopeCustomOption, UnaryOp, galois_add, galois_cpy, galois_cpy_pair, galois_matmul, galois_matmul_add, galois_matmul_fused, galois_mul, galois_rms_norm,
+from .op import (RopeCustomOption, UnaryOp, galois_add, galois_cpy, galois_cpy_pair, galois_matmul, galois_matmul_add, galois_matmul_fused, galois_matmul_swiglu, galois_mul, galois_rms_norm,
                  galois_rms_norm_mul, galois_rope_custom, galois_silu_mul, galois_soft_max_ext, galois_unary)
 from .tensor import Device, GGmlType, Tensor
 
@@ -56,7 +56,9 @@ class DecodeLayer:
     the same numbers bit for bit.
     ``fused=True, attention_kernel=True``: 6 kernels.  Rope, the two cache appends and the scores run as one
     launch, the masked soft_max and the context product as a second (``galois_b200_decode_attention_f32``, the
-    attention phases of the persistent decode kernel as plain kernels), again the same numbers bit for bit."""
+    attention phases of the persistent decode kernel as plain kernels); the rows of W_gate and W_up are
+    interleaved at upload so that silu(gate) * up leaves the mat-vec that forms both (``galois_matmul_swiglu``)
+    and the down projection quantises it directly; again the same numbers bit for bit."""
 
     def __init__(self, dev, shape: LayerShape, weights: dict, attn_norm: np.ndarray, ffn_norm: np.ndarray,
                  k_cache: np.ndarray, v_cache: np.ndarray, fused: bool = False, attention_kernel: bool = False):
@@ -72,7 +74,13 @@ class DecodeLayer:
         if fused:
             raw = lambda name: np.ascontiguousarray(weights[name]).view(np.uint8).reshape(-1)
             self.w["wqkv"] = Tensor.from_raw(np.concatenate([raw("wq"), raw("wk"), raw("wv")]), (s.hidden, 3 * s.hidden), GGmlType.Q4_0, G)
-            self.w["w_gate_up"] = Tensor.from_raw(np.concatenate([raw("w_gate"), raw("w_up")]), (s.hidden, 2 * s.ffn), GGmlType.Q4_0, G)
+            if attention_kernel:
+                # rows interleaved (gate_0, up_0, gate_1, up_1, ...): the SwiGLU product leaves the mat-vec that forms both
+                rb = s.hidden // 32 * 18
+                gu = np.stack([raw("w_gate").reshape(s.ffn, rb), raw("w_up").reshape(s.ffn, rb)], axis=1).reshape(-1)
+                self.w["w_gate_up"] = Tensor.from_raw(gu, (s.hidden, 2 * s.ffn), GGmlType.Q4_0, G)
+            else:
+                self.w["w_gate_up"] = Tensor.from_raw(np.concatenate([raw("w_gate"), raw("w_up")]), (s.hidden, 2 * s.ffn), GGmlType.Q4_0, G)
             self.qkv = Tensor.zeros((3 * s.hidden, 1), GGmlType.F32, G)
             self.qkr = Tensor.zeros((s.head_dim, 2 * s.heads, 1), GGmlType.F32, G)
             self.gu = Tensor.zeros((2 * s.ffn, 1), GGmlType.F32, G)
@@ -190,6 +198,11 @@ class DecodeLayer:
         s = self.shape
         galois_matmul_add(self.w["wo"], ctx_flat, x, self.x2)  # x2 = x + Wo ctx
         # feed-forward block (SwiGLU)
+        if self.attention_kernel:
+            # gate and up rows interleaved: silu(gate) * up is formed where the two sums meet, down takes it as it is
+            galois_matmul_swiglu(self.w["w_gate_up"], self.x2, self.a, rms_gain=self.ffn_norm, eps=s.eps)
+            galois_matmul_fused(self.w["w_down"], self.a, self.out, res=self.x2)  # out = x2 + Wdown a
+            return self.out
         # rows [0, ffn) = gate, [ffn, 2 ffn) = up
         galois_matmul_fused(self.w["w_gate_up"], self.x2, self.gu, rms_gain=self.ffn_norm, eps=s.eps)
         g = self.gu.view((s.ffn, 1), (1, s.ffn, s.ffn, s.ffn))

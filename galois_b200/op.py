@@ -137,6 +137,29 @@ def galois_matmul_fused(src0: Tensor, src1: Tensor, dst: Tensor, *, rms_gain: Te
     _check(ctx, rc, "galois_matmul_fused")
 
 
+def galois_matmul_swiglu(src0: Tensor, src1: Tensor, dst: Tensor, *, rms_gain: Tensor | None = None, eps: float = 0.0) -> None:
+    """Gate and up projection with their SwiGLU product for a weight whose rows are interleaved at upload
+    (row 2i = gate_i, row 2i + 1 = up_i): dst[i] = galois_mul(galois_unary(Silu)(gate_i . t), up_i . t) with
+    t = src1 or rms_norm + gain of it; bit-identical to the separate calls (src/op.rs:3093-3111, 3232-3256,
+    3113-3127).  dst is {N / 2, batch}.  Not part of the reference API."""
+    import ctypes as C
+
+    from ._lib import GaloisPrologue
+
+    ops = [t for t in (src0, src1, dst, rms_gain) if t is not None]
+    ctx = _gpu_ctx(*ops)
+    _want(src0, GGmlType.Q4_0, "galois_matmul_swiglu src0")
+    for t in ops[1:]:
+        _want(t, GGmlType.F32, "galois_matmul_swiglu")
+    pro = GaloisPrologue()
+    if rms_gain is not None:
+        if rms_gain.dim().shape[0] < src1.dim().shape[0]:
+            raise GError("galois_matmul_swiglu: gain row shorter than the activation row")
+        pro.kind, pro.aux, pro.eps = 1, rms_gain.data_ptr(), eps
+    rc = lib.galois_b200_mul_mat_q4_0_f32_swiglu(ctx, _p(src0), _d(src0), _p(src1), _d(src1), C.byref(pro), _p(dst), _d(dst))
+    _check(ctx, rc, "galois_matmul_swiglu")
+
+
 def galois_rms_norm_mul(src: Tensor, gain: Tensor, dst: Tensor, eps: float) -> None:
     """galois_rms_norm (src/op.rs:3155-3169) followed by galois_mul with `gain` (src/op.rs:3113-3127) in one
     launch; bit-identical to the two calls.  Not part of the reference API."""

@@ -232,6 +232,16 @@ typedef struct galois_b200_prologue {
 int galois_b200_mul_mat_q4_0_f32_fused(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
                                        const galois_dim* xd, const galois_b200_prologue* pro, const float* res,
                                        const galois_dim* rd, float* dst, const galois_dim* dd);
+/* Gate and up projection of a SwiGLU feed-forward block with their product, for a weight whose rows are
+ * interleaved at upload (row 2i = gate_i, row 2i + 1 = up_i):
+ *   t   = pro ? rms_norm + gain of x : x
+ *   dst[b][i] = galois_mul(galois_unary(Silu)(W[2i] . t), W[2i + 1] . t)      (src/op.rs:3232-3256, :3113-3127)
+ * i.e. two galois_matmul calls, galois_unary(Silu) and galois_mul, same numbers bit for bit.  dst is {N / 2,
+ * batch}.  With one activation row and rows whose two halves meet in one warp of the streaming GEMV
+ * (K = 256 * 2^m) it is ONE launch; other shapes run the fused mat-mul into a context-owned buffer and a
+ * small pairing kernel. */
+int galois_b200_mul_mat_q4_0_f32_swiglu(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
+                                        const galois_dim* xd, const galois_b200_prologue* pro, float* dst, const galois_dim* dd);
 /* The same with no prologue and a residual: galois_matmul then galois_add. */
 int galois_b200_mul_mat_q4_0_f32_add(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x,
                                      const galois_dim* xd, const float* res, const galois_dim* rd, float* dst,

@@ -295,3 +295,41 @@ def test_auto_prepare_follows_alloc_upload_and_free(gb, dev, oracle):
         dev.set_mul_mat_variant(0)
         if ptr.value:
             gb.lib.galois_b200_free(dev.ctx, ptr)
+
+
+@pytest.mark.parametrize("n2,k,b", [(2 * 11008, 4096, 1), (2 * 300, 256, 1), (2 * 64, 1024, 1), (2 * 100, 11008, 1), (2 * 96, 512, 3)])
+@pytest.mark.parametrize("with_norm", [False, True])
+def test_swiglu_mat_vec_equals_the_separate_ops(gb, dev, oracle, n2, k, b, with_norm):
+    """galois_matmul_swiglu on a weight with gate / up rows interleaved = two mat-muls, Silu and Mul of the reference
+    API, bit for bit: in one launch where a warp holds both rows of a pair, otherwise through the pairing kernel."""
+    G = gb.Device.Gpu(dev)
+    f = n2 // 2
+    wg = oracle.quantize_q4_0(oracle.fill_normal(f * k, 240 + k, 0, 0.02).reshape(f, k))
+    wu = oracle.quantize_q4_0(oracle.fill_normal(f * k, 241 + k, 0, 0.02).reshape(f, k))
+    rb = k // 32 * 18
+    inter = np.stack([wg.reshape(f, rb), wu.reshape(f, rb)], axis=1).reshape(n2, rb)
+    x = oracle.fill_normal(b * k, 242).reshape(b, k)
+    gain = (1.0 + 0.1 * oracle.fill_normal(k, 243)).reshape(1, k)
+    xt = gb.Tensor.from_numpy(x, gb.GGmlType.F32, G)
+    gt = gb.Tensor.from_numpy(gain, gb.GGmlType.F32, G)
+    # the separate ops
+    h = gb.Tensor.zeros((k, b), gb.GGmlType.F32, G)
+    if with_norm:
+        gb.galois_rms_norm(xt, h, 1e-6)
+        gb.galois_mul(h, gt, h)
+    else:
+        h = xt
+    g_out, u_out = gb.Tensor.zeros((f, b), gb.GGmlType.F32, G), gb.Tensor.zeros((f, b), gb.GGmlType.F32, G)
+    gb.galois_matmul(gb.Tensor.from_raw(wg, (k, f), gb.GGmlType.Q4_0, G), h, g_out)
+    gb.galois_matmul(gb.Tensor.from_raw(wu, (k, f), gb.GGmlType.Q4_0, G), h, u_out)
+    a = gb.Tensor.zeros((f, b), gb.GGmlType.F32, G)
+    gb.galois_unary(g_out, a, gb.UnaryOp.Silu)
+    gb.galois_mul(a, u_out, a)
+    want = a.to_numpy()
+    got = gb.Tensor.zeros((f, b), gb.GGmlType.F32, G)
+    l0 = dev.launch_count()
+    gb.galois_matmul_swiglu(gb.Tensor.from_raw(inter, (k, n2), gb.GGmlType.Q4_0, G), xt, got, rms_gain=gt if with_norm else None, eps=1e-6)
+    launches = dev.launch_count() - l0
+    if b == 1 and k in (256, 512, 1024, 4096):
+        assert launches == 1
+    assert np.array_equal(got.to_numpy().view(np.uint32), want.view(np.uint32))
