@@ -155,7 +155,7 @@ __device__ __forceinline__ uint32_t ldg_word_a2(const uint8_t* a) {
 // additions over super-blocks differs from the kernel above.
 // Needs the tensor's first byte on a 4-byte boundary (blocks inside it may sit at 2 mod 4).
 template <int NB>
-__global__ void __launch_bounds__(256) mul_mat_q6k_words_kernel(const uint8_t* __restrict__ w, int64_t nb01, int64_t nb02, int64_t nb03, int64_t ne02,
+__global__ void __launch_bounds__(256, NB == 1 ? 6 : 4) mul_mat_q6k_words_kernel(const uint8_t* __restrict__ w, int64_t nb01, int64_t nb02, int64_t nb03, int64_t ne02,
                                                                 int64_t ne03, const int8_t* __restrict__ xq, const float* __restrict__ xd,
                                                                 float* __restrict__ dst, int64_t nb1, int64_t nb2, int64_t nb3, int K, int64_t N,
                                                                 int64_t ne11, int64_t ne12, int64_t ne13) {
@@ -181,6 +181,12 @@ __global__ void __launch_bounds__(256) mul_mat_q6k_words_kernel(const uint8_t* _
     float acc[NB];
 #pragma unroll
     for (int b = 0; b < NB; b++) acc[b] = 0.0f;
+    // This lane's super-blocks are sbi, sbi + 4, ...: 840 bytes apart, so they all sit at the same offset mod 4.
+    // Five aligned words and a funnel shift by 0 or 16 bits give the four words of a 16-byte piece either way
+    // (the fifth word lies inside the super-block for both pieces).
+    const uint8_t* blk0 = wrow + sbi * Q6K_BYTES;
+    const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(blk0) & 2);
+    const uint32_t fshift = mis * 8;
 #pragma unroll Q6K_UNROLL
     for (int sb0 = 0; sb0 < nsb; sb0 += 4) {
         const int sb = sb0 + sbi;
@@ -188,10 +194,15 @@ __global__ void __launch_bounds__(256) mul_mat_q6k_words_kernel(const uint8_t* _
         int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0}, sc_lo = 0, sc_hi = 0;
         float dw = 0.0f;
         if (live) {
-            const uint8_t* blk = wrow + sb * Q6K_BYTES;
+            const uint8_t* blk = blk0 + sb0 * Q6K_BYTES;
+            const uint32_t* pl = reinterpret_cast<const uint32_t*>(blk - mis + ql_off);
+            const uint32_t* ph = reinterpret_cast<const uint32_t*>(blk - mis + qh_off);
+            uint32_t wl[5], wh[5];
+#pragma unroll
+            for (int i = 0; i < 5; i++) wl[i] = __ldg(pl + i), wh[i] = __ldg(ph + i);
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const uint32_t ql = ldg_word_a2(blk + ql_off + 4 * i), qh = ldg_word_a2(blk + qh_off + 4 * i);
+                const uint32_t ql = __funnelshift_r(wl[i], wl[i + 1], fshift), qh = __funnelshift_r(wh[i], wh[i + 1], fshift);
                 const uint32_t l6 = (ql & 0x0F0F0F0Fu) | (((qh >> sh_lo) & 0x03030303u) << 4);
                 const uint32_t h6 = ((ql >> 4) & 0x0F0F0F0Fu) | (((qh >> sh_hi) & 0x03030303u) << 4);
                 // one activation row: keep the quants 0..63 and subtract 32 * (sum of the activations) below
