@@ -137,14 +137,6 @@ __global__ void __launch_bounds__(128) mul_mat_q6k_kernel(const uint8_t* __restr
     }
 }
 
-// A 32-bit word at a 2-byte-aligned address: one aligned load, or two and a funnel shift (the second
-// word of the misaligned case lies inside the same super-block for every field read this way).
-__device__ __forceinline__ uint32_t ldg_word_a2(const uint8_t* a) {
-    if ((reinterpret_cast<uintptr_t>(a) & 2) == 0) return __ldg(reinterpret_cast<const uint32_t*>(a));
-    const uint32_t* p = reinterpret_cast<const uint32_t*>(a - 2);
-    return __funnelshift_r(__ldg(p), __ldg(p + 1), 16);
-}
-
 // The same product with 32-bit loads and dp4a.  Eight lanes share a super-block, so a warp works on four
 // super-blocks of its row at a time: lane (sbi = lane / 8, u = lane % 8) takes 16 consecutive bytes of ql
 // (half j = u / 4, group grp = (u / 2) % 2, byte positions p0 = 16 (u % 2) .. + 15) and the matching 16
