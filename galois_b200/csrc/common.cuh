@@ -41,6 +41,7 @@ struct galois_b200_ctx {
     int hazard_tracking;   // 0: every kernel waits for its predecessors at entry (no deferred waits)
     int hazard_unknown;
     int hazard_n;
+    int deferred_streak;     // deferred one-row launches since the last launch of another kind
     int64_t sync_counts[3];  // one-row GEMV launches by ordering mode: wait at entry, deferred wait, barrier
     struct { uintptr_t lo, hi; } hazard[GB_HAZARD_MAX];
     int64_t launches;      // kernels launched through this context
