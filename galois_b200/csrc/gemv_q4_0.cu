@@ -461,10 +461,10 @@ gemv_plan plan_gemv(const galois_b200_ctx* ctx, int64_t K, int64_t N, int64_t B,
     if (p.smem > 227 * 1024) return p;
     const int64_t nchunks = (N + rows_per_chunk - 1) / rows_per_chunk;
     int cps = ctx->tune_ctas_per_sm > 0 ? ctx->tune_ctas_per_sm : (GEMV_WARPS == 8 ? 1 : 2);
-    // ... except the first deferred launch behind a launch that waited at entry: it has only that one kernel to
-    // share the SMs with (the K after Q, the up after gate of a decoder layer) and takes two CTAs per SM
-    // (measured: 22-op layer 97.2 -> 94.5 us, 9-kernel layer 70.7 -> 68.1 us, the FFN mix unchanged)
-    if (deferred) cps = ctx->tune_dcps > 0 ? ctx->tune_dcps : (ctx->deferred_streak == 0 ? 2 : 1);
+    // ... except the first two deferred launches behind a launch that waited at entry: they have few kernels to
+    // share the SMs with (K and V after Q, up after gate of a decoder layer) and take two CTAs per SM
+    // (measured: 22-op layer 97.2 -> 93.3 us, 9-kernel layer 70.7 -> 67.6 us, the FFN mix unchanged)
+    if (deferred) cps = ctx->tune_dcps > 0 ? ctx->tune_dcps : (ctx->deferred_streak < 2 ? 2 : 1);
     int64_t grid = (int64_t)ctx->sm_count * cps;
     if (grid > (nchunks + GEMV_WARPS - 1) / GEMV_WARPS) grid = (nchunks + GEMV_WARPS - 1) / GEMV_WARPS;
     if (grid < 1) grid = 1;
