@@ -452,7 +452,7 @@ static bool skinny_beats_tc(const galois_b200_ctx* ctx, const void* w, const gal
     const double skinny_us = ceil(B / 16.0) * pass_us;
     // a weight the context may prepare on first use counts as prepared
     const bool prepared = gb_mm_tc_prepared(const_cast<galois_b200_ctx*>(ctx), w, wd) || (ctx->auto_prepare && gb_tracked(ctx, w));
-    const double bn = B <= 64.0 ? 64.0 : 128.0;
+    const double bn = prepared ? (double)gb_mm_tp_bn(ctx, (int64_t)N, (int64_t)B) : (B <= 64.0 ? 64.0 : 128.0);
     const double tiles = ceil(N / 128.0) * ceil(B / bn);
     const double per_block = !prepared ? 0.68 : (bn == 64.0 ? 0.20 : 0.36);
     const double tc_us = ceil(tiles / (double)ctx->sm_count) * (K / 32.0) * per_block + (prepared ? 3.5 : 0.0);

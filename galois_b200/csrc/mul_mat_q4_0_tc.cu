@@ -763,13 +763,20 @@ static int launch_tp(galois_b200_ctx* ctx, const gb_weight_pack* p, const uint8_
     return 0;
 }
 
+// Column-tile width of the prepared-weight kernel: 128, or 64 where 128-column tiles would leave more than half of
+// the SMs without a CTA (4096 x 4096 x 256: 64 tiles of 128 columns 48.8 us, 128 tiles of 64 columns 35.2 us).
+int gb_mm_tp_bn(const galois_b200_ctx* ctx, int64_t N, int64_t B) {
+    const int64_t tiles128 = ((N + TC_M - 1) / TC_M) * ((B + 127) / 128);
+    return (B <= 64 || tiles128 * 2 <= ctx->sm_count) ? 64 : 128;
+}
+
 // The GEMM on the prepared copy of w (two launches: quantiser, GEMM); scratch as for gb_mm_q4_0_tc.
 int gb_mm_q4_0_tp(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
                   const galois_dim* dd, void* scratch) {
     const gb_weight_pack* p = tp_find(ctx, w);
     if (p == nullptr) return gb_fail(ctx, GALOIS_B200_E_STATE, "mul_mat_q4_0: weight not prepared");
     const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
-    const int BN = pick_bn(B);
+    const int BN = gb_mm_tp_bn(ctx, N, B);
     const int Bp = (B + BN - 1) / BN * BN;
     uint8_t* qs = (uint8_t*)scratch;
     uint8_t* xs = qs + (((size_t)Bp * K + 255) & ~(size_t)255);

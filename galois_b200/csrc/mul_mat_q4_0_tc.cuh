@@ -28,6 +28,7 @@ int gb_mm_tc_release(galois_b200_ctx* ctx, const void* w);
 int gb_mm_tc_release_range(galois_b200_ctx* ctx, const void* lo, const void* hi);
 void gb_mm_tc_release_all(galois_b200_ctx* ctx);
 bool gb_mm_tc_prepared(galois_b200_ctx* ctx, const void* w, const galois_dim* wd);
+int gb_mm_tp_bn(const galois_b200_ctx* ctx, int64_t N, int64_t B);
 // The GEMM on the prepared copy (quantiser + GEMM, two launches; same scratch as gb_mm_q4_0_tc).
 int gb_mm_q4_0_tp(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
                   const galois_dim* dd, void* scratch);
