@@ -444,7 +444,7 @@ int gb_validate_mul_mat(galois_b200_ctx* ctx, const void* w, const galois_dim* w
 // the tcgen05 kernel (one 128 x 128 output tile per CTA, whole waves of CTAs) apply; the choice follows
 // a cost model fitted to measurements on a B200: a skinny pass costs max(6.8 us, weight bytes at
 // 1.6 TB/s) (passes after the first read the weights from L2), a wave of tensor-core tiles 0.68 us
-// per 32-element block of K; on a weight prepared at upload 0.36 us (128-column tiles) or 0.20 us (64-column
+// (0.47 us with 64-column tiles) per 32-element block of K; on a weight prepared at upload 0.36 us (128-column tiles) or 0.20 us (64-column
 // tiles, up to 64 activation rows) plus 3.5 us for the quantiser in front of it.
 static bool skinny_beats_tc(const galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const galois_dim* xd) {
     const double K = (double)wd->ne[0], N = (double)wd->ne[1], B = (double)xd->ne[1];
@@ -452,9 +452,9 @@ static bool skinny_beats_tc(const galois_b200_ctx* ctx, const void* w, const gal
     const double skinny_us = ceil(B / 16.0) * pass_us;
     // a weight the context may prepare on first use counts as prepared
     const bool prepared = gb_mm_tc_prepared(const_cast<galois_b200_ctx*>(ctx), w, wd) || (ctx->auto_prepare && gb_tracked(ctx, w));
-    const double bn = prepared ? (double)gb_mm_tp_bn(ctx, (int64_t)N, (int64_t)B) : (B <= 64.0 ? 64.0 : 128.0);
+    const double bn = (double)gb_mm_tp_bn(ctx, (int64_t)N, (int64_t)B);
     const double tiles = ceil(N / 128.0) * ceil(B / bn);
-    const double per_block = !prepared ? 0.68 : (bn == 64.0 ? 0.20 : 0.36);
+    const double per_block = !prepared ? (bn == 64.0 ? 0.47 : 0.68) : (bn == 64.0 ? 0.20 : 0.36);
     const double tc_us = ceil(tiles / (double)ctx->sm_count) * (K / 32.0) * per_block + (prepared ? 3.5 : 0.0);
     return skinny_us <= tc_us;
 }

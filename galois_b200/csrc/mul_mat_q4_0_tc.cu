@@ -386,7 +386,7 @@ size_t gb_mm_tc_scratch_bytes(const galois_dim* wd, const galois_dim* xd) {
 int gb_mm_q4_0_tc(galois_b200_ctx* ctx, const void* w, const galois_dim* wd, const float* x, const galois_dim* xd, float* dst,
                   const galois_dim* dd, void* scratch) {
     const int K = (int)wd->ne[0], N = (int)wd->ne[1], B = (int)xd->ne[1];
-    const int BN = pick_bn(B);
+    const int BN = gb_mm_tp_bn(ctx, N, B);  // 64-column tiles where 128-column ones would leave most SMs idle
     const int Bp = (B + BN - 1) / BN * BN;
     uint8_t* qs = (uint8_t*)scratch;
     uint8_t* xs = qs + (((size_t)Bp * K + 255) & ~(size_t)255);
